@@ -1,0 +1,442 @@
+#!/usr/bin/env python
+"""Benchmark of the decay-rule (LFW) hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload train|decode|long]
+                    [--gates raw_f1|raw|sigmoid] [--impl ours|reference]
+
+Default workload ("train"): one LFW layer at GPT-2-small shape, fp16, B*H=96, T=1024,
+D=K=64, x,q,k,f_key ~ N(0,1) with q,k scaled by 1/8, forget gate f = 1, zero initial state;
+a step is one forward + backward over the whole batch.  Prints ONE JSON line on stdout
+(rank 0):
+
+  value ..... tokens/s with the inputs resident in HBM, kernels called through the C ABI,
+              timed with CUDA events over exactly K steps, max over ranks
+  e2e ....... the same metric through LFWFunction.apply with HOST (pinned) inputs: every step
+              copies the six inputs to the device, runs forward + backward through autograd and
+              copies outputs, next state and the six gradients back
+  roofline .. algorithmic bytes of the slower of the two calls (forward / backward) over its
+              measured duration, against the measured HBM copy bandwidth
+  cpu_baseline  the per-step PyTorch restatement of the reference's TorchScript path
+              (oracle/torch_port.py) on this machine's host cores, on a bounded sample
+
+`--impl reference` times that CPU path alone and prints the same line with "impl": "reference".
+Under torchrun each rank runs the full workload on its own GPU (weak scaling, no collective on
+the data path); rank 0 reports the aggregate.
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, T, D, K)
+    "train": (96, 1024, 64, 64),     # single layer, GPT-2-small shape, fwd + bwd
+    "decode": (4096, 1, 64, 64),     # T=1 decode step, GPT-2-medium heads x batch 256
+    "long": (16, 16384, 128, 128),   # long-sequence prefill + backward
+}
+CPU_SAMPLE_ROWS = {"train": 16, "decode": 4096, "long": 1}
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--workload", default="train", choices=sorted(WORKLOADS))
+    p.add_argument("--gates", default="raw_f1", choices=["raw_f1", "raw", "sigmoid"])
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--seed", type=int, default=0)
+    return p.parse_args()
+
+
+def make_inputs(torch, B, T, D, K, gates, seed, workload):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, T, D, generator=g)
+    q = torch.randn(B, T, K, generator=g) / math.sqrt(K)
+    k = torch.randn(B, T, K, generator=g) / math.sqrt(K)
+    fk = torch.randn(B, T, K, generator=g)
+    if gates == "sigmoid":
+        fk = torch.sigmoid(fk)
+    if gates == "raw_f1":
+        f = torch.ones(B, T, D)
+    else:
+        f = torch.sigmoid(torch.randn(B, T, D, generator=g))
+    if workload == "train":
+        s = torch.zeros(B, D, K)
+    else:
+        s = torch.randn(B, D, K, generator=g) * 0.1
+    go = torch.randn(B, T, D, generator=g)
+    gs = torch.randn(B, D, K, generator=g)
+    return [x, f, q, k, fk, s, go, gs]
+
+
+def algorithmic_bytes(B, T, D, K, e=2):
+    """Bytes the recurrence must move (fp16 I/O), excluding checkpoints and scratch."""
+    n = B * T
+    fwd = e * (n * (2 * D + 3 * K) + n * D + 2 * B * D * K)
+    bwd = e * (n * D + 2 * n * (2 * D + 3 * K) + 3 * B * D * K)
+    return fwd, bwd
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples taken while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                c = [t.strip() for t in line.split(",")]
+                if len(c) < 9:
+                    continue
+                try:
+                    sm.append(float(c[1]))
+                    mx.append(float(c[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                      "sw_power_cap"), c[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out["sm_mhz"] = statistics.median(sm)
+            out["sm_max_mhz"] = max(mx)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def cpu_reference_run(workload, gates, steps, warmup, seed):
+    """Times oracle/torch_port (the port of the reference's TorchScript CPU path) on a bounded
+    sample of the workload; returns (tokens/s or steps/s, description dict)."""
+    import torch
+    from oracle import torch_port
+
+    B, T, D, K = WORKLOADS[workload]
+    rows = min(B, CPU_SAMPLE_ROWS[workload])
+    x, f, q, k, fk, s, go, gs = [t[:rows].contiguous() for t in
+                                 make_inputs(torch, rows, T, D, K, gates, seed, workload)]
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        if workload == "decode":
+            with torch.no_grad():
+                torch_port.lfw_loop(x, f, q, k, fk, s)
+        else:
+            torch_port.lfw_fwd_bwd(x, f, q, k, fk, s, go, gs)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    med = statistics.median(times)
+    value = rows * T / med
+    desc = {
+        "value": value, "unit": "tokens/s", "cores": torch.get_num_threads(),
+        "host_cpus": os.cpu_count(), "kind": "port",
+        "sample": "%d of %d batch rows, T=%d, D=K=%d, fp32, %s; median of %d calls after %d warm-up"
+                  % (rows, B, T, D, "forward only" if workload == "decode" else "forward+backward",
+                     len(times), warmup),
+        "s_per_call": med,
+    }
+    return value, desc
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 5))
+    warmup = max(2, min(args.warmup, 3))
+    B, T, D, K = WORKLOADS[args.workload]
+    value, desc = cpu_reference_run(args.workload, args.gates, steps, warmup, args.seed)
+    line = {
+        "impl": "reference", "metric": metric_name(args.workload), "value": value,
+        "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+        "ms_per_step": desc["s_per_call"] * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, B, T, D, K),
+        "cpu_baseline": desc,
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def metric_name(workload):
+    return {"train": "lfw_fwd_bwd_tokens_per_s", "decode": "lfw_decode_tokens_per_s",
+            "long": "lfw_fwd_bwd_tokens_per_s"}[workload]
+
+
+def workload_config(args, B, T, D, K):
+    return {
+        "workload": "%s: LFW %s, B*H=%d per GPU, T=%d, D=K=%d, fp16 I/O, fp32 state arithmetic"
+                    % (args.workload, "forward (decode step)" if args.workload == "decode"
+                       else "forward+backward", B, T, D),
+        "gates": {"raw_f1": "f=1, f_key~N(0,1)", "raw": "f=sigmoid(N(0,1)), f_key~N(0,1)",
+                  "sigmoid": "f, f_key = sigmoid(N(0,1))"}[args.gates],
+        "sharding": "batch*head rows split across GPUs, no collective",
+    }
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the kernels have no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from t2fw_b200 import _lib, cabi
+    from t2fw_b200.functional_lfw import LFWFunction
+
+    lib = _lib.load_core()
+    B, T, D, K = WORKLOADS[args.workload]
+    decode = args.workload == "decode"
+    dtype = torch.float16
+
+    # Rotating input sets so that consecutive steps never find their data in the 126 MB L2.
+    touched = 2 * (B * T * (3 * D + 3 * K) + 3 * B * D * K) * (1 if decode else 2)
+    n_sets = max(2, min(8, int(math.ceil(500e6 / touched))))
+    base = [t.to(dtype).to(dev).contiguous() for t in
+            make_inputs(torch, B, T, D, K, args.gates, args.seed + 1000 * rank, args.workload)]
+    # distinct data per set without regenerating on the host: roll along the batch axis
+    sets = [base] + [[t.roll(i, 0).contiguous() for t in base] for i in range(1, n_sets)]
+
+    C = cabi.ckpt_every_for(T, D, K, dtype)
+    slots = int(lib.t2fw_lfw_ckpt_slots(T, C))
+    outs = [torch.empty(B, T, D, dtype=dtype, device=dev) for _ in range(n_sets)]
+    ckpts = [torch.empty(B, slots, D, K, dtype=dtype, device=dev) for _ in range(n_sets)]
+    grads = None if decode else [[torch.empty_like(t) for t in s[:6]] for s in sets]
+    code = cabi.dtype_code(base[0])
+    fsb = lib.t2fw_lfw_forward_scratch_bytes(B, T, D, K, code, C)
+    bsb = lib.t2fw_lfw_backward_scratch_bytes(B, T, D, K, code, C)
+    fscr = torch.empty(max(fsb, 1), dtype=torch.uint8, device=dev)
+    bscr = torch.empty(max(bsb, 1), dtype=torch.uint8, device=dev)
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    fwd_ms, bwd_ms = [], []
+
+    if decode:
+        # chained decode: each set's state advances every time the set comes round; the new
+        # state is written to the set's other buffer (inputs are never overwritten in place)
+        state_a = [s[5] for s in sets]
+        state_b = [torch.empty_like(s[5]) for s in sets]
+
+        def step(i, record=None):
+            j = i % n_sets
+            x, f, q, k, fk = sets[j][:5]
+            even = (i // n_sets) % 2 == 0
+            src, dst = (state_a[j], state_b[j]) if even else (state_b[j], state_a[j])
+            if record:
+                record[0].record()
+            cabi.lfw_forward(x, f, q, k, fk, src, ckpt_every=C, out=outs[j],
+                             ckpt=dst.view(B, 1, D, K), scratch=fscr)
+            if record:
+                record[1].record()
+    else:
+        def step(i, record=None):
+            j = i % n_sets
+            x, f, q, k, fk, s, go, gs = sets[j]
+            if record:
+                record[0].record()
+            cabi.lfw_forward(x, f, q, k, fk, s, ckpt_every=C, out=outs[j], ckpt=ckpts[j], scratch=fscr)
+            if record:
+                record[1].record()
+            cabi.lfw_backward(go, gs, x, f, q, k, fk, s, ckpts[j], ckpt_every=C, grads=grads[j],
+                              scratch=bscr)
+            if record:
+                record[2].record()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.t2fw_launch_count()
+    records = [[ev(), ev(), ev()] for _ in range(args.steps)]
+    t_start, t_end = ev(), ev()
+    t_start.record()
+    for i in range(args.steps):
+        step(args.warmup + i, records[i])
+    t_end.record()
+    barrier()
+    launches = lib.t2fw_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t_start.elapsed_time(t_end)
+    for r in records:
+        fwd_ms.append(r[0].elapsed_time(r[1]))
+        if not decode:
+            bwd_ms.append(r[1].elapsed_time(r[2]))
+    tmax = torch.tensor([total_ms], device=dev)
+    if world > 1:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    total_ms = float(tmax.item())
+    tokens = B * T * args.steps * world
+    value = tokens / (total_ms * 1e-3)
+
+    # ---- end to end through the public API with host buffers -------------------------------
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = max(3, min(args.steps, 10))
+        host = [t.to(dtype).pin_memory() for t in
+                make_inputs(torch, B, T, D, K, args.gates, args.seed + 1000 * rank, args.workload)]
+        n_res = 2 if decode else 8
+        res_host = None
+        h2d = sum(t.numel() * t.element_size() for t in (host[:6] if decode else host))
+        d2h = 0
+
+        def e2e_step():
+            nonlocal res_host, d2h
+            devs = [t.to(dev, non_blocking=True) for t in (host[:6] if decode else host)]
+            if decode:
+                with torch.no_grad():
+                    out, nxt = LFWFunction.apply(*devs[:6])
+                results = [out, nxt]
+            else:
+                leaves = [t.requires_grad_(True) for t in devs[:6]]
+                out, nxt = LFWFunction.apply(*leaves)
+                g = torch.autograd.grad([out, nxt], leaves, [devs[6], devs[7]])
+                results = [out, nxt] + list(g)
+            if res_host is None:
+                res_host = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in results]
+                d2h = sum(r.numel() * r.element_size() for r in results)
+            for h, r in zip(res_host, results):
+                h.copy_(r, non_blocking=True)
+            torch.cuda.synchronize()
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        e0, e1 = ev(), ev()
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        wall = time.perf_counter() - t0
+        e2e_ms = max(e0.elapsed_time(e1), 0.0)
+        t2 = torch.tensor([e2e_ms], device=dev)
+        if world > 1:
+            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t2.item())
+        e2e = {"value": B * T * e2e_steps * world / (e2e_ms * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+               "ms_per_step": e2e_ms / e2e_steps, "api": "LFWFunction.apply + autograd, pinned host buffers",
+               "wall_ms_per_step": wall * 1e3 / e2e_steps}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the slower call -------------------------------------------------------
+    fb, bb = algorithmic_bytes(B, T, D, K)
+    peak, peak_kind = measured_hbm_peak()
+    f_ms = statistics.mean(fwd_ms)
+    b_ms = statistics.mean(bwd_ms) if bwd_ms else 0.0
+    if b_ms >= f_ms and not decode:
+        which, alg, dur = "backward call (all kernels of t2fw_lfw_backward)", bb, b_ms
+    else:
+        which, alg, dur = "forward call (all kernels of t2fw_lfw_forward)", fb, f_ms
+    achieved = alg / (dur * 1e-3) / 1e9
+    roofline = {
+        "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind + " copy bandwidth",
+        "kernel": which, "algorithmic_bytes_per_launch": alg, "avg_ms": dur,
+        "fwd_ms": f_ms, "bwd_ms": b_ms,
+        "whole_step_frac": ((fb + (0 if decode else bb)) / ((f_ms + b_ms) * 1e-3) / 1e9) / peak,
+    }
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        _, cpu = cpu_reference_run(args.workload, args.gates, 3, 2, args.seed)
+
+    line = {
+        "metric": metric_name(args.workload), "value": value, "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 state arithmetic, f16 I/O", "data": "synthetic",
+        "config": dict(workload_config(args, B, T, D, K),
+                       l2="inputs larger than L2: %d rotating input/output sets" % n_sets,
+                       ckpt_every=C),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+        "roofline": roofline, "cpu_baseline": cpu,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

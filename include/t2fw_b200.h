@@ -1,0 +1,125 @@
+/*
+ * t2fw_b200 — C ABI of the B200 (sm_100a) fast-weight recurrence library.
+ *
+ * This is the seam a host binding links against: plain pointers, 64-bit sizes, an opaque
+ * stream handle (a cudaStream_t passed as void*), an integer status.  No torch types.
+ * All data pointers are DEVICE pointers to dense row-major arrays; every entry point is
+ * asynchronous on the given stream and never synchronises, allocates or frees.
+ * Inputs are never written.
+ *
+ * Shapes (the reference's names):
+ *   value/forget/outputs and their gradients ... [B, T, D]
+ *   query/key/f_key and their gradients ........ [B, T, K]   (K is "M" in the delta rule)
+ *   state, next_state and their gradients ...... [B, D, K]
+ *   ckpt_states ................................ [B, n_slots, D, K], slot j = state after step
+ *                                                min((j+1)*ckpt_every, T); the last slot is S_T
+ *
+ * Each function below names the reference interface it replaces (path inside the reference
+ * project : lines).
+ */
+#ifndef T2FW_B200_H
+#define T2FW_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types; the reference dispatches half, float and double
+ * (t2fw/csrc/lfw_kernel.cu:157, AT_DISPATCH_FLOATING_TYPES_AND_HALF); bf16 is an addition */
+enum {
+  T2FW_F16 = 0,
+  T2FW_BF16 = 1,
+  T2FW_F32 = 2,
+  T2FW_F64 = 3
+};
+
+/* status codes (0 = success) */
+enum {
+  T2FW_OK = 0,
+  T2FW_ERR_BAD_ARG = 1,     /* null pointer, non-positive size, unknown dtype ... */
+  T2FW_ERR_UNSUPPORTED = 2, /* shape outside what the kernels cover */
+  T2FW_ERR_SCRATCH = 3,     /* scratch buffer missing or too small */
+  T2FW_ERR_CUDA = 4         /* a CUDA runtime call or launch failed */
+};
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char *t2fw_last_error(void);
+
+/* Library version (major*10000 + minor*100 + patch). */
+int t2fw_version(void);
+
+/* Number of kernel launches this process has issued through the library so far. */
+int64_t t2fw_launch_count(void);
+
+/* Checkpoint interval the library recommends for a problem, and the slot count that follows
+ * from an interval.  The reference stores the state of EVERY step
+ * (t2fw/csrc/lfw_kernel.cu:140-144); here only every ckpt_every-th state is kept and the
+ * backward pass recomputes the rest. */
+int64_t t2fw_lfw_default_ckpt_every(int64_t T, int64_t D, int64_t K, int dtype);
+int64_t t2fw_lfw_ckpt_slots(int64_t T, int64_t ckpt_every);
+
+/* Bytes of scratch (global memory beyond inputs and outputs, 256-byte aligned) that the
+ * corresponding call needs for this problem; 0 means the scratch pointer may be NULL. */
+size_t t2fw_lfw_forward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K, int dtype,
+                                      int64_t ckpt_every);
+size_t t2fw_lfw_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K, int dtype,
+                                       int64_t ckpt_every);
+size_t t2fw_dfw_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t M, int dtype);
+
+/*
+ * Decay rule forward:  S_t = (f_t f_key_t^T) .* S_{t-1} + x_t k_t^T ,  o_t = S_t q_t.
+ * Replaces torch.ops.lfw.forward = lfw_forward (t2fw/csrc/lfw.cpp:28-48), i.e. the scan
+ * kernel lfw_cuda_forward (t2fw/csrc/lfw_kernel.cu:124-171) plus the einsum that forms the
+ * outputs (t2fw/csrc/lfw.cpp:45).  Writes outputs and ckpt_states (both of `dtype`).
+ */
+int t2fw_lfw_forward(const void *x, const void *f, const void *q, const void *k,
+                     const void *f_key, const void *state,
+                     void *outputs, void *ckpt_states,
+                     int64_t B, int64_t T, int64_t D, int64_t K, int dtype, int64_t ckpt_every,
+                     void *scratch, size_t scratch_bytes, void *stream);
+
+/*
+ * Decay rule backward: all six gradients in forward-argument order.
+ * Replaces torch.ops.lfw.backward = lfw_backward (t2fw/csrc/lfw.cpp:50-96), i.e. the reverse
+ * scan lfw_cuda_backward (t2fw/csrc/lfw_kernel.cu:173-228), the five einsums and the two
+ * in-place multiplies (t2fw/csrc/lfw.cpp:84-93).  `state` is the forward call's initial state
+ * and `ckpt_states` the tensor the forward call wrote with the same ckpt_every.
+ */
+int t2fw_lfw_backward(const void *grad_output, const void *grad_state,
+                      const void *x, const void *f, const void *q, const void *k,
+                      const void *f_key, const void *state, const void *ckpt_states,
+                      void *d_x, void *d_f, void *d_q, void *d_k, void *d_f_key, void *d_state,
+                      int64_t B, int64_t T, int64_t D, int64_t K, int dtype, int64_t ckpt_every,
+                      void *scratch, size_t scratch_bytes, void *stream);
+
+/*
+ * Delta rule forward:  o_t = S_{t-1} q_t ,  delta_t = v_t - S_{t-1} k_t ,
+ *                      S_t = S_{t-1} + delta_t k_t^T.
+ * Replaces torch.ops.dfw.forward = lfw_forward (t2fw/csrc/dfw.cpp:27-39) and its kernel
+ * (t2fw/csrc/dfw_kernel.cu:105-196, launcher :406-470).  `delta` ([B,T,D]) is kept for the
+ * backward pass; it is float for 16- and 32-bit dtypes and double for T2FW_F64.
+ */
+int t2fw_dfw_forward(const void *q, const void *k, const void *v, const void *state,
+                     void *outputs, void *final_state, void *delta,
+                     int64_t B, int64_t T, int64_t D, int64_t M, int dtype, void *stream);
+
+/*
+ * Delta rule backward: d_query, d_key, d_value, d_state.
+ * Replaces torch.ops.dfw.backward = lfw_backward (t2fw/csrc/dfw.cpp:41-64) and its two
+ * kernels (t2fw/csrc/dfw_kernel.cu:198-283 and :285-384, launcher :472-558).  Like the
+ * reference it needs neither the values nor the initial state: it walks the state backwards
+ * from final_state with the saved delta.
+ */
+int t2fw_dfw_backward(const void *grad_output, const void *grad_state,
+                      const void *q, const void *k, const void *delta, const void *final_state,
+                      void *d_q, void *d_k, void *d_v, void *d_state,
+                      int64_t B, int64_t T, int64_t D, int64_t M, int dtype,
+                      void *scratch, size_t scratch_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* T2FW_B200_H */

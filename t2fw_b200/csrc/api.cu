@@ -1,0 +1,139 @@
+// C ABI of the library (declared in include/t2fw_b200.h): argument checks and dispatch to the
+// kernel launchers.  Nothing here allocates, frees or synchronises.
+#include <atomic>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace t2fw {
+
+namespace {
+thread_local char g_err[512] = "";
+std::atomic<int64_t> g_launches{0};
+}  // namespace
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+}  // namespace t2fw
+
+using namespace t2fw;
+
+extern "C" {
+
+const char *t2fw_last_error(void) { return g_err; }
+
+int t2fw_version(void) { return 100; }
+
+int64_t t2fw_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int64_t t2fw_lfw_default_ckpt_every(int64_t T, int64_t D, int64_t K, int dtype) {
+  (void)T;
+  (void)dtype;
+  return (D >= 128 && K >= 128) ? 128 : 64;
+}
+
+int64_t t2fw_lfw_ckpt_slots(int64_t T, int64_t ckpt_every) {
+  if (T <= 0 || ckpt_every <= 0) return 0;
+  return ceil_div64(T, ckpt_every);
+}
+
+size_t t2fw_lfw_forward_scratch_bytes(int64_t, int64_t, int64_t, int64_t, int, int64_t) {
+  return 0;
+}
+
+size_t t2fw_lfw_backward_scratch_bytes(int64_t, int64_t, int64_t, int64_t, int, int64_t) {
+  return 0;
+}
+
+size_t t2fw_dfw_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t M, int dtype) {
+  (void)M;
+  // d_value is kept in float next to its 16-bit output for the column pass
+  if (dtype == T2FW_F16 || dtype == T2FW_BF16) return align_up((size_t)B * T * D * sizeof(float), 256);
+  return 0;
+}
+
+static int check_common(int64_t B, int64_t T, int64_t D, int64_t K, int dtype) {
+  T2FW_CHECK_ARG(dtype_size(dtype) != 0, "unknown dtype %d", dtype);
+  T2FW_CHECK_ARG(B > 0 && T > 0 && D > 0 && K > 0, "sizes must be positive (B=%lld T=%lld D=%lld K=%lld)",
+                 (long long)B, (long long)T, (long long)D, (long long)K);
+  return T2FW_OK;
+}
+
+int t2fw_lfw_forward(const void *x, const void *f, const void *q, const void *k,
+                     const void *f_key, const void *state, void *outputs, void *ckpt_states,
+                     int64_t B, int64_t T, int64_t D, int64_t K, int dtype, int64_t ckpt_every,
+                     void *scratch, size_t scratch_bytes, void *stream) {
+  (void)scratch;
+  (void)scratch_bytes;
+  int rc = check_common(B, T, D, K, dtype);
+  if (rc != T2FW_OK) return rc;
+  T2FW_CHECK_ARG(x && f && q && k && f_key && state && outputs && ckpt_states, "null pointer argument");
+  T2FW_CHECK_ARG(ckpt_every > 0, "ckpt_every must be positive");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (T == 1 && lfw_decode_supported(D, K, dtype)) {
+    rc = lfw_decode_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, D, K, dtype, st);
+    if (rc != T2FW_ERR_UNSUPPORTED) return rc;
+  }
+  return lfw_scan_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, T, D, K, dtype,
+                          ckpt_every, st);
+}
+
+int t2fw_lfw_backward(const void *grad_output, const void *grad_state, const void *x,
+                      const void *f, const void *q, const void *k, const void *f_key,
+                      const void *state, const void *ckpt_states, void *d_x, void *d_f, void *d_q,
+                      void *d_k, void *d_f_key, void *d_state, int64_t B, int64_t T, int64_t D,
+                      int64_t K, int dtype, int64_t ckpt_every, void *scratch,
+                      size_t scratch_bytes, void *stream) {
+  (void)scratch;
+  (void)scratch_bytes;
+  int rc = check_common(B, T, D, K, dtype);
+  if (rc != T2FW_OK) return rc;
+  T2FW_CHECK_ARG(grad_output && grad_state && x && f && q && k && f_key && state && ckpt_states &&
+                     d_x && d_f && d_q && d_k && d_f_key && d_state,
+                 "null pointer argument");
+  T2FW_CHECK_ARG(ckpt_every > 0, "ckpt_every must be positive");
+  return lfw_scan_backward(grad_output, grad_state, x, f, q, k, f_key, state, ckpt_states, d_x,
+                           d_f, d_q, d_k, d_f_key, d_state, B, T, D, K, dtype, ckpt_every,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int t2fw_dfw_forward(const void *q, const void *k, const void *v, const void *state,
+                     void *outputs, void *final_state, void *delta, int64_t B, int64_t T,
+                     int64_t D, int64_t M, int dtype, void *stream) {
+  int rc = check_common(B, T, D, M, dtype);
+  if (rc != T2FW_OK) return rc;
+  T2FW_CHECK_ARG(q && k && v && state && outputs && final_state && delta, "null pointer argument");
+  return dfw_scan_forward(q, k, v, state, outputs, final_state, delta, B, T, D, M, dtype,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int t2fw_dfw_backward(const void *grad_output, const void *grad_state, const void *q,
+                      const void *k, const void *delta, const void *final_state, void *d_q,
+                      void *d_k, void *d_v, void *d_state, int64_t B, int64_t T, int64_t D,
+                      int64_t M, int dtype, void *scratch, size_t scratch_bytes, void *stream) {
+  int rc = check_common(B, T, D, M, dtype);
+  if (rc != T2FW_OK) return rc;
+  T2FW_CHECK_ARG(grad_output && grad_state && q && k && delta && final_state && d_q && d_k &&
+                     d_v && d_state,
+                 "null pointer argument");
+  const size_t need = t2fw_dfw_backward_scratch_bytes(B, T, D, M, dtype);
+  void *dv_acc = d_v;  // float / double outputs double as the accumulation-type copy
+  if (need != 0) {
+    if (scratch == nullptr || scratch_bytes < need) {
+      set_error("dfw backward needs %zu bytes of scratch, got %zu", need, scratch_bytes);
+      return T2FW_ERR_SCRATCH;
+    }
+    dv_acc = scratch;
+  }
+  return dfw_scan_backward(grad_output, grad_state, q, k, delta, final_state, d_q, d_k, d_v,
+                           d_state, dv_acc, B, T, D, M, dtype, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

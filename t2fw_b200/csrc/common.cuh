@@ -1,0 +1,107 @@
+// Shared helpers for the sm_100a kernels: element-type traits, warp reductions, error plumbing.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/t2fw_b200.h"
+
+namespace t2fw {
+
+// ---- error plumbing -------------------------------------------------------------------
+void set_error(const char *fmt, ...);
+void count_launch(int n = 1);
+
+#define T2FW_CHECK_ARG(cond, ...)                 \
+  do {                                            \
+    if (!(cond)) {                                \
+      ::t2fw::set_error(__VA_ARGS__);             \
+      return T2FW_ERR_BAD_ARG;                    \
+    }                                             \
+  } while (0)
+
+#define T2FW_CHECK_CUDA(expr)                                                        \
+  do {                                                                               \
+    cudaError_t _e = (expr);                                                         \
+    if (_e != cudaSuccess) {                                                         \
+      ::t2fw::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e),      \
+                        __FILE__, __LINE__);                                         \
+      return T2FW_ERR_CUDA;                                                          \
+    }                                                                                \
+  } while (0)
+
+#define T2FW_CHECK_LAUNCH(n)                                                         \
+  do {                                                                               \
+    ::t2fw::count_launch(n);                                                         \
+    T2FW_CHECK_CUDA(cudaGetLastError());                                             \
+  } while (0)
+
+// ---- element types ----------------------------------------------------------------------
+// Acc<T> is the type the recurrences are carried in: float for 16/32-bit storage, double for
+// double.  (The reference accumulates in the storage type, t2fw/csrc/lfw_kernel.cu:49.)
+template <typename T> struct Elem;
+template <> struct Elem<__half> {
+  using acc = float;
+  static __device__ __forceinline__ float ld(const __half *p) { return __half2float(*p); }
+  static __device__ __forceinline__ void st(__half *p, float v) { *p = __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {
+  using acc = float;
+  static __device__ __forceinline__ float ld(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void st(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+};
+template <> struct Elem<float> {
+  using acc = float;
+  static __device__ __forceinline__ float ld(const float *p) { return *p; }
+  static __device__ __forceinline__ void st(float *p, float v) { *p = v; }
+};
+template <> struct Elem<double> {
+  using acc = double;
+  static __device__ __forceinline__ double ld(const double *p) { return *p; }
+  static __device__ __forceinline__ void st(double *p, double v) { *p = v; }
+};
+
+template <typename A>
+__device__ __forceinline__ A warp_sum(A v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static inline size_t dtype_size(int dtype) {
+  switch (dtype) {
+    case T2FW_F16: case T2FW_BF16: return 2;
+    case T2FW_F32: return 4;
+    case T2FW_F64: return 8;
+    default: return 0;
+  }
+}
+
+// Launchers implemented in the kernel translation units.  All return a T2FW_* status.
+int lfw_scan_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,
+                     const void *state, void *out, void *ckpt, int64_t B, int64_t T, int64_t D,
+                     int64_t K, int dtype, int64_t C, cudaStream_t st);
+int lfw_scan_backward(const void *go, const void *gs, const void *x, const void *f, const void *q,
+                      const void *k, const void *fk, const void *state, const void *ckpt,
+                      void *dx, void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B,
+                      int64_t T, int64_t D, int64_t K, int dtype, int64_t C, cudaStream_t st);
+bool lfw_decode_supported(int64_t D, int64_t K, int dtype);
+int lfw_decode_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,
+                       const void *state, void *out, void *new_state, int64_t B, int64_t D,
+                       int64_t K, int dtype, cudaStream_t st);
+int dfw_scan_forward(const void *q, const void *k, const void *v, const void *state, void *out,
+                     void *fin, void *delta, int64_t B, int64_t T, int64_t D, int64_t M, int dtype,
+                     cudaStream_t st);
+int dfw_scan_backward(const void *go, const void *gs, const void *q, const void *k,
+                      const void *delta, const void *fin, void *dq, void *dk, void *dv, void *ds,
+                      void *dv_acc, int64_t B, int64_t T, int64_t D, int64_t M, int dtype,
+                      cudaStream_t st);
+
+}  // namespace t2fw

@@ -1,0 +1,210 @@
+// PyTorch operator library: torch.ops.lfw.{forward,backward} and torch.ops.dfw.{forward,backward}
+// with the schemas of the reference's op libraries (t2fw/csrc/lfw.cpp:98-101,
+// t2fw/csrc/dfw.cpp:66-69).  This file is only an adapter: it validates tensors, allocates the
+// outputs (and scratch) with the caching allocator, picks the caller's device and current
+// stream, and forwards raw pointers to the C ABI in include/t2fw_b200.h.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include <cstdlib>
+#include <vector>
+
+#include "t2fw_b200.h"
+
+namespace {
+
+#define T2FW_CHECK_INPUT(x)                                             \
+  TORCH_CHECK((x).device().is_cuda(), #x " must be a CUDA tensor");     \
+  TORCH_CHECK((x).is_contiguous(), #x " must be contiguous")
+
+int dtype_code(const at::Tensor &t) {
+  switch (t.scalar_type()) {
+    case at::kHalf: return T2FW_F16;
+    case at::kBFloat16: return T2FW_BF16;
+    case at::kFloat: return T2FW_F32;
+    case at::kDouble: return T2FW_F64;
+    default: TORCH_CHECK(false, "t2fw: unsupported dtype ", t.scalar_type());
+  }
+  return -1;
+}
+
+void check_status(int rc, const char *what) {
+  TORCH_CHECK(rc == T2FW_OK, what, " failed (status ", rc, "): ", t2fw_last_error());
+}
+
+void check_same(const at::Tensor &a, const at::Tensor &ref, const char *name) {
+  TORCH_CHECK(a.scalar_type() == ref.scalar_type(), name, ": dtype differs from value's");
+  TORCH_CHECK(a.device() == ref.device(), name, ": device differs from value's");
+}
+
+int64_t ckpt_interval(int64_t T, int64_t D, int64_t K, int dtype) {
+  if (const char *e = std::getenv("T2FW_CKPT_EVERY")) {
+    const long v = std::atol(e);
+    if (v > 0) return v;
+  }
+  return t2fw_lfw_default_ckpt_every(T, D, K, dtype);
+}
+
+at::Tensor make_scratch(size_t bytes, const at::Tensor &like) {
+  if (bytes == 0) return at::Tensor();
+  return at::empty({(int64_t)bytes}, like.options().dtype(at::kByte));
+}
+
+void *ptr_or_null(const at::Tensor &t) { return t.defined() ? t.data_ptr() : nullptr; }
+
+// ---- decay rule ---------------------------------------------------------------------------
+std::vector<at::Tensor> lfw_forward(at::Tensor x, at::Tensor f, at::Tensor query, at::Tensor key,
+                                    at::Tensor f_key, at::Tensor state) {
+  T2FW_CHECK_INPUT(x);
+  T2FW_CHECK_INPUT(f);
+  T2FW_CHECK_INPUT(query);
+  T2FW_CHECK_INPUT(key);
+  T2FW_CHECK_INPUT(f_key);
+  T2FW_CHECK_INPUT(state);
+  TORCH_CHECK(x.dim() == 3 && query.dim() == 3 && state.dim() == 3, "expected x [B,T,D], query [B,T,K], state [B,D,K]");
+  const int64_t B = x.size(0), T = x.size(1), D = x.size(2), K = query.size(2);
+  TORCH_CHECK(f.sizes() == x.sizes(), "f must have x's shape");
+  TORCH_CHECK(query.size(0) == B && query.size(1) == T, "query must be [B,T,K]");
+  TORCH_CHECK(key.sizes() == query.sizes() && f_key.sizes() == query.sizes(), "key and f_key must have query's shape");
+  TORCH_CHECK(state.size(0) == B && state.size(1) == D && state.size(2) == K, "state must be [B,D,K]");
+  check_same(f, x, "f"); check_same(query, x, "query"); check_same(key, x, "key");
+  check_same(f_key, x, "f_key"); check_same(state, x, "state");
+  TORCH_CHECK(B > 0 && T > 0 && D > 0 && K > 0, "empty tensors are not supported");
+
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int dt = dtype_code(x);
+  const int64_t C = ckpt_interval(T, D, K, dt);
+  const int64_t slots = t2fw_lfw_ckpt_slots(T, C);
+  at::Tensor outputs = at::empty({B, T, D}, x.options());
+  at::Tensor ckpt = at::empty({B, slots, D, K}, x.options());
+  const size_t sb = t2fw_lfw_forward_scratch_bytes(B, T, D, K, dt, C);
+  at::Tensor scratch = make_scratch(sb, x);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check_status(t2fw_lfw_forward(x.data_ptr(), f.data_ptr(), query.data_ptr(), key.data_ptr(),
+                                f_key.data_ptr(), state.data_ptr(), outputs.data_ptr(),
+                                ckpt.data_ptr(), B, T, D, K, dt, C, ptr_or_null(scratch), sb,
+                                stream.stream()),
+               "lfw.forward");
+  return {outputs, ckpt};
+}
+
+std::vector<at::Tensor> lfw_backward(at::Tensor grad_output, at::Tensor grad_state,
+                                     at::Tensor value, at::Tensor forget, at::Tensor query,
+                                     at::Tensor key, at::Tensor f_key, at::Tensor outputs,
+                                     at::Tensor state, at::Tensor ckpt_states) {
+  T2FW_CHECK_INPUT(grad_output);
+  T2FW_CHECK_INPUT(grad_state);
+  T2FW_CHECK_INPUT(value);
+  T2FW_CHECK_INPUT(forget);
+  T2FW_CHECK_INPUT(query);
+  T2FW_CHECK_INPUT(key);
+  T2FW_CHECK_INPUT(f_key);
+  T2FW_CHECK_INPUT(outputs);
+  T2FW_CHECK_INPUT(state);
+  T2FW_CHECK_INPUT(ckpt_states);
+  TORCH_CHECK(value.dim() == 3 && query.dim() == 3 && state.dim() == 3 && ckpt_states.dim() == 4, "bad ranks");
+  const int64_t B = value.size(0), T = value.size(1), D = value.size(2), K = query.size(2);
+  TORCH_CHECK(grad_output.sizes() == value.sizes(), "grad_output must be [B,T,D]");
+  TORCH_CHECK(grad_state.sizes() == state.sizes(), "grad_state must be [B,D,K]");
+  check_same(grad_output, value, "grad_output"); check_same(grad_state, value, "grad_state");
+  check_same(ckpt_states, value, "ckpt_states");
+
+  const c10::cuda::CUDAGuard guard(value.device());
+  const int dt = dtype_code(value);
+  const int64_t C = ckpt_interval(T, D, K, dt);
+  TORCH_CHECK(ckpt_states.size(0) == B && ckpt_states.size(1) == t2fw_lfw_ckpt_slots(T, C) &&
+                  ckpt_states.size(2) == D && ckpt_states.size(3) == K,
+              "ckpt_states does not match the checkpoint interval in use");
+  at::Tensor d_x = at::empty_like(value), d_f = at::empty_like(forget);
+  at::Tensor d_q = at::empty_like(query), d_k = at::empty_like(key), d_fk = at::empty_like(f_key);
+  at::Tensor d_s = at::empty_like(state);
+  const size_t sb = t2fw_lfw_backward_scratch_bytes(B, T, D, K, dt, C);
+  at::Tensor scratch = make_scratch(sb, value);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check_status(t2fw_lfw_backward(grad_output.data_ptr(), grad_state.data_ptr(), value.data_ptr(),
+                                 forget.data_ptr(), query.data_ptr(), key.data_ptr(),
+                                 f_key.data_ptr(), state.data_ptr(), ckpt_states.data_ptr(),
+                                 d_x.data_ptr(), d_f.data_ptr(), d_q.data_ptr(), d_k.data_ptr(),
+                                 d_fk.data_ptr(), d_s.data_ptr(), B, T, D, K, dt, C,
+                                 ptr_or_null(scratch), sb, stream.stream()),
+               "lfw.backward");
+  return {d_x, d_f, d_q, d_k, d_fk, d_s};
+}
+
+// ---- delta rule ---------------------------------------------------------------------------
+at::ScalarType acc_type(const at::Tensor &t) {
+  return t.scalar_type() == at::kDouble ? at::kDouble : at::kFloat;
+}
+
+std::vector<at::Tensor> dfw_forward(at::Tensor query, at::Tensor key, at::Tensor value,
+                                    at::Tensor state) {
+  T2FW_CHECK_INPUT(query);
+  T2FW_CHECK_INPUT(key);
+  T2FW_CHECK_INPUT(value);
+  T2FW_CHECK_INPUT(state);
+  TORCH_CHECK(value.dim() == 3 && query.dim() == 3 && state.dim() == 3, "expected value [B,T,D], query [B,T,M], state [B,D,M]");
+  const int64_t B = value.size(0), T = value.size(1), D = value.size(2), M = query.size(2);
+  TORCH_CHECK(query.size(0) == B && query.size(1) == T && key.sizes() == query.sizes(), "query/key must be [B,T,M]");
+  TORCH_CHECK(state.size(0) == B && state.size(1) == D && state.size(2) == M, "state must be [B,D,M]");
+  check_same(query, value, "query"); check_same(key, value, "key"); check_same(state, value, "state");
+  TORCH_CHECK(B > 0 && T > 0 && D > 0 && M > 0, "empty tensors are not supported");
+
+  const c10::cuda::CUDAGuard guard(value.device());
+  const int dt = dtype_code(value);
+  at::Tensor outputs = at::empty_like(value);
+  at::Tensor final_state = at::empty_like(state);
+  at::Tensor delta = at::empty({B, T, D}, value.options().dtype(acc_type(value)));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check_status(t2fw_dfw_forward(query.data_ptr(), key.data_ptr(), value.data_ptr(),
+                                state.data_ptr(), outputs.data_ptr(), final_state.data_ptr(),
+                                delta.data_ptr(), B, T, D, M, dt, stream.stream()),
+               "dfw.forward");
+  return {outputs, final_state, delta};
+}
+
+std::vector<at::Tensor> dfw_backward(at::Tensor grad_output, at::Tensor grad_state,
+                                     at::Tensor query, at::Tensor key, at::Tensor delta_value,
+                                     at::Tensor final_state) {
+  T2FW_CHECK_INPUT(grad_output);
+  T2FW_CHECK_INPUT(grad_state);
+  T2FW_CHECK_INPUT(query);
+  T2FW_CHECK_INPUT(key);
+  T2FW_CHECK_INPUT(delta_value);
+  T2FW_CHECK_INPUT(final_state);
+  TORCH_CHECK(grad_output.dim() == 3 && query.dim() == 3 && final_state.dim() == 3, "bad ranks");
+  const int64_t B = grad_output.size(0), T = grad_output.size(1), D = grad_output.size(2),
+                M = query.size(2);
+  TORCH_CHECK(delta_value.sizes() == grad_output.sizes(), "delta_value must be [B,T,D]");
+  TORCH_CHECK(grad_state.sizes() == final_state.sizes(), "grad_state must be [B,D,M]");
+  TORCH_CHECK(delta_value.scalar_type() == acc_type(query), "delta_value must be the tensor dfw.forward returned");
+  check_same(grad_output, query, "grad_output"); check_same(grad_state, query, "grad_state");
+  check_same(final_state, query, "final_state");
+
+  const c10::cuda::CUDAGuard guard(query.device());
+  const int dt = dtype_code(query);
+  at::Tensor d_q = at::empty_like(query), d_k = at::empty_like(key);
+  at::Tensor d_v = at::empty_like(grad_output), d_s = at::empty_like(final_state);
+  const size_t sb = t2fw_dfw_backward_scratch_bytes(B, T, D, M, dt);
+  at::Tensor scratch = make_scratch(sb, query);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check_status(t2fw_dfw_backward(grad_output.data_ptr(), grad_state.data_ptr(), query.data_ptr(),
+                                 key.data_ptr(), delta_value.data_ptr(), final_state.data_ptr(),
+                                 d_q.data_ptr(), d_k.data_ptr(), d_v.data_ptr(), d_s.data_ptr(), B,
+                                 T, D, M, dt, ptr_or_null(scratch), sb, stream.stream()),
+               "dfw.backward");
+  return {d_q, d_k, d_v, d_s};
+}
+
+}  // namespace
+
+TORCH_LIBRARY(lfw, m) {
+  m.def("forward", lfw_forward);
+  m.def("backward", lfw_backward);
+}
+
+TORCH_LIBRARY(dfw, m) {
+  m.def("forward", dfw_forward);
+  m.def("backward", dfw_backward);
+}

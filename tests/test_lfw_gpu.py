@@ -1,0 +1,189 @@
+"""Parity of the CUDA decay-rule path with the oracle, through the C ABI and through the
+autograd wrapper.  Tolerances (max relative error, see helpers.max_rel_err): fp16 outputs and
+states 1e-2, fp16 gradients 2e-2; fp32 2e-4 / 5e-4; fp64 1e-9."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import (GRAD_TOL, OUT_TOL, golden_files, lfw_inputs, load_golden, max_rel_err, to_dev)
+from oracle import fw_oracle
+
+pytestmark = pytest.mark.gpu
+
+GRAD_NAMES = ("d_x", "d_f", "d_q", "d_k", "d_f_key", "d_state")
+
+
+def run_cabi(x, f, q, k, fk, s, go, gs, ckpt_every=None):
+    from t2fw_b200 import cabi
+
+    out = torch.full_like(x, float("nan"))
+    out, ckpt = cabi.lfw_forward(x, f, q, k, fk, s, ckpt_every=ckpt_every, out=out)
+    grads = cabi.lfw_backward(go, gs, x, f, q, k, fk, s, ckpt, ckpt_every=ckpt_every)
+    torch.cuda.synchronize()
+    return out, ckpt[:, -1], grads
+
+
+def check_against_oracle(dev_inputs, got, dtype, rows=None):
+    """dev_inputs are the (already rounded) device tensors; the oracle sees the same values."""
+    x, f, q, k, fk, s, go, gs = [t if rows is None else t[rows] for t in dev_inputs]
+    out, fin, grads = got
+    if rows is not None:
+        out, fin, grads = out[rows], fin[rows], [g[rows] for g in grads]
+    r_out, r_fin = fw_oracle.lfw_forward(x, f, q, k, fk, s)
+    r_grads = fw_oracle.lfw_backward(go, gs, x, f, q, k, fk, s)
+    assert max_rel_err(out, r_out) <= OUT_TOL[dtype], "outputs"
+    assert max_rel_err(fin, r_fin) <= OUT_TOL[dtype], "next_state"
+    for g, r, n in zip(grads, r_grads, GRAD_NAMES):
+        assert max_rel_err(g, r) <= GRAD_TOL[dtype], n
+
+
+@pytest.mark.parametrize("path", golden_files("lfw_"), ids=lambda p: p.split("/")[-1][:-4])
+def test_golden_fp32_direct(cuda, path):
+    """fp32 kernels against the reference's own fp32 results (no oracle in between)."""
+    g = load_golden(path)
+    names = ("x", "f", "q", "k", "f_key", "state", "grad_out", "grad_state")
+    dev = to_dev([g[n] for n in names], torch.float32, cuda)
+    out, fin, grads = run_cabi(*dev)
+    assert max_rel_err(out, g["out"]) <= OUT_TOL[torch.float32]
+    assert max_rel_err(fin, g["final_state"]) <= OUT_TOL[torch.float32]
+    for got, n in zip(grads, GRAD_NAMES):
+        assert max_rel_err(got, g[n]) <= GRAD_TOL[torch.float32], n
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float64])
+@pytest.mark.parametrize("path", golden_files("lfw_"), ids=lambda p: p.split("/")[-1][:-4])
+def test_golden_inputs_other_dtypes(cuda, path, dtype):
+    g = load_golden(path)
+    names = ("x", "f", "q", "k", "f_key", "state", "grad_out", "grad_state")
+    dev = to_dev([g[n] for n in names], dtype, cuda)
+    check_against_oracle(dev, run_cabi(*dev), dtype)
+
+
+def reference_grid():
+    # the reference's shape grid (tests/test_lfw.py:19-24): kdim = ceil(dim / 2)
+    for bsz in range(1, 16, 4):
+        for dim in range(1, 64, 32):
+            for seqlen in range(1, 512, 128):
+                yield bsz, seqlen, dim
+    yield 2, 1024, 32
+
+
+@pytest.mark.parametrize("bsz,seqlen,dim", list(reference_grid()))
+def test_reference_shape_grid_fp16(cuda, bsz, seqlen, dim):
+    kdim = math.ceil(dim / 2)
+    # gates as in tests/test_lfw.py:38,41; state ~ N(0,1) as in tests/test_lfw.py:42
+    cpu = lfw_inputs(bsz, seqlen, dim, kdim, "bias", 1.0, 100 + bsz + seqlen + dim)
+    dev = to_dev(cpu, torch.float16, cuda)
+    check_against_oracle(dev, run_cabi(*dev), torch.float16)
+
+
+@pytest.mark.parametrize("ckpt_every", [1, 7, 16, 64, 100, 4096])
+def test_checkpoint_interval_does_not_change_results(cuda, ckpt_every):
+    cpu = lfw_inputs(3, 150, 24, 40, "sigmoid", 0.5, 21)
+    dev = to_dev(cpu, torch.float32, cuda)
+    check_against_oracle(dev, run_cabi(*dev, ckpt_every=ckpt_every), torch.float32)
+
+
+@pytest.mark.parametrize("gates", ["raw_f1", "raw", "sigmoid"])
+def test_config2_full_size_fp16(cuda, gates):
+    """B*H=96, T=1024, D=K=64 at full size; three batch rows are checked against the oracle and
+    the whole result must be finite."""
+    cpu = lfw_inputs(96, 1024, 64, 64, gates, 0.0, 2)
+    dev = to_dev(cpu, torch.float16, cuda)
+    got = run_cabi(*dev)
+    assert all(torch.isfinite(t).all() for t in (got[0], got[1], *got[2]))
+    check_against_oracle(dev, got, torch.float16, rows=[0, 47, 95])
+
+
+def test_config2_split_sequence_matches_single_call(cuda):
+    """Feeding next_state back in (two calls of T/2) reproduces the single call."""
+    from t2fw_b200 import cabi
+
+    x, f, q, k, fk, s, _, _ = to_dev(lfw_inputs(96, 1024, 64, 64, "sigmoid", 0.1, 3), torch.float16, cuda)
+    out, ckpt = cabi.lfw_forward(x, f, q, k, fk, s)
+    h = 512
+    o1, c1 = cabi.lfw_forward(*[t[:, :h].contiguous() for t in (x, f, q, k, fk)], s)
+    o2, c2 = cabi.lfw_forward(*[t[:, h:].contiguous() for t in (x, f, q, k, fk)], c1[:, -1].contiguous())
+    assert max_rel_err(torch.cat([o1, o2], 1), out) <= OUT_TOL[torch.float16]
+    assert max_rel_err(c2[:, -1], ckpt[:, -1]) <= OUT_TOL[torch.float16]
+
+
+def test_config3_decode_steps_fp16(cuda):
+    """B*H=4096, T=1, D=K=64: five chained steps, every element checked."""
+    from t2fw_b200 import cabi
+
+    torch.manual_seed(5)
+    B, D, K = 4096, 64, 64
+    s = (torch.randn(B, D, K) * 0.1).half().to(cuda)
+    s_ref = s.double().cpu().numpy()
+    for step in range(5):
+        x, q, k, fk = (torch.randn(B, 1, n).half().to(cuda) for n in (D, K, K, K))
+        f = torch.sigmoid(torch.randn(B, 1, D)).half().to(cuda)
+        out, ckpt = cabi.lfw_forward(x, f, q, k, fk, s)
+        r_out, r_fin = fw_oracle.lfw_forward(x, f, q, k, fk, s_ref)
+        assert max_rel_err(out, r_out) <= OUT_TOL[torch.float16]
+        assert max_rel_err(ckpt[:, -1], r_fin) <= OUT_TOL[torch.float16]
+        s = ckpt[:, -1].contiguous()
+        s_ref = s.double().cpu().numpy()  # the API round-trips the state through fp16
+
+
+def test_config4_long_sequence_fp16(cuda):
+    """B*H=16, T=16384, D=K=128 (more than 2^31 state-steps); one head against the oracle."""
+    cpu = lfw_inputs(16, 16384, 128, 128, "sigmoid", 0.1, 4)
+    dev = to_dev(cpu, torch.float16, cuda)
+    got = run_cabi(*dev)
+    assert all(torch.isfinite(t).all() for t in (got[0], got[1], *got[2]))
+    check_against_oracle(dev, got, torch.float16, rows=[5])
+
+
+def test_autograd_wrapper_matches_oracle_and_is_deterministic(cuda):
+    from t2fw_b200.functional_lfw import LFWFunction
+
+    cpu = lfw_inputs(4, 200, 64, 64, "sigmoid", 0.3, 6)
+    x, f, q, k, fk, s, go, gs = to_dev(cpu, torch.float16, cuda)
+    leaves = [t.clone().requires_grad_(True) for t in (x, f, q, k, fk, s)]
+    out, nxt = LFWFunction.apply(*leaves)
+    assert out.shape == x.shape and nxt.shape == s.shape and nxt.dtype == s.dtype
+    # non-contiguous upstream gradient, as autograd may hand over
+    go_nc = go.transpose(0, 1).contiguous().transpose(0, 1)
+    assert not go_nc.is_contiguous()
+    grads = torch.autograd.grad([out, nxt], leaves, [go_nc, gs])
+    check_against_oracle((x, f, q, k, fk, s, go, gs), (out, nxt, grads), torch.float16)
+    # inputs untouched, second run bitwise identical
+    for a, b in zip(leaves, (x, f, q, k, fk, s)):
+        assert torch.equal(a.detach(), b)
+    out2, nxt2 = LFWFunction.apply(*leaves)
+    grads2 = torch.autograd.grad([out2, nxt2], leaves, [go_nc, gs])
+    assert torch.equal(out, out2) and torch.equal(nxt, nxt2)
+    for a, b in zip(grads, grads2):
+        assert torch.equal(a, b)
+
+
+def test_next_state_feeds_the_next_call(cuda):
+    """The returned state has the input dtype and can be passed straight back in."""
+    from t2fw_b200.functional_lfw import LFWFunction
+
+    x, f, q, k, fk, s, _, _ = to_dev(lfw_inputs(2, 40, 16, 8, "sigmoid", 0.2, 8), torch.float16, cuda)
+    _, s1 = LFWFunction.apply(x, f, q, k, fk, s)
+    o2, _ = LFWFunction.apply(x, f, q, k, fk, s1)
+    r1, f1 = fw_oracle.lfw_forward(x, f, q, k, fk, s)
+    r2, _ = fw_oracle.lfw_forward(x, f, q, k, fk, s1)
+    assert max_rel_err(s1, f1) <= OUT_TOL[torch.float16]
+    assert max_rel_err(o2, r2) <= OUT_TOL[torch.float16]
+
+
+def test_second_device_stream_is_respected(cuda):
+    """The op runs on the caller's current stream."""
+    from t2fw_b200.functional_lfw import LFWFunction
+
+    x, f, q, k, fk, s, _, _ = to_dev(lfw_inputs(2, 64, 32, 32, "sigmoid", 0.2, 9), torch.float16, cuda)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        o, _ = LFWFunction.apply(x, f, q, k, fk, s)
+    side.synchronize()
+    r, _ = fw_oracle.lfw_forward(x, f, q, k, fk, s)
+    assert max_rel_err(o, r) <= OUT_TOL[torch.float16]
