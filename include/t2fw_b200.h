@@ -119,6 +119,37 @@ int t2fw_dfw_backward(const void *grad_output, const void *grad_state,
                       int64_t B, int64_t T, int64_t D, int64_t M, int dtype,
                       void *scratch, size_t scratch_bytes, void *stream);
 
+/*
+ * Delta rule backward without caller-provided scratch.  No counterpart in the reference
+ * (its backward allocates freely through ATen).
+ *
+ * Same inputs, outputs and results as t2fw_dfw_backward, for hosts that cannot give the call
+ * any device memory beyond the operator's own tensors and cannot call cudaMalloc themselves:
+ * a runtime that reserved the entire GPU for its own pool when it started, a latency-critical
+ * loop that must avoid the device-wide synchronisation an allocation implies, or a foreign
+ * function bridge that only marshals an operator's inputs and outputs.  The float copy of
+ * d_value that 16-bit problems need is kept in a 16 MiB array that is part of the library
+ * image, so each GPU that uses the library carries it until the process ends.
+ *
+ * Limits and rules:
+ *  - 16-bit dtypes: B*T*D <= t2fw_dfw_backward_noalloc_max_elems() (4 Mi elements), otherwise
+ *    T2FW_ERR_SCRATCH with an explanatory message; 32- and 64-bit dtypes use no scratch and
+ *    have no limit.
+ *  - The first call on a device looks up the array's device address (with that device
+ *    current); make that first call outside any stream capture.
+ *  - The call allocates and frees nothing.  All calls on a device share the one array: it
+ *    keeps whatever the previous call left (nothing in it has to start at zero, the row pass
+ *    rewrites every element it later reads), and two calls that overlap on the GPU - from
+ *    different streams or processes' threads - race on it.  Serialise them.
+ */
+size_t t2fw_dfw_backward_noalloc_max_elems(void);
+int t2fw_dfw_backward_noalloc(const void *grad_output, const void *grad_state,
+                              const void *q, const void *k, const void *delta,
+                              const void *final_state,
+                              void *d_q, void *d_k, void *d_v, void *d_state,
+                              int64_t B, int64_t T, int64_t D, int64_t M, int dtype,
+                              void *stream);
+
 #ifdef __cplusplus
 }
 #endif

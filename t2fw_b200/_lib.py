@@ -20,6 +20,7 @@ EXPORTS = (
     "t2fw_lfw_forward_scratch_bytes", "t2fw_lfw_backward_scratch_bytes",
     "t2fw_dfw_backward_scratch_bytes",
     "t2fw_lfw_forward", "t2fw_lfw_backward", "t2fw_dfw_forward", "t2fw_dfw_backward",
+    "t2fw_dfw_backward_noalloc_max_elems", "t2fw_dfw_backward_noalloc",
 )
 
 _core = None
@@ -61,6 +62,10 @@ def load_core():
     lib.t2fw_dfw_forward.argtypes = [_vp] * 7 + [_i64] * 4 + [_int, _vp]
     lib.t2fw_dfw_backward.restype = _int
     lib.t2fw_dfw_backward.argtypes = [_vp] * 10 + [_i64] * 4 + [_int, _vp, _sz, _vp]
+    lib.t2fw_dfw_backward_noalloc_max_elems.restype = _sz
+    lib.t2fw_dfw_backward_noalloc_max_elems.argtypes = []
+    lib.t2fw_dfw_backward_noalloc.restype = _int
+    lib.t2fw_dfw_backward_noalloc.argtypes = [_vp] * 10 + [_i64] * 4 + [_int, _vp]
     _core = lib
     return lib
 
