@@ -1,6 +1,7 @@
 // C ABI of the library (declared in include/t2fw_b200.h): argument checks and dispatch to the
 // kernel launchers.  Nothing here allocates, frees or synchronises.
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -44,11 +45,22 @@ int64_t t2fw_lfw_ckpt_slots(int64_t T, int64_t ckpt_every) {
   return ceil_div64(T, ckpt_every);
 }
 
-size_t t2fw_lfw_forward_scratch_bytes(int64_t, int64_t, int64_t, int64_t, int, int64_t) {
+static bool chunk_path_enabled() {
+  const char *e = std::getenv("T2FW_DISABLE_CHUNK");
+  return !(e && e[0] == '1');
+}
+
+size_t t2fw_lfw_forward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K, int dtype,
+                                      int64_t ckpt_every) {
+  if (T > 1 && chunk_path_enabled() && lfw_chunk_supported(D, K, dtype, ckpt_every))
+    return lfw_chunk_forward_scratch_bytes(B, T);
   return 0;
 }
 
-size_t t2fw_lfw_backward_scratch_bytes(int64_t, int64_t, int64_t, int64_t, int, int64_t) {
+size_t t2fw_lfw_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K, int dtype,
+                                       int64_t ckpt_every) {
+  if (chunk_path_enabled() && lfw_chunk_supported(D, K, dtype, ckpt_every))
+    return lfw_chunk_backward_scratch_bytes(B, T);
   return 0;
 }
 
@@ -70,8 +82,6 @@ int t2fw_lfw_forward(const void *x, const void *f, const void *q, const void *k,
                      const void *f_key, const void *state, void *outputs, void *ckpt_states,
                      int64_t B, int64_t T, int64_t D, int64_t K, int dtype, int64_t ckpt_every,
                      void *scratch, size_t scratch_bytes, void *stream) {
-  (void)scratch;
-  (void)scratch_bytes;
   int rc = check_common(B, T, D, K, dtype);
   if (rc != T2FW_OK) return rc;
   T2FW_CHECK_ARG(x && f && q && k && f_key && state && outputs && ckpt_states, "null pointer argument");
@@ -80,6 +90,21 @@ int t2fw_lfw_forward(const void *x, const void *f, const void *q, const void *k,
   if (T == 1 && lfw_decode_supported(D, K, dtype)) {
     rc = lfw_decode_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, D, K, dtype, st);
     if (rc != T2FW_ERR_UNSUPPORTED) return rc;
+  }
+  const size_t need = t2fw_lfw_forward_scratch_bytes(B, T, D, K, dtype, ckpt_every);
+  if (need != 0) {
+    if (scratch == nullptr || scratch_bytes < need) {
+      set_error("lfw forward needs %zu bytes of scratch, got %zu", need, scratch_bytes);
+      return T2FW_ERR_SCRATCH;
+    }
+    const int *rowflag = nullptr;
+    rc = lfw_chunk_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, T, dtype, scratch,
+                           st, &rowflag);
+    if (rc != T2FW_OK) return rc;
+    // batch rows whose gate products left the range the factored form can hold are redone by
+    // the scan kernel (it exits at once for all other rows)
+    return lfw_scan_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, T, D, K, dtype,
+                            ckpt_every, st, rowflag);
   }
   return lfw_scan_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, T, D, K, dtype,
                           ckpt_every, st);
@@ -91,14 +116,27 @@ int t2fw_lfw_backward(const void *grad_output, const void *grad_state, const voi
                       void *d_k, void *d_f_key, void *d_state, int64_t B, int64_t T, int64_t D,
                       int64_t K, int dtype, int64_t ckpt_every, void *scratch,
                       size_t scratch_bytes, void *stream) {
-  (void)scratch;
-  (void)scratch_bytes;
   int rc = check_common(B, T, D, K, dtype);
   if (rc != T2FW_OK) return rc;
   T2FW_CHECK_ARG(grad_output && grad_state && x && f && q && k && f_key && state && ckpt_states &&
                      d_x && d_f && d_q && d_k && d_f_key && d_state,
                  "null pointer argument");
   T2FW_CHECK_ARG(ckpt_every > 0, "ckpt_every must be positive");
+  const size_t need = t2fw_lfw_backward_scratch_bytes(B, T, D, K, dtype, ckpt_every);
+  if (need != 0) {
+    if (scratch == nullptr || scratch_bytes < need) {
+      set_error("lfw backward needs %zu bytes of scratch, got %zu", need, scratch_bytes);
+      return T2FW_ERR_SCRATCH;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int *rowflag = nullptr;
+    rc = lfw_chunk_backward(grad_output, grad_state, x, f, q, k, f_key, state, ckpt_states, d_x,
+                            d_f, d_q, d_k, d_f_key, d_state, B, T, dtype, scratch, st, &rowflag);
+    if (rc != T2FW_OK) return rc;
+    return lfw_scan_backward(grad_output, grad_state, x, f, q, k, f_key, state, ckpt_states, d_x,
+                             d_f, d_q, d_k, d_f_key, d_state, B, T, D, K, dtype, ckpt_every, st,
+                             rowflag);
+  }
   return lfw_scan_backward(grad_output, grad_state, x, f, q, k, f_key, state, ckpt_states, d_x,
                            d_f, d_q, d_k, d_f_key, d_state, B, T, D, K, dtype, ckpt_every,
                            static_cast<cudaStream_t>(stream));

@@ -87,11 +87,24 @@ static inline size_t dtype_size(int dtype) {
 // Launchers implemented in the kernel translation units.  All return a T2FW_* status.
 int lfw_scan_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,
                      const void *state, void *out, void *ckpt, int64_t B, int64_t T, int64_t D,
-                     int64_t K, int dtype, int64_t C, cudaStream_t st);
+                     int64_t K, int dtype, int64_t C, cudaStream_t st,
+                     const int *rowflag = nullptr);
 int lfw_scan_backward(const void *go, const void *gs, const void *x, const void *f, const void *q,
                       const void *k, const void *fk, const void *state, const void *ckpt,
                       void *dx, void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B,
-                      int64_t T, int64_t D, int64_t K, int dtype, int64_t C, cudaStream_t st);
+                      int64_t T, int64_t D, int64_t K, int dtype, int64_t C, cudaStream_t st,
+                      const int *rowflag = nullptr);
+// chunked tensor-core path (D = K = 64, 16-bit storage, checkpoint interval 64)
+bool lfw_chunk_supported(int64_t D, int64_t K, int dtype, int64_t ckpt_every);
+size_t lfw_chunk_forward_scratch_bytes(int64_t B, int64_t T);
+int lfw_chunk_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,
+                      const void *state, void *out, void *ckpt, int64_t B, int64_t T, int dtype,
+                      void *scratch, cudaStream_t st, const int **rowflag_out);
+size_t lfw_chunk_backward_scratch_bytes(int64_t B, int64_t T);
+int lfw_chunk_backward(const void *go, const void *gs, const void *x, const void *f, const void *q,
+                       const void *k, const void *fk, const void *state, const void *ckpt, void *dx,
+                       void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B, int64_t T,
+                       int dtype, void *scratch, cudaStream_t st, const int **rowflag_out);
 bool lfw_decode_supported(int64_t D, int64_t K, int dtype);
 int lfw_decode_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,
                        const void *state, void *out, void *new_state, int64_t B, int64_t D,

@@ -28,7 +28,8 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
 lfw_scan_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__restrict__ q,
                     const T *__restrict__ k, const T *__restrict__ fk,
                     const T *__restrict__ state, T *__restrict__ out, T *__restrict__ ckpt,
-                    int64_t B, int64_t T_, int64_t D, int64_t K, int64_t C, int64_t nslots) {
+                    int64_t B, int64_t T_, int64_t D, int64_t K, int64_t C, int64_t nslots,
+                    const int *__restrict__ rowflag) {
   using A = typename Elem<T>::acc;
   const int lane = threadIdx.x & 31;
   const int64_t groups = (D + OWN - 1) / OWN;
@@ -36,6 +37,7 @@ lfw_scan_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *_
   if (warp >= B * groups) return;
   const int64_t b = warp / groups;
   const int64_t r0 = (warp % groups) * OWN;
+  if (rowflag != nullptr && rowflag[b] == 0) return;  // only rows the caller marked
 
   A S[OWN][NL];
 #pragma unroll
@@ -101,6 +103,7 @@ struct LineArgs {
   int64_t so, sl;         // strides of the own / lane axis inside one [D,K] state
   int64_t C, nslots;      // checkpoint interval and slot count
   int seg;                // steps of state history kept in shared memory at once
+  const int *rowflag;     // if not null, only batch rows with a non-zero flag are processed
 };
 
 template <typename T, int NL, int OWN, bool WITH_SP>
@@ -117,6 +120,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) lfw_line_bwd_kernel(const L
   const int64_t b = warp / groups;
   const int64_t o0 = (warp % groups) * OWN;
   const int64_t DK = a.NO * a.NLn;
+  if (a.rowflag != nullptr && a.rowflag[b] == 0) return;
 
   auto state_off = [&](int o, int j) { return (o0 + o) * a.so + (int64_t)(lane + 32 * j) * a.sl; };
   auto valid = [&](int o, int j) { return (o0 + o) < a.NO && (lane + 32 * j) < a.NLn; };
@@ -231,13 +235,13 @@ int pick_nl(int64_t extent) {
 template <typename T, int NL>
 int launch_fwd(const void *x, const void *f, const void *q, const void *k, const void *fk,
                const void *state, void *out, void *ckpt, int64_t B, int64_t T_, int64_t D,
-               int64_t K, int64_t C, cudaStream_t st) {
+               int64_t K, int64_t C, cudaStream_t st, const int *rowflag) {
   constexpr int OWN = 4;
   const int64_t warps = B * ceil_div64(D, OWN);
   const int64_t grid = ceil_div64(warps, kWarpsPerCta);
   lfw_scan_fwd_kernel<T, NL, OWN><<<(unsigned)grid, kWarpsPerCta * 32, 0, st>>>(
       (const T *)x, (const T *)f, (const T *)q, (const T *)k, (const T *)fk, (const T *)state,
-      (T *)out, (T *)ckpt, B, T_, D, K, C, ceil_div64(T_, C));
+      (T *)out, (T *)ckpt, B, T_, D, K, C, ceil_div64(T_, C), rowflag);
   T2FW_CHECK_LAUNCH(1);
   return T2FW_OK;
 }
@@ -262,13 +266,13 @@ int launch_line(LineArgs<T> a, cudaStream_t st) {
 template <typename T>
 int fwd_typed(const void *x, const void *f, const void *q, const void *k, const void *fk,
               const void *state, void *out, void *ckpt, int64_t B, int64_t T_, int64_t D,
-              int64_t K, int64_t C, cudaStream_t st) {
+              int64_t K, int64_t C, cudaStream_t st, const int *rowflag) {
   switch (pick_nl(K)) {
-    case 1: return launch_fwd<T, 1>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st);
-    case 2: return launch_fwd<T, 2>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st);
-    case 4: return launch_fwd<T, 4>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st);
-    case 8: return launch_fwd<T, 8>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st);
-    case 16: return launch_fwd<T, 16>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st);
+    case 1: return launch_fwd<T, 1>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st, rowflag);
+    case 2: return launch_fwd<T, 2>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st, rowflag);
+    case 4: return launch_fwd<T, 4>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st, rowflag);
+    case 8: return launch_fwd<T, 8>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st, rowflag);
+    case 16: return launch_fwd<T, 16>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st, rowflag);
   }
   set_error("lfw forward: K=%lld exceeds the supported maximum of 512", (long long)K);
   return T2FW_ERR_UNSUPPORTED;
@@ -291,7 +295,7 @@ template <typename T>
 int bwd_typed(const void *go, const void *gs, const void *x, const void *f, const void *q,
               const void *k, const void *fk, const void *state, const void *ckpt, void *dx,
               void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B, int64_t T_, int64_t D,
-              int64_t K, int64_t C, cudaStream_t st) {
+              int64_t K, int64_t C, cudaStream_t st, const int *rowflag) {
   LineArgs<T> row{};
   row.xo = (const T *)x; row.go = (const T *)f; row.po = (const T *)go;
   row.xl = (const T *)k; row.gl = (const T *)fk; row.pl = (const T *)q;
@@ -299,7 +303,7 @@ int bwd_typed(const void *go, const void *gs, const void *x, const void *f, cons
   row.state0 = (const T *)state; row.ckpt = (const T *)ckpt; row.grad_state = (const T *)gs;
   row.d_state = (T *)ds;
   row.B = B; row.T_ = T_; row.NO = D; row.NLn = K; row.so = K; row.sl = 1;
-  row.C = C; row.nslots = ceil_div64(T_, C);
+  row.C = C; row.nslots = ceil_div64(T_, C); row.rowflag = rowflag;
   int rc = line_typed<T, false>(row, st);
   if (rc != T2FW_OK) return rc;
 
@@ -310,7 +314,7 @@ int bwd_typed(const void *go, const void *gs, const void *x, const void *f, cons
   col.state0 = (const T *)state; col.ckpt = (const T *)ckpt; col.grad_state = (const T *)gs;
   col.d_state = nullptr;
   col.B = B; col.T_ = T_; col.NO = K; col.NLn = D; col.so = 1; col.sl = K;
-  col.C = C; col.nslots = ceil_div64(T_, C);
+  col.C = C; col.nslots = ceil_div64(T_, C); col.rowflag = rowflag;
   return line_typed<T, true>(col, st);
 }
 
@@ -318,12 +322,12 @@ int bwd_typed(const void *go, const void *gs, const void *x, const void *f, cons
 
 int lfw_scan_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,
                      const void *state, void *out, void *ckpt, int64_t B, int64_t T_, int64_t D,
-                     int64_t K, int dtype, int64_t C, cudaStream_t st) {
+                     int64_t K, int dtype, int64_t C, cudaStream_t st, const int *rowflag) {
   switch (dtype) {
-    case T2FW_F16: return fwd_typed<__half>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st);
-    case T2FW_BF16: return fwd_typed<__nv_bfloat16>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st);
-    case T2FW_F32: return fwd_typed<float>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st);
-    case T2FW_F64: return fwd_typed<double>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st);
+    case T2FW_F16: return fwd_typed<__half>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st, rowflag);
+    case T2FW_BF16: return fwd_typed<__nv_bfloat16>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st, rowflag);
+    case T2FW_F32: return fwd_typed<float>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st, rowflag);
+    case T2FW_F64: return fwd_typed<double>(x, f, q, k, fk, state, out, ckpt, B, T_, D, K, C, st, rowflag);
   }
   set_error("unknown dtype %d", dtype);
   return T2FW_ERR_BAD_ARG;
@@ -332,7 +336,8 @@ int lfw_scan_forward(const void *x, const void *f, const void *q, const void *k,
 int lfw_scan_backward(const void *go, const void *gs, const void *x, const void *f, const void *q,
                       const void *k, const void *fk, const void *state, const void *ckpt,
                       void *dx, void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B,
-                      int64_t T_, int64_t D, int64_t K, int dtype, int64_t C, cudaStream_t st) {
+                      int64_t T_, int64_t D, int64_t K, int dtype, int64_t C, cudaStream_t st,
+                      const int *rowflag) {
   if (D > 512 || K > 512) {
     set_error("lfw backward: D=%lld, K=%lld exceed the supported maximum of 512", (long long)D,
               (long long)K);
@@ -340,13 +345,13 @@ int lfw_scan_backward(const void *go, const void *gs, const void *x, const void 
   }
   switch (dtype) {
     case T2FW_F16:
-      return bwd_typed<__half>(go, gs, x, f, q, k, fk, state, ckpt, dx, df, dq, dk, dfk, ds, B, T_, D, K, C, st);
+      return bwd_typed<__half>(go, gs, x, f, q, k, fk, state, ckpt, dx, df, dq, dk, dfk, ds, B, T_, D, K, C, st, rowflag);
     case T2FW_BF16:
-      return bwd_typed<__nv_bfloat16>(go, gs, x, f, q, k, fk, state, ckpt, dx, df, dq, dk, dfk, ds, B, T_, D, K, C, st);
+      return bwd_typed<__nv_bfloat16>(go, gs, x, f, q, k, fk, state, ckpt, dx, df, dq, dk, dfk, ds, B, T_, D, K, C, st, rowflag);
     case T2FW_F32:
-      return bwd_typed<float>(go, gs, x, f, q, k, fk, state, ckpt, dx, df, dq, dk, dfk, ds, B, T_, D, K, C, st);
+      return bwd_typed<float>(go, gs, x, f, q, k, fk, state, ckpt, dx, df, dq, dk, dfk, ds, B, T_, D, K, C, st, rowflag);
     case T2FW_F64:
-      return bwd_typed<double>(go, gs, x, f, q, k, fk, state, ckpt, dx, df, dq, dk, dfk, ds, B, T_, D, K, C, st);
+      return bwd_typed<double>(go, gs, x, f, q, k, fk, state, ckpt, dx, df, dq, dk, dfk, ds, B, T_, D, K, C, st, rowflag);
   }
   set_error("unknown dtype %d", dtype);
   return T2FW_ERR_BAD_ARG;

@@ -187,3 +187,31 @@ def test_second_device_stream_is_respected(cuda):
     side.synchronize()
     r, _ = fw_oracle.lfw_forward(x, f, q, k, fk, s)
     assert max_rel_err(o, r) <= OUT_TOL[torch.float16]
+
+
+@pytest.mark.parametrize("kind", ["tiny_constant", "exact_zeros", "large"])
+def test_extreme_gates_d64(cuda, kind):
+    """D=K=64 inputs whose gate products leave the range of the factored tensor-core form: the
+    affected batch rows must still come out right (they are redone by the scan kernels)."""
+    x, f, q, k, fk, s, go, gs = lfw_inputs(3, 200, 64, 64, "sigmoid", 0.5, 40)
+    if kind == "tiny_constant":
+        fk[1] = 1e-3          # (1e-3)^16 underflows fp32 in one sub-block
+        f[2] = 2e-3
+    elif kind == "exact_zeros":
+        fk[0, 17, 5] = 0.0
+        fk[0, 18, 5] = 0.0
+        fk[0, 19, 5] = 0.0
+        fk[0, 20, 5] = 0.0
+        f[1, 100, :] = 0.0    # a hard reset of the whole state
+    else:
+        fk[2, 64:80] = 100.0  # one-sided products overflow the safe range ...
+        f[2, 64:80] = 0.01    # ... while the state itself stays bounded
+    dev = to_dev((x, f, q, k, fk, s, go, gs), torch.float16, cuda)
+    check_against_oracle(dev, run_cabi(*dev), torch.float16)
+
+
+@pytest.mark.parametrize("T", [1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 130])
+def test_d64_sequence_lengths(cuda, T):
+    """Chunk (64) and sub-block (16) boundaries of the tensor-core path, including ragged tails."""
+    dev = to_dev(lfw_inputs(2, T, 64, 64, "sigmoid", 0.5, 50 + T), torch.float16, cuda)
+    check_against_oracle(dev, run_cabi(*dev), torch.float16)
