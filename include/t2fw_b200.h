@@ -54,6 +54,11 @@ int t2fw_version(void);
 /* Number of kernel launches this process has issued through the library so far. */
 int64_t t2fw_launch_count(void);
 
+/* 0 if no kernel of the library has ever given up a bounded wait on this device (the kernels
+ * never spin forever: a wait that does not complete sets a flag and the kernel returns), a
+ * positive value if one has, negative if the flag could not be read.  Synchronises the device. */
+int t2fw_device_status(void);
+
 /* Checkpoint interval the library recommends for a problem, and the slot count that follows
  * from an interval.  The reference stores the state of EVERY step
  * (t2fw/csrc/lfw_kernel.cu:140-144); here only every ckpt_every-th state is kept and the

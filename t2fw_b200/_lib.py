@@ -15,7 +15,7 @@ OPS_PATH = os.path.join(_HERE, "lib", "t2fw_torch_ops.so")
 
 # every entry point include/t2fw_b200.h declares
 EXPORTS = (
-    "t2fw_last_error", "t2fw_version", "t2fw_launch_count",
+    "t2fw_last_error", "t2fw_version", "t2fw_launch_count", "t2fw_device_status",
     "t2fw_lfw_default_ckpt_every", "t2fw_lfw_ckpt_slots",
     "t2fw_lfw_forward_scratch_bytes", "t2fw_lfw_backward_scratch_bytes",
     "t2fw_dfw_backward_scratch_bytes",
@@ -44,6 +44,8 @@ def load_core():
     lib.t2fw_last_error.argtypes = []
     lib.t2fw_version.restype = _int
     lib.t2fw_launch_count.restype = _i64
+    lib.t2fw_device_status.restype = _int
+    lib.t2fw_device_status.argtypes = []
     lib.t2fw_lfw_default_ckpt_every.restype = _i64
     lib.t2fw_lfw_default_ckpt_every.argtypes = [_i64, _i64, _i64, _int]
     lib.t2fw_lfw_ckpt_slots.restype = _i64

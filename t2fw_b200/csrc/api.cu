@@ -32,6 +32,8 @@ const char *t2fw_last_error(void) { return g_err; }
 
 int t2fw_version(void) { return 100; }
 
+int t2fw_device_status(void) { return lfw_decode_bulk_status(); }
+
 int64_t t2fw_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int64_t t2fw_lfw_default_ckpt_every(int64_t T, int64_t D, int64_t K, int dtype) {
@@ -43,6 +45,11 @@ int64_t t2fw_lfw_default_ckpt_every(int64_t T, int64_t D, int64_t K, int dtype) 
 int64_t t2fw_lfw_ckpt_slots(int64_t T, int64_t ckpt_every) {
   if (T <= 0 || ckpt_every <= 0) return 0;
   return ceil_div64(T, ckpt_every);
+}
+
+static bool decode_bulk_enabled() {
+  const char *e = std::getenv("T2FW_DISABLE_DECODE_BULK");
+  return !(e && e[0] == '1');
 }
 
 static bool chunk_path_enabled() {
@@ -87,9 +94,19 @@ int t2fw_lfw_forward(const void *x, const void *f, const void *q, const void *k,
   T2FW_CHECK_ARG(x && f && q && k && f_key && state && outputs && ckpt_states, "null pointer argument");
   T2FW_CHECK_ARG(ckpt_every > 0, "ckpt_every must be positive");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (T == 1 && lfw_decode_supported(D, K, dtype)) {
-    rc = lfw_decode_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, D, K, dtype, st);
-    if (rc != T2FW_ERR_UNSUPPORTED) return rc;
+  if (T == 1) {
+    const bool al = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(f) |
+                      reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                      reinterpret_cast<uintptr_t>(f_key) | reinterpret_cast<uintptr_t>(state) |
+                      reinterpret_cast<uintptr_t>(outputs) |
+                      reinterpret_cast<uintptr_t>(ckpt_states)) & 15u) == 0;
+    if (al && decode_bulk_enabled() && lfw_decode_bulk_supported(B, D, K, dtype))
+      return lfw_decode_bulk_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, D, K,
+                                     dtype, st);
+    if (lfw_decode_supported(D, K, dtype)) {
+      rc = lfw_decode_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, D, K, dtype, st);
+      if (rc != T2FW_ERR_UNSUPPORTED) return rc;
+    }
   }
   const size_t need = t2fw_lfw_forward_scratch_bytes(B, T, D, K, dtype, ckpt_every);
   if (need != 0) {

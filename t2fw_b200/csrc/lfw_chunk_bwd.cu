@@ -170,18 +170,30 @@ lfw_chunk_bwd_carry_kernel(const T *__restrict__ grad_state, float *__restrict__
   float2 s01 = Pair<T>::ld(sp), s23 = Pair<T>::ld(sp + 2);
   float R[4] = {s01.x, s01.y, s23.x, s23.y};
   int any = 0;
-  for (int64_t c = nc - 1; c >= 0; --c) {
-    const size_t bc = (size_t)b * nc + c;
-    float4 *gp = reinterpret_cast<float4 *>(G + (bc * kDim + d) * kDim + k0);
-    const float4 l = *gp;
-    const float a = Ac[bc * kDim + d];
-    const float4 gg = *reinterpret_cast<const float4 *>(Gc + bc * kDim + k0);
-    *gp = make_float4(R[0], R[1], R[2], R[3]);
-    R[0] = a * gg.x * R[0] + l.x;
-    R[1] = a * gg.y * R[1] + l.y;
-    R[2] = a * gg.z * R[2] + l.z;
-    R[3] = a * gg.w * R[3] + l.w;
-    if (d == 0 && k0 == 0) any |= flags[bc];
+  // batches of 4 chunks, last chunk first: loads of a batch precede its dependent FMA chain
+  for (int64_t c0 = nc - 1; c0 >= 0; c0 -= 4) {
+    float4 l[4], gg[4];
+    float a[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t c = (c0 - j >= 0) ? c0 - j : 0;
+      const size_t bc = (size_t)b * nc + c;
+      l[j] = *reinterpret_cast<const float4 *>(G + (bc * kDim + d) * kDim + k0);
+      a[j] = Ac[bc * kDim + d];
+      gg[j] = *reinterpret_cast<const float4 *>(Gc + bc * kDim + k0);
+      if (d == 0 && k0 == 0) any |= flags[bc];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (c0 - j >= 0) {
+        const size_t bc = (size_t)b * nc + c0 - j;
+        *reinterpret_cast<float4 *>(G + (bc * kDim + d) * kDim + k0) = make_float4(R[0], R[1], R[2], R[3]);
+        R[0] = a[j] * gg[j].x * R[0] + l[j].x;
+        R[1] = a[j] * gg[j].y * R[1] + l[j].y;
+        R[2] = a[j] * gg[j].z * R[2] + l[j].z;
+        R[3] = a[j] * gg[j].w * R[3] + l[j].w;
+      }
+    }
   }
   T *dp = d_state + ((size_t)b * kDim + d) * kDim + k0;
   Pair<T>::st(dp, R[0], R[1]);

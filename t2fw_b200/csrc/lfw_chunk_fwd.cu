@@ -124,21 +124,33 @@ lfw_chunk_carry_kernel(const T *__restrict__ state, float *__restrict__ L, const
   float2 s01 = Pair<T>::ld(sp), s23 = Pair<T>::ld(sp + 2);
   float S[4] = {s01.x, s01.y, s23.x, s23.y};
   int any = 0;
-  for (int64_t c = 0; c < nc; ++c) {
-    const size_t bc = (size_t)b * nc + c;
-    float4 *lp = reinterpret_cast<float4 *>(L + (bc * kDim + d) * kDim + k0);
-    const float4 l = *lp;
-    const float a = Ac[bc * kDim + d];
-    const float4 gg = *reinterpret_cast<const float4 *>(Gc + bc * kDim + k0);
-    *lp = make_float4(S[0], S[1], S[2], S[3]);
-    S[0] = a * gg.x * S[0] + l.x;
-    S[1] = a * gg.y * S[1] + l.y;
-    S[2] = a * gg.z * S[2] + l.z;
-    S[3] = a * gg.w * S[3] + l.w;
-    T *cp = ckpt + (bc * kDim + d) * kDim + k0;
-    Pair<T>::st(cp, S[0], S[1]);
-    Pair<T>::st(cp + 2, S[2], S[3]);
-    if (d == 0 && k0 == 0) any |= flags[bc];
+  // batches of 4 chunks: all loads of a batch are issued before its dependent FMA chain
+  for (int64_t c0 = 0; c0 < nc; c0 += 4) {
+    float4 l[4], gg[4];
+    float a[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t c = (c0 + j < nc) ? c0 + j : nc - 1;
+      const size_t bc = (size_t)b * nc + c;
+      l[j] = *reinterpret_cast<const float4 *>(L + (bc * kDim + d) * kDim + k0);
+      a[j] = Ac[bc * kDim + d];
+      gg[j] = *reinterpret_cast<const float4 *>(Gc + bc * kDim + k0);
+      if (d == 0 && k0 == 0) any |= flags[bc];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (c0 + j < nc) {
+        const size_t bc = (size_t)b * nc + c0 + j;
+        *reinterpret_cast<float4 *>(L + (bc * kDim + d) * kDim + k0) = make_float4(S[0], S[1], S[2], S[3]);
+        S[0] = a[j] * gg[j].x * S[0] + l[j].x;
+        S[1] = a[j] * gg[j].y * S[1] + l[j].y;
+        S[2] = a[j] * gg[j].z * S[2] + l[j].z;
+        S[3] = a[j] * gg[j].w * S[3] + l[j].w;
+        T *cp = ckpt + (bc * kDim + d) * kDim + k0;
+        Pair<T>::st(cp, S[0], S[1]);
+        Pair<T>::st(cp + 2, S[2], S[3]);
+      }
+    }
   }
   if (d == 0 && k0 == 0) rowflag[b] = any;
 }

@@ -215,3 +215,17 @@ def test_d64_sequence_lengths(cuda, T):
     """Chunk (64) and sub-block (16) boundaries of the tensor-core path, including ragged tails."""
     dev = to_dev(lfw_inputs(2, T, 64, 64, "sigmoid", 0.5, 50 + T), torch.float16, cuda)
     check_against_oracle(dev, run_cabi(*dev), torch.float16)
+
+
+@pytest.mark.parametrize("B,D,K", [(1, 64, 64), (300, 64, 64), (7, 8, 8), (5, 128, 128), (9, 24, 256), (3, 20, 64)])
+def test_decode_shapes(cuda, B, D, K):
+    """T=1 through both decode kernels (the bulk-copy pipelined one needs D % 8 == 0)."""
+    from t2fw_b200 import _lib, cabi
+
+    x, f, q, k, fk, s, _, _ = to_dev(lfw_inputs(B, 1, D, K, "sigmoid", 0.5, 60 + B), torch.float16, cuda)
+    out, ckpt = cabi.lfw_forward(x, f, q, k, fk, s)
+    torch.cuda.synchronize()
+    r_out, r_fin = fw_oracle.lfw_forward(x, f, q, k, fk, s)
+    assert max_rel_err(out, r_out) <= OUT_TOL[torch.float16]
+    assert max_rel_err(ckpt[:, -1], r_fin) <= OUT_TOL[torch.float16]
+    assert _lib.load_core().t2fw_device_status() == 0
