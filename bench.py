@@ -166,6 +166,8 @@ def cpu_reference_run(workload, gates, steps, warmup, seed):
 
     B, T, D, K = WORKLOADS[workload]
     rows = min(B, CPU_SAMPLE_ROWS[workload])
+    # launchers such as torchrun pin OMP_NUM_THREADS=1; the CPU baseline uses every host core
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     x, f, q, k, fk, s, go, gs = [t[:rows].contiguous() for t in
                                  make_inputs(torch, rows, T, D, K, gates, seed, workload)]
     times = []
@@ -245,6 +247,7 @@ def run_ours(args):
 
     from t2fw_b200 import _lib, cabi
     from t2fw_b200.functional_lfw import LFWFunction
+    from t2fw_b200.parallel import job_throughput, max_over_ranks
 
     lib = _lib.load_core()
     B, T, D, K = WORKLOADS[args.workload]
@@ -360,12 +363,8 @@ def run_ours(args):
             bwd_ms.append(r[1].elapsed_time(r[2]))
     if decode and graph is not None:
         fwd_ms[:] = [total_ms / args.steps]      # eager per-call events include host launch gaps
-    tmax = torch.tensor([total_ms], device=dev)
-    if world > 1:
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-    total_ms = float(tmax.item())
-    tokens = B * T * args.steps * world
-    value = tokens / (total_ms * 1e-3)
+    total_ms = max_over_ranks(total_ms, dev)
+    value = job_throughput(B * T * args.steps, world, total_ms)
 
     # ---- end to end through the public API with host buffers -------------------------------
     e2e = None
@@ -409,10 +408,7 @@ def run_ours(args):
         barrier()
         wall = time.perf_counter() - t0
         e2e_ms = max(e0.elapsed_time(e1), 0.0)
-        t2 = torch.tensor([e2e_ms], device=dev)
-        if world > 1:
-            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t2.item())
+        e2e_ms = max_over_ranks(e2e_ms, dev)
         e2e = {"value": B * T * e2e_steps * world / (e2e_ms * 1e-3), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                "ms_per_step": e2e_ms / e2e_steps, "api": "LFWFunction.apply + autograd, pinned host buffers",
