@@ -155,6 +155,19 @@ int t2fw_dfw_backward_noalloc(const void *grad_output, const void *grad_state,
                               int64_t B, int64_t T, int64_t D, int64_t M, int dtype,
                               void *stream);
 
+/*
+ * Diagnostic: exercises the tensor-core building blocks of the chunked kernels in isolation
+ * (tensor-memory allocation, shared-memory matrix descriptors in both operand orientations,
+ * tcgen05.mma, completion tracking, accumulator loads).  No counterpart in the reference.
+ * Computes D1 = A1 * B1^T and D2 = A2 * B2^T with A [64 x Kc], B [N x Kc], D [64 x N], all
+ * row-major fp32 device arrays (operands are used at TF32 precision).  a_mn / b_mn must be 0:
+ * TF32 operands are K-major only in the un-swizzled shared-memory form.  *status (device int)
+ * is set to 1 if a bounded wait expired.  N, Kc: multiples of 8 in [8, 64].
+ */
+int t2fw_selftest_umma(const float *A1, const float *B1, const float *A2, const float *B2,
+                       float *D1, float *D2, int N, int Kc, int a_mn, int b_mn, int *status,
+                       void *stream);
+
 #ifdef __cplusplus
 }
 #endif

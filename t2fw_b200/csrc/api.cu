@@ -22,6 +22,11 @@ void set_error(const char *fmt, ...) {
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+bool umma_enabled() {
+  const char *e = std::getenv("T2FW_DISABLE_UMMA");
+  return !(e && e[0] == '1');
+}
+
 }  // namespace t2fw
 
 using namespace t2fw;
@@ -32,7 +37,11 @@ const char *t2fw_last_error(void) { return g_err; }
 
 int t2fw_version(void) { return 100; }
 
-int t2fw_device_status(void) { return lfw_decode_bulk_status(); }
+int t2fw_device_status(void) {
+  const int a = lfw_decode_bulk_status(), b = lfw_chunk_umma_status();
+  if (a < 0 || b < 0) return -1;
+  return a | b;
+}
 
 int64_t t2fw_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

@@ -21,6 +21,8 @@
 // from identical TF32-rounded operands on both sides:
 //   H = suffix_t[ Qt.*(dOt S0 + Z Kt) - Kt.*(Z^T Qt) ] + exclusive_prefix_t[ Kt.*gI.*((Xt aI) R) ]
 //       + gI .* sum_d aI R S0 ;   d_f_key = H / g        (d side: same with the roles exchanged)
+#include <type_traits>
+
 #include "lfw_chunk.cuh"
 
 namespace t2fw {
@@ -156,7 +158,7 @@ lfw_chunk_bwd_local_kernel(const T *__restrict__ go, const T *__restrict__ f, co
 // R_end(c-1) = (Ac Gc^T) R_end(c) + G_c, from the last chunk (R_end = grad_state) down; G_c is
 // overwritten with R_end(c).  The value left after chunk 0 is d_state.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 lfw_chunk_bwd_carry_kernel(const T *__restrict__ grad_state, float *__restrict__ G,
                            const float *__restrict__ Ac, const float *__restrict__ Gc,
                            const int *__restrict__ flags, int *__restrict__ rowflag,
@@ -170,12 +172,12 @@ lfw_chunk_bwd_carry_kernel(const T *__restrict__ grad_state, float *__restrict__
   float2 s01 = Pair<T>::ld(sp), s23 = Pair<T>::ld(sp + 2);
   float R[4] = {s01.x, s01.y, s23.x, s23.y};
   int any = 0;
-  // batches of 4 chunks, last chunk first: loads of a batch precede its dependent FMA chain
-  for (int64_t c0 = nc - 1; c0 >= 0; c0 -= 4) {
-    float4 l[4], gg[4];
-    float a[4];
+  // batches of 8 chunks, last chunk first: loads of a batch precede its dependent FMA chain
+  for (int64_t c0 = nc - 1; c0 >= 0; c0 -= 8) {
+    float4 l[8], gg[8];
+    float a[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 8; ++j) {
       const int64_t c = (c0 - j >= 0) ? c0 - j : 0;
       const size_t bc = (size_t)b * nc + c;
       l[j] = *reinterpret_cast<const float4 *>(G + (bc * kDim + d) * kDim + k0);
@@ -184,7 +186,7 @@ lfw_chunk_bwd_carry_kernel(const T *__restrict__ grad_state, float *__restrict__
       if (d == 0 && k0 == 0) any |= flags[bc];
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 8; ++j) {
       if (c0 - j >= 0) {
         const size_t bc = (size_t)b * nc + c0 - j;
         *reinterpret_cast<float4 *>(G + (bc * kDim + d) * kDim + k0) = make_float4(R[0], R[1], R[2], R[3]);
@@ -574,11 +576,17 @@ static int chunk_backward_typed(const void *go, const void *gs, const void *x, c
                           4 * kDim + kDim + kFixCap) * sizeof(float) + 5 * kSub * kStgLd * sizeof(T);
   T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_chunk_bwd_main_kernel<T>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_main));
-  lfw_chunk_bwd_local_kernel<T><<<(unsigned)(B * nc), kThreads, sm_local, st>>>(
-      (const T *)go, (const T *)f, (const T *)q, (const T *)fk, s.G, s.Ac, s.Gc, s.flags, T_, nc);
-  T2FW_CHECK_LAUNCH(1);
+  if (umma_enabled()) {
+    const int rc = lfw_chunk_local_umma(true, go, f, q, fk, s.G, s.Ac, s.Gc, s.flags, B, T_,
+                                        std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16, st);
+    if (rc != T2FW_OK) return rc;
+  } else {
+    lfw_chunk_bwd_local_kernel<T><<<(unsigned)(B * nc), kThreads, sm_local, st>>>(
+        (const T *)go, (const T *)f, (const T *)q, (const T *)fk, s.G, s.Ac, s.Gc, s.flags, T_, nc);
+    T2FW_CHECK_LAUNCH(1);
+  }
   const int64_t n_carry = B * kDim * (kDim / 4);
-  lfw_chunk_bwd_carry_kernel<T><<<(unsigned)ceil_div64(n_carry, 256), 256, 0, st>>>(
+  lfw_chunk_bwd_carry_kernel<T><<<(unsigned)ceil_div64(n_carry, 128), 128, 0, st>>>(
       (const T *)gs, s.G, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ds, B, nc);
   T2FW_CHECK_LAUNCH(1);
   lfw_chunk_bwd_main_kernel<T><<<(unsigned)(B * nc), kThreads, sm_main, st>>>(

@@ -11,6 +11,8 @@
 // Scratch layout (floats): L[B][nc][64][64] | Ac[B][nc][64] | Gc[B][nc][64] | flags[B][nc] (int)
 // | rowflag[B] (int).  flags mark chunks whose gate products left the safe range; such batch
 // rows are recomputed by the scan kernels afterwards.
+#include <type_traits>
+
 #include "lfw_chunk.cuh"
 
 namespace t2fw {
@@ -111,7 +113,7 @@ lfw_chunk_local_kernel(const T *__restrict__ x, const T *__restrict__ f, const T
 // One thread per (b, d, 4 consecutive k): S_{c+1} = (Ac Gc^T) S_c + L_c.  L_c is overwritten with
 // the state at the START of chunk c; ckpt slot c receives the state after chunk c.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 lfw_chunk_carry_kernel(const T *__restrict__ state, float *__restrict__ L, const float *__restrict__ Ac,
                        const float *__restrict__ Gc, const int *__restrict__ flags,
                        int *__restrict__ rowflag, T *__restrict__ ckpt, int64_t B, int64_t nc) {
@@ -124,12 +126,12 @@ lfw_chunk_carry_kernel(const T *__restrict__ state, float *__restrict__ L, const
   float2 s01 = Pair<T>::ld(sp), s23 = Pair<T>::ld(sp + 2);
   float S[4] = {s01.x, s01.y, s23.x, s23.y};
   int any = 0;
-  // batches of 4 chunks: all loads of a batch are issued before its dependent FMA chain
-  for (int64_t c0 = 0; c0 < nc; c0 += 4) {
-    float4 l[4], gg[4];
-    float a[4];
+  // batches of 8 chunks: all loads of a batch are issued before its dependent FMA chain
+  for (int64_t c0 = 0; c0 < nc; c0 += 8) {
+    float4 l[8], gg[8];
+    float a[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 8; ++j) {
       const int64_t c = (c0 + j < nc) ? c0 + j : nc - 1;
       const size_t bc = (size_t)b * nc + c;
       l[j] = *reinterpret_cast<const float4 *>(L + (bc * kDim + d) * kDim + k0);
@@ -138,7 +140,7 @@ lfw_chunk_carry_kernel(const T *__restrict__ state, float *__restrict__ L, const
       if (d == 0 && k0 == 0) any |= flags[bc];
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 8; ++j) {
       if (c0 + j < nc) {
         const size_t bc = (size_t)b * nc + c0 + j;
         *reinterpret_cast<float4 *>(L + (bc * kDim + d) * kDim + k0) = make_float4(S[0], S[1], S[2], S[3]);
@@ -272,11 +274,17 @@ static int chunk_forward_typed(const void *x, const void *f, const void *q, cons
   const size_t sm_out = (4 * kC * kLd + kNSub * kSub * kLdP + 2 * kNSub * kDim) * sizeof(float);
   T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_chunk_output_kernel<T>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_out));
-  lfw_chunk_local_kernel<T><<<(unsigned)(B * nc), kThreads, sm_local, st>>>(
-      (const T *)x, (const T *)f, (const T *)k, (const T *)fk, s.L, s.Ac, s.Gc, s.flags, T_, nc);
-  T2FW_CHECK_LAUNCH(1);
+  if (umma_enabled()) {
+    const int rc = lfw_chunk_local_umma(false, x, f, k, fk, s.L, s.Ac, s.Gc, s.flags, B, T_,
+                                        std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16, st);
+    if (rc != T2FW_OK) return rc;
+  } else {
+    lfw_chunk_local_kernel<T><<<(unsigned)(B * nc), kThreads, sm_local, st>>>(
+        (const T *)x, (const T *)f, (const T *)k, (const T *)fk, s.L, s.Ac, s.Gc, s.flags, T_, nc);
+    T2FW_CHECK_LAUNCH(1);
+  }
   const int64_t n_carry = B * kDim * (kDim / 4);
-  lfw_chunk_carry_kernel<T><<<(unsigned)ceil_div64(n_carry, 256), 256, 0, st>>>(
+  lfw_chunk_carry_kernel<T><<<(unsigned)ceil_div64(n_carry, 128), 128, 0, st>>>(
       (const T *)state, s.L, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ckpt, B, nc);
   T2FW_CHECK_LAUNCH(1);
   lfw_chunk_output_kernel<T><<<(unsigned)(B * nc), kThreads, sm_out, st>>>(
