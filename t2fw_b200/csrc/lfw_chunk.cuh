@@ -119,9 +119,11 @@ __device__ __forceinline__ float sanitize_gate(float g) {
 template <typename T>
 __device__ __forceinline__ bool prep_side(const T *__restrict__ gate, const T *__restrict__ mul,
                                           const T *__restrict__ div, int nvalid, float *out_mul,
-                                          float *out_div, float *out_pre, float *out_raw, float *blk) {
-  const int I = threadIdx.x >> 5;
-  const int c = (threadIdx.x & 31) * 2;
+                                          float *out_div, float *out_pre, float *out_raw, float *blk,
+                                          int tid = -1) {
+  if (tid < 0) tid = threadIdx.x;       // callers with more than 128 threads pass a 0..127 index
+  const int I = tid >> 5;
+  const int c = (tid & 31) * 2;
   float2 gv[kSub], mv[kSub], dv[kSub];
 #pragma unroll
   for (int t = 0; t < kSub; ++t) {
@@ -154,6 +156,97 @@ __device__ __forceinline__ bool prep_side(const T *__restrict__ gate, const T *_
   *reinterpret_cast<float2 *>(blk + I * kDim + c) = make_float2(p0, p1);
   // !(x >= lo) also catches NaN
   return !(lo >= kRangeLo) || !(hi <= kRangeHi);
+}
+
+// ---- pieces shared by the backward kernels --------------------------------------------------
+// A[m][k] = t[(m0+m)*ld + k0+k] * sc[k0+k]  (per-contraction-index scale)
+__device__ __forceinline__ void lda_colscaled(uint32_t (&a)[4], const float *t, int ld, int m0, int k0,
+                                              int g, int tq, const float *sc) {
+  const float s0 = sc[k0 + tq], s1 = sc[k0 + tq + 4];
+  a[0] = to_tf32(t[(m0 + g) * ld + k0 + tq] * s0);
+  a[1] = to_tf32(t[(m0 + g + 8) * ld + k0 + tq] * s0);
+  a[2] = to_tf32(t[(m0 + g) * ld + k0 + tq + 4] * s1);
+  a[3] = to_tf32(t[(m0 + g + 8) * ld + k0 + tq + 4] * s1);
+}
+
+// state step on accumulator registers (warp w owns rows 16w..16w+15, all 64 columns):
+//   S <- (aI gI^T) .* S + (Xt aI)^T (Kt gI)   for sub-block I
+__device__ __forceinline__ void state_step_regs(float (&S)[8][4], const float *Xt, const float *Kt,
+                                                const float *aI, const float *gI, int I, int w, int g,
+                                                int tq) {
+  const float a_lo = aI[I * kDim + 16 * w + g], a_hi = aI[I * kDim + 16 * w + g + 8];
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+    const float2 gg = *reinterpret_cast<const float2 *>(gI + I * kDim + nt * 8 + 2 * tq);
+    S[nt][0] *= a_lo * gg.x;
+    S[nt][1] *= a_lo * gg.y;
+    S[nt][2] *= a_hi * gg.x;
+    S[nt][3] *= a_hi * gg.y;
+  }
+#pragma unroll
+  for (int ks = 0; ks < 2; ++ks) {
+    uint32_t a[4];
+    lda_t_scaled(a, Xt, kLd, 16 * w, I * kSub + 8 * ks, g, tq, a_lo, a_hi);
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      uint32_t b[2];
+      ldb_scaled(b, Kt, kLd, I * kSub + 8 * ks, nt * 8, g, tq, gI[I * kDim + nt * 8 + g]);
+      mma_tf32(S[nt], a, b);
+    }
+  }
+}
+
+// state-gradient step: R <- (aI gI^T) .* R + dOt_I^T Qt_I
+__device__ __forceinline__ void grad_step_regs(float (&R)[8][4], const float *dOt, const float *Qt,
+                                               const float *aI, const float *gI, int I, int w, int g,
+                                               int tq, bool scale_old) {
+  if (scale_old) {
+    const float a_lo = aI[I * kDim + 16 * w + g], a_hi = aI[I * kDim + 16 * w + g + 8];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const float2 gg = *reinterpret_cast<const float2 *>(gI + I * kDim + nt * 8 + 2 * tq);
+      R[nt][0] *= a_lo * gg.x;
+      R[nt][1] *= a_lo * gg.y;
+      R[nt][2] *= a_hi * gg.x;
+      R[nt][3] *= a_hi * gg.y;
+    }
+  }
+#pragma unroll
+  for (int ks = 0; ks < 2; ++ks) {
+    uint32_t a[4];
+    lda_t(a, dOt, kLd, 16 * w, I * kSub + 8 * ks, g, tq);   // A[d][s] = dOt[s][d]
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      uint32_t b[2];
+      ldb(b, Qt, kLd, I * kSub + 8 * ks, nt * 8, g, tq);    // B[s][k] = Qt[s][k]
+      mma_tf32(R[nt], a, b);
+    }
+  }
+}
+
+// inclusive suffix / exclusive prefix sums over the 16 rows of a sub-block for values held in
+// the MMA accumulator layout (row g -> lo, row g+8 -> hi; lanes with equal tq share a column)
+__device__ __forceinline__ void suffix16(float &lo, float &hi, int g, int tq) {
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) {
+    const float yl = __shfl_down_sync(0xffffffffu, lo, 4 * o);
+    const float yh = __shfl_down_sync(0xffffffffu, hi, 4 * o);
+    if (g + o < 8) { lo += yl; hi += yh; }
+  }
+  lo += __shfl_sync(0xffffffffu, hi, tq);   // g = 0 holds the whole upper half
+}
+__device__ __forceinline__ void exclusive_prefix16(float &lo, float &hi, int g, int tq) {
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) {
+    const float yl = __shfl_up_sync(0xffffffffu, lo, 4 * o);
+    const float yh = __shfl_up_sync(0xffffffffu, hi, 4 * o);
+    if (g >= o) { lo += yl; hi += yh; }
+  }
+  const float tot_lo = __shfl_sync(0xffffffffu, lo, 28 + tq);  // g = 7 holds the whole lower half
+  const float el = __shfl_up_sync(0xffffffffu, lo, 4);
+  const float eh = __shfl_up_sync(0xffffffffu, hi, 4);
+  lo = (g >= 1) ? el : 0.f;
+  hi = ((g >= 1) ? eh : 0.f) + tot_lo;
 }
 
 }  // namespace chunk
