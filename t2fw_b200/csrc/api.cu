@@ -47,8 +47,10 @@ int64_t t2fw_launch_count(void) { return g_launches.load(std::memory_order_relax
 
 int64_t t2fw_lfw_default_ckpt_every(int64_t T, int64_t D, int64_t K, int dtype) {
   (void)T;
+  (void)D;
+  (void)K;
   (void)dtype;
-  return (D >= 128 && K >= 128) ? 128 : 64;
+  return 64;   // the interval the chunked tensor-core kernels are built around
 }
 
 int64_t t2fw_lfw_ckpt_slots(int64_t T, int64_t ckpt_every) {
@@ -70,6 +72,8 @@ size_t t2fw_lfw_forward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K
                                       int64_t ckpt_every) {
   if (T > 1 && chunk_path_enabled() && lfw_chunk_supported(D, K, dtype, ckpt_every))
     return lfw_chunk_forward_scratch_bytes(B, T);
+  if (T > 1 && chunk_path_enabled() && lfw_blocked_supported(D, K, dtype, ckpt_every))
+    return lfw_blocked_forward_scratch_bytes(B, T, D, K);
   return 0;
 }
 
@@ -77,6 +81,8 @@ size_t t2fw_lfw_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t 
                                        int64_t ckpt_every) {
   if (chunk_path_enabled() && lfw_chunk_supported(D, K, dtype, ckpt_every))
     return lfw_chunk_backward_scratch_bytes(B, T);
+  if (chunk_path_enabled() && lfw_blocked_supported(D, K, dtype, ckpt_every))
+    return lfw_blocked_backward_scratch_bytes(B, T, D, K);
   return 0;
 }
 
@@ -123,6 +129,9 @@ int t2fw_lfw_forward(const void *x, const void *f, const void *q, const void *k,
       set_error("lfw forward needs %zu bytes of scratch, got %zu", need, scratch_bytes);
       return T2FW_ERR_SCRATCH;
     }
+    if (!lfw_chunk_supported(D, K, dtype, ckpt_every))
+      return lfw_blocked_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, T, D, K, dtype,
+                                 scratch, st);
     const int *rowflag = nullptr;
     rc = lfw_chunk_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, T, dtype, scratch,
                            st, &rowflag);
@@ -155,6 +164,9 @@ int t2fw_lfw_backward(const void *grad_output, const void *grad_state, const voi
       return T2FW_ERR_SCRATCH;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!lfw_chunk_supported(D, K, dtype, ckpt_every))
+      return lfw_blocked_backward(grad_output, grad_state, x, f, q, k, f_key, state, ckpt_states,
+                                  d_x, d_f, d_q, d_k, d_f_key, d_state, B, T, D, K, dtype, scratch, st);
     const int *rowflag = nullptr;
     rc = lfw_chunk_backward(grad_output, grad_state, x, f, q, k, f_key, state, ckpt_states, d_x,
                             d_f, d_q, d_k, d_f_key, d_state, B, T, dtype, scratch, st, &rowflag);

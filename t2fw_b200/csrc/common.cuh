@@ -105,6 +105,17 @@ int lfw_chunk_backward(const void *go, const void *gs, const void *x, const void
                        const void *k, const void *fk, const void *state, const void *ckpt, void *dx,
                        void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B, int64_t T,
                        int dtype, void *scratch, cudaStream_t st, const int **rowflag_out);
+// state shapes that are grids of 64 x 64 blocks (D, K multiples of 64, up to 256)
+bool lfw_blocked_supported(int64_t D, int64_t K, int dtype, int64_t ckpt_every);
+size_t lfw_blocked_forward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K);
+size_t lfw_blocked_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K);
+int lfw_blocked_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,
+                        const void *state, void *out, void *ckpt, int64_t B, int64_t T, int64_t D,
+                        int64_t K, int dtype, void *scratch, cudaStream_t st);
+int lfw_blocked_backward(const void *go, const void *gs, const void *x, const void *f, const void *q,
+                         const void *k, const void *fk, const void *state, const void *ckpt, void *dx,
+                         void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B, int64_t T,
+                         int64_t D, int64_t K, int dtype, void *scratch, cudaStream_t st);
 // tcgen05 versions of the two chunk-local kernels (same scratch layout as the mma.sync ones)
 int lfw_chunk_local_umma(bool backward, const void *val_d, const void *gate_d, const void *val_k,
                          const void *gate_k, float *M, float *Ac, float *Gc, int *flags, int64_t B,

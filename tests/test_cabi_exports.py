@@ -44,7 +44,7 @@ def test_cheap_entry_points_run_without_gpu():
     assert lib.t2fw_lfw_ckpt_slots(385, 64) == 7
     assert lib.t2fw_lfw_ckpt_slots(1, 64) == 1
     assert lib.t2fw_lfw_default_ckpt_every(1024, 64, 64, 0) == 64
-    assert lib.t2fw_lfw_default_ckpt_every(16384, 128, 128, 0) == 128
+    assert lib.t2fw_lfw_default_ckpt_every(16384, 128, 128, 0) == 64
     assert lib.t2fw_dfw_backward_scratch_bytes(2, 8, 4, 4, 0) == 256
     assert lib.t2fw_dfw_backward_scratch_bytes(2, 8, 4, 4, 2) == 0
 

@@ -229,3 +229,20 @@ def test_decode_shapes(cuda, B, D, K):
     assert max_rel_err(out, r_out) <= OUT_TOL[torch.float16]
     assert max_rel_err(ckpt[:, -1], r_fin) <= OUT_TOL[torch.float16]
     assert _lib.load_core().t2fw_device_status() == 0
+
+
+@pytest.mark.parametrize("D,K", [(128, 64), (64, 128), (128, 128), (192, 64), (64, 256)])
+def test_blocked_state_shapes(cuda, D, K):
+    """D x K states that are grids of 64 x 64 blocks run on the tensor-core path as a virtual
+    batch; outputs and gradients are sums over the other axis' blocks."""
+    dev = to_dev(lfw_inputs(2, 150, D, K, "sigmoid", 0.5, D + K), torch.float16, cuda)
+    check_against_oracle(dev, run_cabi(*dev), torch.float16)
+
+
+def test_blocked_extreme_gates(cuda):
+    """Flagged blocks of a D=K=128 problem fall back to the scan kernels block by block."""
+    x, f, q, k, fk, s, go, gs = lfw_inputs(2, 100, 128, 128, "sigmoid", 0.5, 71)
+    fk[1, :, 64:] = 1e-3
+    f[0, 30, :] = 0.0
+    dev = to_dev((x, f, q, k, fk, s, go, gs), torch.float16, cuda)
+    check_against_oracle(dev, run_cabi(*dev), torch.float16)
