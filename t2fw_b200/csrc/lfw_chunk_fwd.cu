@@ -11,6 +11,7 @@
 // Scratch layout (floats): L[B][nc][64][64] | Ac[B][nc][64] | Gc[B][nc][64] | flags[B][nc] (int)
 // | rowflag[B] (int).  flags mark chunks whose gate products left the safe range; such batch
 // rows are recomputed by the scan kernels afterwards.
+#include <cstdlib>
 #include <type_traits>
 
 #include "lfw_chunk.cuh"
@@ -18,6 +19,15 @@
 namespace t2fw {
 
 using namespace chunk;
+
+// persistent, prefetching version of the output phase (lfw_chunk_fwd_out.cu)
+int lfw_chunk_output_persist(const void *x, const void *f, const void *q, const void *k, const void *fk,
+                             const float *Sstart, void *out, int64_t B, int64_t T_, int dtype,
+                             cudaStream_t st);
+static bool persist_enabled() {
+  const char *e = std::getenv("T2FW_DISABLE_PERSIST");
+  return !(e && e[0] == '1');
+}
 
 namespace {
 
@@ -287,10 +297,17 @@ static int chunk_forward_typed(const void *x, const void *f, const void *q, cons
   lfw_chunk_carry_kernel<T><<<(unsigned)ceil_div64(n_carry, 128), 128, 0, st>>>(
       (const T *)state, s.L, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ckpt, B, nc);
   T2FW_CHECK_LAUNCH(1);
-  lfw_chunk_output_kernel<T><<<(unsigned)(B * nc), kThreads, sm_out, st>>>(
-      (const T *)x, (const T *)f, (const T *)q, (const T *)k, (const T *)fk, s.L, (T *)out, T_, nc);
-  T2FW_CHECK_LAUNCH(1);
-  return T2FW_OK;
+  int rc_out = T2FW_ERR_UNSUPPORTED;
+  if (persist_enabled())
+    rc_out = lfw_chunk_output_persist(x, f, q, k, fk, s.L, out, B, T_,
+                                      std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16, st);
+  if (rc_out == T2FW_ERR_UNSUPPORTED) {
+    lfw_chunk_output_kernel<T><<<(unsigned)(B * nc), kThreads, sm_out, st>>>(
+        (const T *)x, (const T *)f, (const T *)q, (const T *)k, (const T *)fk, s.L, (T *)out, T_, nc);
+    T2FW_CHECK_LAUNCH(1);
+    rc_out = T2FW_OK;
+  }
+  return rc_out;
 }
 
 int lfw_chunk_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,

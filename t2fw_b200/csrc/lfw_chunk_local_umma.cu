@@ -145,7 +145,8 @@ namespace {
 int *g_umma_status_addr[64] = {};
 }
 
-static int umma_status_ptr(int **out) {
+// device address of the status word kernels set when a bounded wait expires
+int lfw_chunk_status_ptr(int **out) {
   int dev = 0;
   T2FW_CHECK_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) {
@@ -173,7 +174,7 @@ int lfw_chunk_local_umma(bool backward, const void *val_d, const void *gate_d, c
                          int64_t T_, int dtype, cudaStream_t st) {
   const int64_t nc = ceil_div64(T_, kC);
   int *status = nullptr;
-  int rc = umma_status_ptr(&status);
+  int rc = lfw_chunk_status_ptr(&status);
   if (rc != T2FW_OK) return rc;
   const size_t smem = 2 * (size_t)kTileBytes;
   const unsigned grid = (unsigned)(B * nc);
