@@ -161,11 +161,14 @@ static int chunk_backward_typed(const void *go, const void *gs, const void *x, c
   const int64_t nc = ceil_div64(T_, kC);
   BwdScratch s = carve(scratch, B, nc);
   const size_t sm_local = (2 * kC * kLd + 2 * kNSub * kDim) * sizeof(float);
+  bool local_done = false;
   if (umma_enabled()) {
     const int rc = lfw_chunk_local_umma(true, go, f, q, fk, s.G, s.Ac, s.Gc, s.flags, B, T_,
                                         std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16, st);
-    if (rc != T2FW_OK) return rc;
-  } else {
+    if (rc == T2FW_OK) local_done = true;
+    else if (rc != T2FW_ERR_UNSUPPORTED) return rc;
+  }
+  if (!local_done) {
     lfw_chunk_bwd_local_kernel<T><<<(unsigned)(B * nc), kThreads, sm_local, st>>>(
         (const T *)go, (const T *)f, (const T *)q, (const T *)fk, s.G, s.Ac, s.Gc, s.flags, T_, nc);
     T2FW_CHECK_LAUNCH(1);

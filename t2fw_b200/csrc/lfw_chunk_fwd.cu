@@ -284,11 +284,14 @@ static int chunk_forward_typed(const void *x, const void *f, const void *q, cons
   const size_t sm_out = (4 * kC * kLd + kNSub * kSub * kLdP + 2 * kNSub * kDim) * sizeof(float);
   T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_chunk_output_kernel<T>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_out));
+  bool local_done = false;
   if (umma_enabled()) {
     const int rc = lfw_chunk_local_umma(false, x, f, k, fk, s.L, s.Ac, s.Gc, s.flags, B, T_,
                                         std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16, st);
-    if (rc != T2FW_OK) return rc;
-  } else {
+    if (rc == T2FW_OK) local_done = true;
+    else if (rc != T2FW_ERR_UNSUPPORTED) return rc;
+  }
+  if (!local_done) {
     lfw_chunk_local_kernel<T><<<(unsigned)(B * nc), kThreads, sm_local, st>>>(
         (const T *)x, (const T *)f, (const T *)k, (const T *)fk, s.L, s.Ac, s.Gc, s.flags, T_, nc);
     T2FW_CHECK_LAUNCH(1);
