@@ -168,6 +168,12 @@ int t2fw_selftest_umma(const float *A1, const float *B1, const float *A2, const 
                        float *D1, float *D2, int N, int Kc, int a_mn, int b_mn, int *status,
                        void *stream);
 
+/* Same diagnostic with bf16 operands (rounded from the fp32 inputs inside the kernel); here both
+ * operand orientations exist, a_mn / b_mn in {0, 1}.  Kc: multiple of 16 in [16, 64]. */
+int t2fw_selftest_umma16(const float *A1, const float *B1, const float *A2, const float *B2,
+                         float *D1, float *D2, int N, int Kc, int a_mn, int b_mn, int *status,
+                         void *stream);
+
 #ifdef __cplusplus
 }
 #endif

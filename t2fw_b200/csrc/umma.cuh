@@ -62,6 +62,43 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N, bool a_mn, 
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
+// ---- 16-bit operand tiles (bf16 / fp16): core matrix = 8 rows x 8 elements (16 bytes per row) --
+constexpr int kColGroupBytes16 = 144;
+__host__ __device__ constexpr int tile16_row_group_bytes(int cols) { return (cols / 8) * kColGroupBytes16; }
+__host__ __device__ constexpr int tile16_bytes(int rows, int cols) {
+  return ((rows + 7) / 8) * tile16_row_group_bytes(cols);
+}
+__device__ __forceinline__ int tile16_off(int r, int c, int cols) {
+  return (r & 7) * 16 + (c & 7) * 2 + (r >> 3) * tile16_row_group_bytes(cols) + (c >> 3) * kColGroupBytes16;
+}
+// K-major view (tile rows = M/N index, contraction along tile columns), k-step = 16 columns
+__device__ __forceinline__ uint64_t desc16_kmajor(uint32_t tile_addr, int cols, int row0, int ks) {
+  const uint32_t a = tile_addr + (row0 >> 3) * tile16_row_group_bytes(cols) + ks * 2 * kColGroupBytes16;
+  return make_desc(a, kColGroupBytes16, tile16_row_group_bytes(cols));
+}
+// MN-major view (tile columns = M/N index, contraction along tile rows), k-step = 16 rows
+__device__ __forceinline__ uint64_t desc16_mnmajor(uint32_t tile_addr, int cols, int col0, int ks, int row0 = 0) {
+  const uint32_t a = tile_addr + ((row0 >> 3) + 2 * ks) * tile16_row_group_bytes(cols) + (col0 >> 3) * kColGroupBytes16;
+  return make_desc(a, tile16_row_group_bytes(cols), kColGroupBytes16);
+}
+// instruction descriptor: BF16 x BF16 -> F32 (fmt 1) or F16 x F16 -> F32 (fmt 0), dense
+__host__ __device__ constexpr uint32_t make_idesc_16(int M, int N, bool a_mn, bool b_mn, int fmt) {
+  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((a_mn ? 1u : 0u) << 15) |
+         ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+
 // ---- tensor memory --------------------------------------------------------------------------
 // One full warp allocates `cols` columns (power of two >= 32); the base address lands in *slot.
 __device__ __forceinline__ void tmem_alloc(uint32_t *slot, uint32_t cols) {

@@ -96,11 +96,99 @@ umma_selftest_kernel(const float *__restrict__ A1, const float *__restrict__ B1,
   if (warp == 0) tmem_dealloc(tbase, 64);
 }
 
+// bf16 variant: operands arrive as fp32, are rounded to bf16 in the kernel; both orientations
+__global__ void __launch_bounds__(128)
+umma_selftest16_kernel(const float *__restrict__ A1, const float *__restrict__ B1,
+                       const float *__restrict__ A2, const float *__restrict__ B2,
+                       float *__restrict__ D1, float *__restrict__ D2, int N, int Kc, int a_mn,
+                       int b_mn, int *__restrict__ status) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_fail;
+  const int a_rows = a_mn ? Kc : kM, a_cols = a_mn ? kM : Kc;
+  const int b_rows = b_mn ? Kc : N, b_cols = b_mn ? N : Kc;
+  const int a_bytes = tile16_bytes(a_rows, a_cols), b_bytes = tile16_bytes(b_rows, b_cols);
+  unsigned char *tA1 = smem, *tA2 = tA1 + a_bytes, *tB1 = tA2 + a_bytes, *tB2 = tB1 + b_bytes;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    s_fail = 0;
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 64);
+  for (int idx = threadIdx.x; idx < kM * Kc; idx += blockDim.x) {
+    const int m = idx / Kc, kk = idx % Kc;
+    const int off = a_mn ? tile16_off(kk, m, a_cols) : tile16_off(m, kk, a_cols);
+    *reinterpret_cast<__nv_bfloat16 *>(tA1 + off) = __float2bfloat16_rn(A1[idx]);
+    *reinterpret_cast<__nv_bfloat16 *>(tA2 + off) = __float2bfloat16_rn(A2[idx]);
+  }
+  for (int idx = threadIdx.x; idx < N * Kc; idx += blockDim.x) {
+    const int n = idx / Kc, kk = idx % Kc;
+    const int off = b_mn ? tile16_off(kk, n, b_cols) : tile16_off(n, kk, b_cols);
+    *reinterpret_cast<__nv_bfloat16 *>(tB1 + off) = __float2bfloat16_rn(B1[idx]);
+    *reinterpret_cast<__nv_bfloat16 *>(tB2 + off) = __float2bfloat16_rn(B2[idx]);
+  }
+  fence_async_smem();
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tbase = tmem_slot;
+  if (threadIdx.x == 0) {
+    const uint32_t idesc = make_idesc_16(kM, N, a_mn != 0, b_mn != 0, 1);
+    for (int pair = 0; pair < 2; ++pair) {
+      const uint32_t ta = smem_u32(pair ? tA2 : tA1), tb = smem_u32(pair ? tB2 : tB1);
+      const uint32_t d = tmem_addr(tbase, pair * 16, 0);
+      for (int ks = 0; ks < Kc / 16; ++ks) {
+        const uint64_t da = a_mn ? desc16_mnmajor(ta, a_cols, 0, ks) : desc16_kmajor(ta, a_cols, 0, ks);
+        const uint64_t db = b_mn ? desc16_mnmajor(tb, b_cols, 0, ks) : desc16_kmajor(tb, b_cols, 0, ks);
+        mma_f16(d, da, db, idesc, ks > 0);
+      }
+    }
+    mma_commit(&bar);
+  }
+  if (!mbar_wait(&bar, 0)) s_fail = 1;
+  __syncthreads();
+  fence_after_sync();
+  if (!s_fail) {
+    const int row = 16 * warp + (lane & 15);
+    float *dst = (lane < 16 ? D1 : D2) + (size_t)row * N;
+    for (int c0 = 0; c0 < N; c0 += 16) {
+      float v[16];
+      tmem_ld16(tmem_addr(tbase, 32 * warp, c0), v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (c0 + j < N) dst[c0 + j] = v[j];
+    }
+  } else if (threadIdx.x == 0) {
+    atomicExch(status, 1);
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 64);
+}
+
 }  // namespace
 
 }  // namespace t2fw
 
 using namespace t2fw;
+
+extern "C" int t2fw_selftest_umma16(const float *A1, const float *B1, const float *A2, const float *B2,
+                                    float *D1, float *D2, int N, int Kc, int a_mn, int b_mn,
+                                    int *status, void *stream) {
+  T2FW_CHECK_ARG(A1 && B1 && A2 && B2 && D1 && D2 && status, "null pointer argument");
+  T2FW_CHECK_ARG(N >= 8 && N <= 64 && N % 8 == 0 && Kc >= 16 && Kc <= 64 && Kc % 16 == 0,
+                 "selftest16: N multiple of 8 in [8, 64], Kc multiple of 16 in [16, 64]");
+  const int a_bytes = a_mn ? umma::tile16_bytes(Kc, 64) : umma::tile16_bytes(64, Kc);
+  const int b_bytes = b_mn ? umma::tile16_bytes(Kc, N) : umma::tile16_bytes(N, Kc);
+  const size_t smem = 2 * (size_t)a_bytes + 2 * (size_t)b_bytes;
+  umma_selftest16_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(A1, B1, A2, B2, D1, D2, N,
+                                                                             Kc, a_mn, b_mn, status);
+  T2FW_CHECK_LAUNCH(1);
+  return T2FW_OK;
+}
 
 extern "C" int t2fw_selftest_umma(const float *A1, const float *B1, const float *A2, const float *B2,
                                   float *D1, float *D2, int N, int Kc, int a_mn, int b_mn,

@@ -51,3 +51,35 @@ def test_mn_major_tf32_is_rejected():
     fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 4 + [ctypes.c_void_p, ctypes.c_void_p]
     assert fn(1, 1, 1, 1, 1, 1, 16, 16, 1, 0, 1, None) == 1
     assert b"K-major" in lib.t2fw_last_error()
+
+
+def _bf16(t):
+    return t.to(torch.bfloat16).to(torch.float32)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("a_mn", [0, 1])
+@pytest.mark.parametrize("b_mn", [0, 1])
+@pytest.mark.parametrize("N,Kc", [(8, 16), (16, 16), (16, 64), (64, 16), (64, 64), (32, 48)])
+def test_umma16_products(cuda, N, Kc, a_mn, b_mn):
+    from t2fw_b200 import _lib
+
+    lib = _lib.load_core()
+    fn = lib.t2fw_selftest_umma16
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 4 + [ctypes.c_void_p, ctypes.c_void_p]
+    g = torch.Generator().manual_seed(N * 100 + Kc + 7)
+    A1, A2 = (_bf16(torch.randn(64, Kc, generator=g)).to(cuda) for _ in range(2))
+    B1, B2 = (_bf16(torch.randn(N, Kc, generator=g)).to(cuda) for _ in range(2))
+    D1 = torch.full((64, N), float("nan"), device=cuda)
+    D2 = torch.full((64, N), float("nan"), device=cuda)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    rc = fn(A1.data_ptr(), B1.data_ptr(), A2.data_ptr(), B2.data_ptr(), D1.data_ptr(), D2.data_ptr(),
+            N, Kc, a_mn, b_mn, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.t2fw_last_error().decode()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded wait expired"
+    for D, A, B in ((D1, A1, B1), (D2, A2, B2)):
+        ref = (A.double() @ B.double().T)
+        assert torch.isfinite(D).all()
+        assert (D.double() - ref).abs().max().item() <= 1e-4 * max(1.0, ref.abs().max().item())
