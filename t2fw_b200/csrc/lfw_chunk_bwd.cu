@@ -21,6 +21,7 @@
 // from identical TF32-rounded operands on both sides:
 //   H = suffix_t[ Qt.*(dOt S0 + Z Kt) - Kt.*(Z^T Qt) ] + exclusive_prefix_t[ Kt.*gI.*((Xt aI) R) ]
 //       + gI .* sum_d aI R S0 ;   d_f_key = H / g        (d side: same with the roles exchanged)
+#include <cstdlib>
 #include <type_traits>
 
 #include "lfw_chunk.cuh"
@@ -35,7 +36,21 @@ int lfw_chunk_bwd_main(const void *go, const void *x, const void *f, const void 
                        void *dx, void *df, void *dq, void *dk, void *dfk, int *rowflag, int64_t B,
                        int64_t T_, int dtype, cudaStream_t st);
 
+// tcgen05 main kernel (lfw_chunk_bwd_umma.cu); T2FW_ERR_UNSUPPORTED without a launch if it cannot run
+int lfw_chunk_bwd_main_umma(const void *go, const void *x, const void *f, const void *q, const void *k,
+                            const void *fk, const void *state, const void *ckpt, const float *Rend,
+                            void *dx, void *df, void *dq, void *dk, void *dfk, int *rowflag, int64_t B,
+                            int64_t T_, int dtype, cudaStream_t st);
+
 namespace {
+
+bool bwd_umma_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("T2FW_ENABLE_BWD_UMMA");   // experimental: off unless asked for
+    return e && e[0] == '1';
+  }();
+  return on && umma_enabled();
+}
 
 struct BwdScratch {
   float *G, *Ac, *Gc;
@@ -177,8 +192,14 @@ static int chunk_backward_typed(const void *go, const void *gs, const void *x, c
   lfw_chunk_bwd_carry_kernel<T><<<(unsigned)ceil_div64(n_carry, 128), 128, 0, st>>>(
       (const T *)gs, s.G, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ds, B, nc);
   T2FW_CHECK_LAUNCH(1);
+  const int dt = std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16;
+  if (bwd_umma_enabled()) {
+    const int rc = lfw_chunk_bwd_main_umma(go, x, f, q, k, fk, state, ckpt, s.G, dx, df, dq, dk, dfk,
+                                           s.rowflag, B, T_, dt, st);
+    if (rc != T2FW_ERR_UNSUPPORTED) return rc;
+  }
   return lfw_chunk_bwd_main(go, x, f, q, k, fk, state, ckpt, s.G, dx, df, dq, dk, dfk, s.rowflag, B, T_,
-                            std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16, st);
+                            dt, st);
 }
 
 int lfw_chunk_backward(const void *go, const void *gs, const void *x, const void *f, const void *q,
