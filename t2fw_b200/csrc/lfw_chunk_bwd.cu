@@ -46,8 +46,8 @@ namespace {
 
 bool bwd_umma_enabled() {
   static const bool on = [] {
-    const char *e = std::getenv("T2FW_ENABLE_BWD_UMMA");   // experimental: off unless asked for
-    return e && e[0] == '1';
+    const char *e = std::getenv("T2FW_DISABLE_BWD_UMMA");
+    return !(e && e[0] == '1');
   }();
   return on && umma_enabled();
 }

@@ -8,16 +8,18 @@
 //     transposed copies exist.  A product of two split operands is three MMAs (hi*hi, hi*lo,
 //     lo*hi) with fp32 accumulation in tensor memory.
 //   * every result is feature-major: a [64 features x 16 steps] accumulator whose rows are
-//     tensor-memory lanes, so that after tcgen05.ld a thread holds ONE feature over the steps of
-//     a sub-block and all the prefix / suffix sums of the gate gradients are register-local.
-//     k-side results live in tensor-memory lanes 0-15 of each quarter, d-side results in lanes
-//     16-31, so the two halves of every warp run the same code on the two sides.
+//     tensor-memory lanes, so that after tcgen05.ld a thread holds ONE feature over four steps
+//     of a sub-block and the prefix / suffix sums of the gate gradients are register-local up
+//     to one exchange between the four warps of a lane quarter.  k-side results live in
+//     tensor-memory lanes 0-15 of each quarter, d-side results in lanes 16-31, so the two
+//     halves of every warp run the same code on the two sides.
 //   * the forward states S[0..3] at the starts of the four sub-blocks are built once per chunk
 //     and stay in tensor memory (fp32); the state gradient R stays in registers (fp32).
-//   * four more warps do nothing but issue MMAs (one elected thread each: a thread issues a
-//     small MMA only every ~90 cycles, the tensor core retires one every ~30).  The MMAs of a
-//     sub-block go into one of two accumulator buffers and run while the eight worker warps do
-//     the register work of the previous sub-block (epilogue, exact tiny-gate path, write-out).
+//   * 16 worker warps (lane quarter x column / step quarter) do the register work; 4 helper
+//     warps issue the MMAs (one elected thread each: a thread issues a small MMA only every
+//     ~55 cycles, the tensor core retires one every ~25), evaluate the exact tiny-gate formula
+//     and write the results out.  The MMAs of a sub-block go into one of two accumulator
+//     buffers and run while the workers finish the previous sub-block.
 //   * the CTA is persistent; the six raw 8 KB input blocks, the start state and the end-of-chunk
 //     state gradient of the next chunk are fetched by bulk asynchronous copies while the
 //     current chunk is processed.
@@ -26,7 +28,7 @@
 //   TQ = S0^T dOt + Kt Z^T      T2 = Qt Z        T7 = R~^T Xt       (rows k;  Z = tril(dOt^T Xt))
 //   TO = S0 Qt   + Xt P^T       T4 = dOt P       T8 = R~ Kt         (rows d;  P = tril(Qt^T Kt))
 //   dq = gp.*TQ   dk = (T2+T7)./gp   dx = (T4+T8)./ap   R_prev = R~ + dOt Qt^T
-//   H  = suffix_t[Qt.*TQ - Kt.*T2] + exclusive_prefix_t[Kt.*T7] + diag(R~^T S0);  d_f_key = H./g
+//   H  = suffix_t[Qt.*TQ - Kt.*T2] + exclusive_prefix_t[Kt.*T7] + sum_d (R~ .* S0);  d_f_key = H./g
 //   (d side the same with the roles exchanged; gates below 2^-10 get the exact formula).
 #include <type_traits>
 
@@ -56,15 +58,16 @@ __device__ long long g_prof[32];
 
 namespace {
 
-constexpr int kT = 256;        // worker threads: 8 warps = 4 lane quarters x 2 column / step halves
-constexpr int kIssuers = 4;
-constexpr int kTAll = kT + 32 * kIssuers;   // + warps 8..11: one elected thread each issues MMAs
+constexpr int kParts = 4;                   // column / step quarters
+constexpr int kTW = 128 * kParts;           // worker threads: 4 lane quarters x 4 parts
+constexpr int kHelpers = 4;                 // helper warps
+constexpr int kTAll = kTW + 32 * kHelpers;
 constexpr int kCG = umma::kColGroupBytes16;                // 144
-constexpr int kRG = umma::tile16_row_group_bytes(kDim);    // 1152
 constexpr int kTile = umma::tile16_bytes(kDim, kDim);      // 9216
 constexpr int kRGs = umma::tile16_row_group_bytes(kSub);   // 288
 constexpr int kTileS = umma::tile16_bytes(kSub, kSub);     // 576
 constexpr int kStgLd = 72;      // elements per row of the 16-bit output staging tiles
+constexpr int kStgBytes = 5 * kSub * kStgLd * 2;
 constexpr int kFixCap = 64;     // tiny-gate entries per sub-block
 constexpr float kTinyGate = 9.765625e-4f;   // 2^-10
 constexpr int kRawBytes = kC * kDim * 2;
@@ -77,24 +80,30 @@ constexpr int oP = 12 * kTile;                    // [4 blocks][hi, lo] small ti
 constexpr int oZ = oP + 8 * kTileS;
 constexpr int oaI = oZ + 8 * kTileS;
 constexpr int ogI = oaI + kNSub * kDim * 4;
-constexpr int oXc = ogI + kNSub * kDim * 4;       // [2][256] floats
-constexpr int oFixCode = oXc + 2 * kT * 4;        // [4][kFixCap] int
+constexpr int oXc = ogI + kNSub * kDim * 4;       // [2][kTW] floats: scan totals of the parts
+constexpr int oC4 = oXc + 2 * kTW * 4;            // [2 buffers][k side, d side][4][64] floats
+constexpr int oFixCode = oC4 + 2 * 2 * 4 * kDim * 4;     // [4][kFixCap] int
 constexpr int oFixRg = oFixCode + kNSub * kFixCap * 4;   // [4][kFixCap] float: 1 / gate
 constexpr int oFixVal = oFixRg + kNSub * kFixCap * 4;    // [2][kFixCap] float: exact gradients
-constexpr int oStg = oFixVal + 2 * kFixCap * 4;   // 5 tiles [16][kStgLd] 16-bit
-constexpr int oRaw = oStg + 5 * kSub * kStgLd * 2;   // x, f, q, k, fk, dO raw blocks
+constexpr int oStg = oFixVal + 2 * kFixCap * 4;   // [2 buffers] 5 tiles [16][kStgLd] 16-bit
+constexpr int oRaw = oStg + 2 * kStgBytes;        // x, f, q, k, fk, dO raw blocks
 constexpr int oS0 = oRaw + 6 * kRawBytes;         // start-of-chunk state [64][64] 16-bit
 constexpr int oRe = oS0 + kRawBytes;              // end-of-chunk state gradient [64][64] fp32
 constexpr int kSmem = oRe + kDim * kDim * 4;
-static_assert(kSmem <= 227 * 1024, "shared memory budget");
+static_assert(kSmem + 256 <= 227 * 1024, "shared memory budget");
 static_assert(oRaw % 128 == 0 && oStg % 16 == 0, "alignment of the bulk-copy and staging areas");
 
 // tensor-memory columns.  Lanes A = lanes 0-15 of every quarter, lanes B = lanes 16-31.
 constexpr int cS = 0;        // A: S[0..3] at 64*I;  B: dOt Qt^T of block I+1 at 64*I
 constexpr int cTs = 256;     // A: chain accumulator; afterwards result buffer 1
 constexpr int cRes0 = 320;   // result buffer 0: +0 TQ|TO, +16 T2|T4, +32 T7|T8
-constexpr int cPZ = 384;     // A: P, B: Z (whole chunk); afterwards boundary buffer 1
-constexpr int cDg0 = 448;    // boundary buffer 0: A: R~^T S0, B: S0 R~^T (diagonals used)
+constexpr int cPZ = 384;     // A: P, B: Z (whole chunk)
+
+// named barriers: 1-4 = the four warps of a lane quarter, then
+constexpr int kBarH = 5;     // the helper warps among themselves
+constexpr int kBarA = 6;     // workers -> helpers: tiles of a block published
+constexpr int kBarB = 7;     // (7, 8) workers -> helpers: staging of a block complete
+constexpr int kBarY = 9;     // helpers -> workers: exact path done, earlier staging written out
 
 __device__ __forceinline__ void sync_all() {
   umma::fence_before_sync();
@@ -102,33 +111,53 @@ __device__ __forceinline__ void sync_all() {
   umma::fence_after_sync();
 }
 
+__device__ __forceinline__ void split2(float a, float b, uint32_t &hi, uint32_t &lo) {
+  const __nv_bfloat162 hh = __floats2bfloat162_rn(a, b);
+  const float2 hf = __bfloat1622float2(hh);
+  const __nv_bfloat162 ll = __floats2bfloat162_rn(a - hf.x, b - hf.y);
+  hi = *reinterpret_cast<const uint32_t *>(&hh);
+  lo = *reinterpret_cast<const uint32_t *>(&ll);
+}
+__device__ __forceinline__ float2 join2(uint32_t hi, uint32_t lo) {
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&hi));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&lo));
+  return make_float2(a.x + b.x, a.y + b.y);
+}
 // 8 floats -> 8 bf16 (hi) + 8 bf16 (lo) at the same offset of a hi / lo tile pair (lo at +LO)
 template <int LO>
 __device__ __forceinline__ void write8(unsigned char *th, int off, const float *v) {
   uint4 h, l;
-  uint32_t *hw = reinterpret_cast<uint32_t *>(&h), *lw = reinterpret_cast<uint32_t *>(&l);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const __nv_bfloat162 hh = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-    const float2 hf = __bfloat1622float2(hh);
-    const __nv_bfloat162 ll = __floats2bfloat162_rn(v[2 * j] - hf.x, v[2 * j + 1] - hf.y);
-    hw[j] = *reinterpret_cast<const uint32_t *>(&hh);
-    lw[j] = *reinterpret_cast<const uint32_t *>(&ll);
-  }
+  split2(v[0], v[1], h.x, l.x);
+  split2(v[2], v[3], h.y, l.y);
+  split2(v[4], v[5], h.z, l.z);
+  split2(v[6], v[7], h.w, l.w);
   *reinterpret_cast<uint4 *>(th + off) = h;
   *reinterpret_cast<uint4 *>(th + LO + off) = l;
+}
+// 4 floats -> 4 + 4 bf16 (8-byte stores)
+template <int LO>
+__device__ __forceinline__ void write4(unsigned char *th, int off, const float *v) {
+  uint2 h, l;
+  split2(v[0], v[1], h.x, l.x);
+  split2(v[2], v[3], h.y, l.y);
+  *reinterpret_cast<uint2 *>(th + off) = h;
+  *reinterpret_cast<uint2 *>(th + LO + off) = l;
 }
 __device__ __forceinline__ void read8(const unsigned char *th, int off, float *v) {
   const uint4 h = *reinterpret_cast<const uint4 *>(th + off);
   const uint4 l = *reinterpret_cast<const uint4 *>(th + kTile + off);
-  const __nv_bfloat162 *hp = reinterpret_cast<const __nv_bfloat162 *>(&h);
-  const __nv_bfloat162 *lp = reinterpret_cast<const __nv_bfloat162 *>(&l);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 a = __bfloat1622float2(hp[j]), b = __bfloat1622float2(lp[j]);
-    v[2 * j] = a.x + b.x;
-    v[2 * j + 1] = a.y + b.y;
-  }
+  float2 t;
+  t = join2(h.x, l.x); v[0] = t.x; v[1] = t.y;
+  t = join2(h.y, l.y); v[2] = t.x; v[3] = t.y;
+  t = join2(h.z, l.z); v[4] = t.x; v[5] = t.y;
+  t = join2(h.w, l.w); v[6] = t.x; v[7] = t.y;
+}
+__device__ __forceinline__ void read4(const unsigned char *th, int off, float *v) {
+  const uint2 h = *reinterpret_cast<const uint2 *>(th + off);
+  const uint2 l = *reinterpret_cast<const uint2 *>(th + kTile + off);
+  float2 t;
+  t = join2(h.x, l.x); v[0] = t.x; v[1] = t.y;
+  t = join2(h.y, l.y); v[2] = t.x; v[3] = t.y;
 }
 // one element (hi + lo) of a 64-column tile pair
 __device__ __forceinline__ float rd1(const unsigned char *th, int r, int c) {
@@ -168,8 +197,37 @@ __device__ __forceinline__ void gemm3(uint32_t d, uint32_t a_lo, uint32_t b_lo) 
   }
 }
 
+// producer side of a named barrier: counts this thread without waiting
+__device__ __forceinline__ void bar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(umma::smem_u32(bar)) : "memory");
+}
+
+// sum of a[c] over the 16 lanes of a half warp, for 16 columns c at once: lane fl returns column fl
+__device__ __forceinline__ float colsum16(float (&a)[16], int fl) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const bool up = fl & 8;
+    const float send = up ? a[i] : a[i + 8], keep = up ? a[i + 8] : a[i];
+    a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const bool up = fl & 4;
+    const float send = up ? a[i] : a[i + 4], keep = up ? a[i + 4] : a[i];
+    a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const bool up = fl & 2;
+    const float send = up ? a[i] : a[i + 2], keep = up ? a[i + 2] : a[i];
+    a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+  }
+  const bool up = fl & 1;
+  const float send = up ? a[0] : a[1], keep = up ? a[1] : a[0];
+  return keep + __shfl_xor_sync(0xffffffffu, send, 1);
 }
 
 template <typename T>
@@ -184,22 +242,25 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
   extern __shared__ __align__(128) unsigned char sm[];
   __shared__ __align__(8) uint64_t barM, barRaw;
   __shared__ uint32_t tmem_slot;
-  __shared__ int s_fail, fix_n[kNSub];
+  __shared__ volatile int s_fail;
+  __shared__ int fix_n[kNSub];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qd = warp & 3, half = warp >> 2, side = lane >> 4, fl = lane & 15, feat = 16 * qd + fl;
-  const bool worker = warp < 8, issuer = !worker && lane == 0;
-  const int iw = warp - 8;   // issuer index 0..3
+  const bool worker = warp < 4 * kParts;
+  const int qd = warp & 3, part = (warp >> 2) & 3, side = lane >> 4, fl = lane & 15, feat = 16 * qd + fl;
+  const int hw = warp - 4 * kParts;            // helper index 0..3 (helpers only)
+  const int ht = threadIdx.x - kTW;            // helper thread 0..127 (helpers only)
+  const bool issuer = !worker && lane == 0;
 
   // per-side views: side 0 = k side (gates fk; Qt, Kt), side 1 = d side (gates f; dOt, Xt)
   unsigned char *mulT = sm + (side ? oO : oQ), *divT = sm + (side ? oX : oK);
   float *blk = reinterpret_cast<float *>(sm + (side ? oaI : ogI));
   const float *aI = reinterpret_cast<const float *>(sm + oaI), *gI = reinterpret_cast<const float *>(sm + ogI);
   float *xc = reinterpret_cast<float *>(sm + oXc);
+  float *c4 = reinterpret_cast<float *>(sm + oC4);
   int *fix_code = reinterpret_cast<int *>(sm + oFixCode);
   float *fix_rg = reinterpret_cast<float *>(sm + oFixRg);
   float *fix_val = reinterpret_cast<float *>(sm + oFixVal);
-  T *stg = reinterpret_cast<T *>(sm + oStg);
   const T *raw = reinterpret_cast<const T *>(sm + oRaw);   // [6][64][64]: x, f, q, k, fk, dO
   const T *r_gate = raw + (side ? 1 : 4) * kC * kDim;
   const T *r_mul = raw + (side ? 5 : 2) * kC * kDim;
@@ -225,11 +286,12 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
 
   bool raw_pending = false;   // thread 0: a prefetch has been issued and not yet awaited
   if (threadIdx.x == 0) {
-    umma::mbar_init(&barM, kIssuers);
+    umma::mbar_init(&barM, kHelpers);
     umma::mbar_init(&barRaw, 1);
     umma::mbar_fence_init();
     s_fail = 0;
   }
+  if (threadIdx.x < 2 * kFixCap) fix_val[threadIdx.x] = 0.f;
   if (warp == 0) umma::tmem_alloc(&tmem_slot, 512);
   sync_all();
   const uint32_t tb = tmem_slot;
@@ -245,9 +307,9 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
   const uint32_t dA = tb, dB = umma::tmem_addr(tb, 16, 0);   // lane sets
 
   uint32_t pm = 0, praw = 0;     // mbarrier phase parities
-  // every thread waits for the MMAs of the current round; all issuers arrive once per round
+  // the workers wait for the MMAs of the current round; every helper arrives once per round
   auto wait_mma = [&]() {
-    if (!umma::mbar_wait(&barM, pm)) s_fail = 1;
+    if (!s_fail && !umma::mbar_wait(&barM, pm)) s_fail = 1;   // after a failure: no more waiting
     pm ^= 1u;
     umma::fence_after_sync();
   };
@@ -269,85 +331,86 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
     PROF(1);
 
     // start-of-chunk state (side 0) / end-of-chunk state gradient (side 1): row feat, columns
-    // 32*half .. +31
-    float Rreg[32];   // side 0: S[0] row half (transient); side 1: R~ (persistent over the chunk)
-    float pr[kNSub][8], pp0[kNSub];   // this thread's prefix products, kept for the epilogues
+    // 16*part .. +15
+    float Rreg[16];   // side 0: S[0] row part (transient); side 1: R~ (persistent over the chunk)
+    float pr[kNSub][4], pp0[kNSub];   // this thread's prefix products, kept for the epilogues
     if (worker) {
-    if (side == 0) {
-      const T *Sc = reinterpret_cast<const T *>(sm + oS0) + feat * kDim + 32 * half;
+      if (side == 0) {
+        const uint4 *Sc = reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(sm + oS0) + feat * kDim + 16 * part);
 #pragma unroll
-      for (int j4 = 0; j4 < 4; ++j4) {
-        const uint4 u = *reinterpret_cast<const uint4 *>(Sc + 8 * j4);
-        const T *e = reinterpret_cast<const T *>(&u);
+        for (int j8 = 0; j8 < 2; ++j8) {
+          const uint4 u = Sc[j8];
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) Rreg[8 * j4 + j] = Elem<T>::ld(e + j);
-      }
-    } else {
-      const float *Rc = reinterpret_cast<const float *>(sm + oRe) + feat * kDim + 32 * half;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 v = *reinterpret_cast<const float4 *>(Rc + 4 * j);
-        Rreg[4 * j] = v.x; Rreg[4 * j + 1] = v.y; Rreg[4 * j + 2] = v.z; Rreg[4 * j + 3] = v.w;
-      }
-    }
-    // S[0] into tensor memory (lanes A; lanes B receive values that are never read)
-    umma::tmem_st16(tl + cS + 32 * half, Rreg);
-    umma::tmem_st16(tl + cS + 32 * half + 16, Rreg + 16);
-    umma::tmem_st16(tl + cTs + 32 * half, Rreg);
-    umma::tmem_st16(tl + cTs + 32 * half + 16, Rreg + 16);
-
-    PROF(11);
-    // ---- operand tiles: thread = (side, feature, token half); prefix products restart per block
-    bool out_of_range = false;
-#pragma unroll
-    for (int I = 0; I < kNSub; ++I) {
-      float p = 1.f;
-      const int tbk = kSub * I;
-      if (half) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          p *= sanitize_gate(tbk + j < nvalid ? Elem<T>::ld(r_gate + (tbk + j) * kDim + feat) : 1.f);
-      }
-      pp0[I] = p;
-      const int t0 = tbk + 8 * half;
-      float mv[8], dv[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int t = t0 + j;
-        const bool in = t < nvalid;
-        const float pprev = p;
-        p *= sanitize_gate(in ? Elem<T>::ld(r_gate + t * kDim + feat) : 1.f);
-        pr[I][j] = p;
-        mv[j] = (in ? Elem<T>::ld(r_mul + t * kDim + feat) : 0.f) * p;
-        dv[j] = __fdividef(in ? Elem<T>::ld(r_div + t * kDim + feat) : 0.f, p);
-        if (fabsf(pprev) * kTinyGate > fabsf(p)) {           // |gate| < 2^-10: exact formula later
-          const int slot = atomicAdd(&fix_n[I], 1);
-          if (slot < kFixCap) {
-            fix_code[I * kFixCap + slot] = (side << 16) | ((8 * half + j) << 8) | feat;
-            fix_rg[I * kFixCap + slot] = __fdividef(pprev, p);
-          } else {
-            out_of_range = true;
+          for (int j = 0; j < 4; ++j) {
+            const float2 v = Pair<T>::ld(reinterpret_cast<const T *>(&w[j]));
+            Rreg[8 * j8 + 2 * j] = v.x;
+            Rreg[8 * j8 + 2 * j + 1] = v.y;
           }
         }
-      }
-      // the ratio operands need the sub-block prefix products within [2^-60, 2^60] and the
-      // divided operands below 2^56, so that no product of two of them overflows
-      float plo = fabsf(pr[I][0]), phi = plo, dhi = fabsf(dv[0]);
+      } else {
+        const float *Rc = reinterpret_cast<const float *>(sm + oRe) + feat * kDim + 16 * part;
 #pragma unroll
-      for (int j = 1; j < 8; ++j) {
-        plo = fminf(plo, fabsf(pr[I][j]));
-        phi = fmaxf(phi, fabsf(pr[I][j]));
-        dhi = fmaxf(dhi, fabsf(dv[j]));
+        for (int j = 0; j < 4; ++j) {
+          const float4 v = *reinterpret_cast<const float4 *>(Rc + 4 * j);
+          Rreg[4 * j] = v.x; Rreg[4 * j + 1] = v.y; Rreg[4 * j + 2] = v.z; Rreg[4 * j + 3] = v.w;
+        }
       }
-      out_of_range |= !(plo >= kBlockLo && phi <= kBlockHi && dhi <= kDivHi);
-      const int off = umma::tile16_off(feat, t0, kDim);
-      write8<kTile>(mulT, off, mv);
-      write8<kTile>(divT, off, dv);
-      if (half) blk[I * kDim + feat] = p;
-    }
-    PROF(12);
-    if (out_of_range) atomicExch(rowflag + b, 1);   // the scan kernels redo this batch row
-    umma::tmem_st_wait();
+      // S[0] into tensor memory (lanes A; lanes B receive values that are never read)
+      umma::tmem_st16(tl + cS + 16 * part, Rreg);
+      umma::tmem_st16(tl + cTs + 16 * part, Rreg);
+      PROF(11);
+
+      // ---- operand tiles: thread = (side, feature, step quarter); prefix products restart per block
+      bool out_of_range = false;
+#pragma unroll
+      for (int I = 0; I < kNSub; ++I) {
+        float p = 1.f;
+        const int tbk = kSub * I;
+#pragma unroll
+        for (int j = 0; j < 12; ++j)
+          if (j < 4 * part)      // uniform per warp
+            p *= sanitize_gate(tbk + j < nvalid ? Elem<T>::ld(r_gate + (tbk + j) * kDim + feat) : 1.f);
+        pp0[I] = p;
+        const int t0 = tbk + 4 * part;
+        float mv[4], dv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int t = t0 + j;
+          const bool in = t < nvalid;
+          const float pprev = p;
+          p *= sanitize_gate(in ? Elem<T>::ld(r_gate + t * kDim + feat) : 1.f);
+          pr[I][j] = p;
+          mv[j] = (in ? Elem<T>::ld(r_mul + t * kDim + feat) : 0.f) * p;
+          dv[j] = __fdividef(in ? Elem<T>::ld(r_div + t * kDim + feat) : 0.f, p);
+          if (fabsf(pprev) * kTinyGate > fabsf(p)) {           // |gate| < 2^-10: exact formula later
+            const int slot = atomicAdd(&fix_n[I], 1);
+            if (slot < kFixCap) {
+              fix_code[I * kFixCap + slot] = (side << 16) | ((4 * part + j) << 8) | feat;
+              fix_rg[I * kFixCap + slot] = __fdividef(pprev, p);
+            } else {
+              out_of_range = true;
+            }
+          }
+        }
+        // the ratio operands need the sub-block prefix products within [2^-60, 2^60] and the
+        // divided operands below 2^56, so that no product of two of them overflows
+        float plo = fabsf(pr[I][0]), phi = plo, dhi = fabsf(dv[0]);
+#pragma unroll
+        for (int j = 1; j < 4; ++j) {
+          plo = fminf(plo, fabsf(pr[I][j]));
+          phi = fmaxf(phi, fabsf(pr[I][j]));
+          dhi = fmaxf(dhi, fabsf(dv[j]));
+        }
+        out_of_range |= !(plo >= kBlockLo && phi <= kBlockHi && dhi <= kDivHi);
+        const int off = umma::tile16_off(feat, t0, kDim);
+        write4<kTile>(mulT, off, mv);
+        write4<kTile>(divT, off, dv);
+        if (part == kParts - 1) blk[I * kDim + feat] = p;
+      }
+      PROF(12);
+      if (out_of_range) atomicExch(rowflag + b, 1);   // the scan kernels redo this batch row
+      umma::tmem_st_wait();
     }
     umma::fence_async_smem();
     sync_all();                       // tiles complete; raw blocks, S0 and R_end buffers consumed
@@ -360,30 +423,30 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
     // ---- round 1: P = Qt^T Kt (lanes A), Z = dOt^T Xt (lanes B) for the whole chunk, and the
     //      first link of the state chain: accumulator (= S[0]) += Xt_0 Kt_0^T ------------------
     if (issuer) {
-      if (iw == 0) {
+      if (hw == 0) {
         gemm3<false, false, kDim, kDim, 1, kDim, true>(dA + cTs, dlo<false, kDim>(aX, 0, 0), dlo<false, kDim>(aK, 0, 0));
         gemm3<true, true, kDim, kDim, 4, kDim, false>(dA + cPZ, dlo<true, kDim>(aQ, 0, 0), dlo<true, kDim>(aK, 0, 0));
         umma::mma_commit(&barM);
-      } else if (iw == 1) {
+      } else if (hw == 1) {
         gemm3<true, true, kDim, kDim, 4, kDim, false>(dB + cPZ, dlo<true, kDim>(aO, 0, 0), dlo<true, kDim>(aX, 0, 0));
         umma::mma_commit(&barM);
       } else {
         mbar_arrive(&barM);
       }
     }
-    wait_mma();
+    if (worker) wait_mma();
     sync_all();
     if (s_fail) break;
     PROF(3);
     if (worker) {
-      // diagonal 16 x 16 block of sub-block qd: row fl, columns 8*half .. +7; keep column <= row
-      float v[8];
-      umma::tmem_ld8(tl + cPZ + 16 * qd + 8 * half, v);
+      // diagonal 16 x 16 block of sub-block qd: row fl, columns 4*part .. +3; keep column <= row
+      float v[4];
+      umma::tmem_ld4(tl + cPZ + 16 * qd + 4 * part, v);
       umma::tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = (8 * half + j <= fl) ? v[j] : 0.f;
+      for (int j = 0; j < 4; ++j) v[j] = (4 * part + j <= fl) ? v[j] : 0.f;
       unsigned char *pt = sm + (side ? oZ : oP) + qd * 2 * kTileS;
-      write8<kTileS>(pt, (fl & 7) * 16 + (fl >> 3) * kRGs + half * kCG, v);
+      write4<kTileS>(pt, (fl & 7) * 16 + (fl >> 3) * kRGs + (part >> 1) * kCG + (part & 1) * 8, v);
     }
 
     // ---- forward states at the starts of sub-blocks 1..3 (lanes A), kept in tensor memory -----
@@ -391,8 +454,8 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
     for (int J = 0; J + 1 < kNSub; ++J) {
       if (J > 0) {
         if (issuer) {
-          // chain accumulator += Xt_J Kt_J^T  (contraction over the 16 steps of block J)
-          if (iw == 0) {
+          if (hw == 0) {
+            // chain accumulator += Xt_J Kt_J^T  (contraction over the 16 steps of block J)
             gemm3<false, false, kDim, kDim, 1, kDim, true>(dA + cTs, dlo<false, kDim>(aX, 0, J),
                                                            dlo<false, kDim>(aK, 0, J));
             umma::mma_commit(&barM);
@@ -400,28 +463,23 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
             mbar_arrive(&barM);
           }
         }
-        wait_mma();
+        if (worker) wait_mma();
         sync_all();
         if (s_fail) break;
       }
       if (worker) {
-      float v[32];
-      umma::tmem_ld16(tl + cTs + 32 * half, *reinterpret_cast<float(*)[16]>(v));
-      umma::tmem_ld16(tl + cTs + 32 * half + 16, *reinterpret_cast<float(*)[16]>(v + 16));
-      umma::tmem_ld_wait();
-      const float ar = aI[J * kDim + feat];
+        float v[16];
+        umma::tmem_ld16(tl + cTs + 16 * part, v);
+        umma::tmem_ld_wait();
+        const float ar = aI[J * kDim + feat];
 #pragma unroll
-      for (int j4 = 0; j4 < 8; ++j4) {
-        const float4 g4 = *reinterpret_cast<const float4 *>(gI + J * kDim + 32 * half + 4 * j4);
-        v[4 * j4] *= ar * g4.x; v[4 * j4 + 1] *= ar * g4.y; v[4 * j4 + 2] *= ar * g4.z; v[4 * j4 + 3] *= ar * g4.w;
-      }
-      umma::tmem_st16(tl + cS + 64 * (J + 1) + 32 * half, v);
-      umma::tmem_st16(tl + cS + 64 * (J + 1) + 32 * half + 16, v + 16);
-      if (J + 2 < kNSub) {
-        umma::tmem_st16(tl + cTs + 32 * half, v);
-        umma::tmem_st16(tl + cTs + 32 * half + 16, v + 16);
-      }
-      umma::tmem_st_wait();
+        for (int j4 = 0; j4 < 4; ++j4) {
+          const float4 g4 = *reinterpret_cast<const float4 *>(gI + J * kDim + 16 * part + 4 * j4);
+          v[4 * j4] *= ar * g4.x; v[4 * j4 + 1] *= ar * g4.y; v[4 * j4 + 2] *= ar * g4.z; v[4 * j4 + 3] *= ar * g4.w;
+        }
+        umma::tmem_st16(tl + cS + 64 * (J + 1) + 16 * part, v);
+        if (J + 2 < kNSub) umma::tmem_st16(tl + cTs + 16 * part, v);
+        umma::tmem_st_wait();
       }
       umma::fence_async_smem();      // (J == 0: the P / Z diagonal blocks written above)
       sync_all();
@@ -429,23 +487,31 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
     if (s_fail) break;
     PROF(4);
 
-    // ---- the four sub-blocks in reverse, software-pipelined: iteration I publishes the S0 / R~
-    //      tiles of block I and issues its MMAs, then finishes block I+1 while they run ----------
+    // ---- the four sub-blocks in reverse, software-pipelined with producer / consumer barriers:
+    //   workers, iteration I: [Y] publish S0 / R~ tiles of block I (A) epilogue of block I+1 (B) wait MMAs(I)
+    //   helpers, iteration I: (A) issue MMAs(I), exact path of block I [Y] (B) patch + write-out of block I+1
+    //   (A), (B): workers arrive, helpers wait.  [Y]: helpers arrive, workers wait - the tiles of
+    //   the previous block are no longer read and the staging buffer of block I+1 has been written out.
 #pragma unroll 1
     for (int I = kNSub - 1; I >= -1; --I) {
-      if (I >= 0) {
-        const int r0 = kSub * I;
-        if (worker) {
+      const int r0 = kSub * (I < 0 ? 0 : I);
+      const int J = I + 1;      // the block whose results are finished in this iteration
+      T *stg = reinterpret_cast<T *>(sm + oStg + (J & 1) * kStgBytes);
+      if (worker) {
+        if (I < kNSub - 1) {
+          umma::named_barrier(kBarY, kTAll);
+          umma::fence_after_sync();
+        }
+        if (I >= 0) {
           // lanes A: S[I];  lanes B: dOt Qt^T of block I+1 (the part of R that block added)
-          float v[32];
-          umma::tmem_ld16(tl + cS + 64 * I + 32 * half, *reinterpret_cast<float(*)[16]>(v));
-          umma::tmem_ld16(tl + cS + 64 * I + 32 * half + 16, *reinterpret_cast<float(*)[16]>(v + 16));
+          float v[16];
+          umma::tmem_ld16(tl + cS + 64 * I + 16 * part, v);
           umma::tmem_ld_wait();
           if (side) {
             const float ar = aI[I * kDim + feat];
 #pragma unroll
-            for (int j4 = 0; j4 < 8; ++j4) {
-              const float4 g4 = *reinterpret_cast<const float4 *>(gI + I * kDim + 32 * half + 4 * j4);
+            for (int j4 = 0; j4 < 4; ++j4) {
+              const float4 g4 = *reinterpret_cast<const float4 *>(gI + I * kDim + 16 * part + 4 * j4);
               const float gg[4] = {g4.x, g4.y, g4.z, g4.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
@@ -457,117 +523,47 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
             }
           }
           unsigned char *th = sm + (side ? oR : oS);
+          write8<kTile>(th, umma::tile16_off(feat, 16 * part, kDim), v);
+          write8<kTile>(th, umma::tile16_off(feat, 16 * part + 8, kDim), v + 8);
+          // boundary terms sum_d R~ .* S0 (k side) and sum_k R~ .* S0 (d side): the two half warps
+          // exchange their rows (same feature row, same columns), partial sums go to shared memory
+          float pd[16], rowsum = 0.f;
 #pragma unroll
-          for (int j8 = 0; j8 < 4; ++j8)
-            write8<kTile>(th, umma::tile16_off(feat, 32 * half + 8 * j8, kDim), v + 8 * j8);
+          for (int j = 0; j < 16; ++j) {
+            pd[j] = v[j] * __shfl_xor_sync(0xffffffffu, v[j], 16);
+            rowsum += pd[j];
+          }
+          const float colsum = colsum16(pd, fl);
+          float *c4b = c4 + (I & 1) * 2 * 4 * kDim;
+          if (side) c4b[4 * kDim + part * kDim + feat] = rowsum;       // d side: [part][d]
+          else c4b[qd * kDim + 16 * part + fl] = colsum;               // k side: [qd][k]
+          umma::fence_async_smem();
+          umma::fence_before_sync();
+          __threadfence_block();
+          bar_arrive(kBarA, kTAll);
         }
-        umma::fence_async_smem();
-        sync_all();
         PROF(5);
-        if (issuer) {
-          const int cres = (I & 1) ? cTs : cRes0, cdg = (I & 1) ? cPZ : cDg0;
-          const uint32_t zI = aZ + I * 2 * kTileS, pI = aP + I * 2 * kTileS;
-          if (iw == 0) {
-            // dOt Qt^T of this block first: the next (earlier) sub-block needs it soonest
-            if (I > 0)
-              gemm3<false, false, kDim, kDim, 1, kDim, false>(dB + cS + 64 * (I - 1), dlo<false, kDim>(aO, 0, I),
-                                                              dlo<false, kDim>(aQ, 0, I));
-            // TQ = S0^T dOt + Kt Z^T ;  T2 = Qt Z
-            gemm3<true, true, kDim, kDim, 4, kSub, false>(dA + cres, dlo<true, kDim>(aS, 0, 0), dlo<true, kDim>(aO, r0, 0));
-            gemm3<false, false, kDim, kSub, 1, kSub, true>(dA + cres, dlo<false, kDim>(aK, 0, I), dlo<false, kSub>(zI, 0, 0));
-            gemm3<false, true, kDim, kSub, 1, kSub, false>(dA + cres + 16, dlo<false, kDim>(aQ, 0, I), dlo<true, kSub>(zI, 0, 0));
-          } else if (iw == 1) {
-            // T7 = R~^T Xt ;  diag(R~^T S0): boundary term of the k side
-            gemm3<true, true, kDim, kDim, 4, kSub, false>(dA + cres + 32, dlo<true, kDim>(aR, 0, 0), dlo<true, kDim>(aX, r0, 0));
-            gemm3<true, true, kDim, kDim, 4, kDim, false>(dA + cdg, dlo<true, kDim>(aR, 0, 0), dlo<true, kDim>(aS, 0, 0));
-          } else if (iw == 2) {
-            // TO = S0 Qt + Xt P^T ;  T4 = dOt P
-            gemm3<false, true, kDim, kDim, 4, kSub, false>(dB + cres, dlo<false, kDim>(aS, 0, 0), dlo<true, kDim>(aQ, r0, 0));
-            gemm3<false, false, kDim, kSub, 1, kSub, true>(dB + cres, dlo<false, kDim>(aX, 0, I), dlo<false, kSub>(pI, 0, 0));
-            gemm3<false, true, kDim, kSub, 1, kSub, false>(dB + cres + 16, dlo<false, kDim>(aO, 0, I), dlo<true, kSub>(pI, 0, 0));
-          } else {
-            // T8 = R~ Kt ;  diag(S0 R~^T): boundary term of the d side
-            gemm3<false, true, kDim, kDim, 4, kSub, false>(dB + cres + 32, dlo<false, kDim>(aR, 0, 0), dlo<true, kDim>(aK, r0, 0));
-            gemm3<false, false, kDim, kDim, 4, kDim, false>(dB + cdg, dlo<false, kDim>(aS, 0, 0), dlo<false, kDim>(aR, 0, 0));
-          }
-          umma::mma_commit(&barM);
-        }
-        PROF(6);
-
-        // ---- exact gate gradients of block I where the gate is too small for the cancelling
-        //      form (needs only the tiles, so it runs under the MMAs):
-        //   dg_t[k] = (1/g_t) sum_d M[d] N[d],  M = S0[d][k] + sum_{i<t} Xt_i[d] Kt_i[k],
-        //                                       N = R~[d][k] + sum_{s>=t} dOt_s[d] Qt_s[k]
-        if (worker) {
-          const int n_fix = fix_n[I] < kFixCap ? fix_n[I] : kFixCap;
-          for (int e = warp; e < n_fix; e += kT / 32) {
-            const int code = fix_code[I * kFixCap + e];
-            const int ds = code >> 16, t = (code >> 8) & 0xff, col = code & 0xff;
-            // k-side entry: the fixed feature is a column of S0 / R~, X and dO rows vary with the
-            // lane, the K and Q rows of the fixed feature are shared; d side: roles exchanged
-            const unsigned char *var1 = sm + (ds ? oK : oX), *var2 = sm + (ds ? oQ : oO);
-            const unsigned char *fix1 = sm + (ds ? oX : oK), *fix2 = sm + (ds ? oO : oQ);
-            float b1[16], b2[16];
-            read8(fix1, umma::tile16_off(col, r0, kDim), b1);
-            read8(fix1, umma::tile16_off(col, r0 + 8, kDim), b1 + 8);
-            read8(fix2, umma::tile16_off(col, r0, kDim), b2);
-            read8(fix2, umma::tile16_off(col, r0 + 8, kDim), b2 + 8);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              b1[i] = (i < t) ? b1[i] : 0.f;
-              b2[i] = (i >= t) ? b2[i] : 0.f;
-            }
-            float acc = 0.f;
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              const int o = lane + 32 * j;
-              float a1[16], a2[16];
-              read8(var1, umma::tile16_off(o, r0, kDim), a1);
-              read8(var1, umma::tile16_off(o, r0 + 8, kDim), a1 + 8);
-              read8(var2, umma::tile16_off(o, r0, kDim), a2);
-              read8(var2, umma::tile16_off(o, r0 + 8, kDim), a2 + 8);
-              float M = ds ? rd1(sm + oS, col, o) : rd1(sm + oS, o, col);
-              float N = ds ? rd1(sm + oR, col, o) : rd1(sm + oR, o, col);
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                M = fmaf(a1[i], b1[i], M);
-                N = fmaf(a2[i], b2[i], N);
-              }
-              acc = fmaf(M, N, acc);
-            }
-            acc = warp_sum(acc);
-            if (lane == 0) fix_val[(I & 1) * kFixCap + e] = acc * fix_rg[I * kFixCap + e];
-          }
-        }
-        PROF(7);
-      }
-
-      if (I < kNSub - 1) {
-        // ---- feature-major epilogue of block J = I + 1: this thread = one feature, 8 steps -------
-        const int J = I + 1, r0 = kSub * J;
-        const int cres = (J & 1) ? cTs : cRes0, cdg = (J & 1) ? cPZ : cDg0;
-        if (worker) {
-          float r0v[8], r1v[8], r2v[8], dg[16];
-          umma::tmem_ld8(tl + cres + 8 * half, r0v);
-          umma::tmem_ld8(tl + cres + 16 + 8 * half, r1v);
-          umma::tmem_ld8(tl + cres + 32 + 8 * half, r2v);
-          umma::tmem_ld16(tl + cdg + 16 * qd, dg);
-          umma::tmem_ld_wait();
-          float c4 = 0.f;
-#pragma unroll
-          for (int e = 0; e < 16; ++e) c4 = (e == fl) ? dg[e] : c4;
-
-          const int t0 = r0 + 8 * half;
-          float mr[8], dr[8], p[8];
+        if (I < kNSub - 1) {
+          // ---- feature-major epilogue of block J: this thread = one feature, 4 steps -------------
+          const int cres = (J & 1) ? cTs : cRes0;
+          float r0v[4], r1v[4], r2v[4];
+          umma::tmem_ld4(tl + cres + 4 * part, r0v);
+          umma::tmem_ld4(tl + cres + 16 + 4 * part, r1v);
+          umma::tmem_ld4(tl + cres + 32 + 4 * part, r2v);
+          const float *c4b = c4 + (J & 1) * 2 * 4 * kDim + (side ? 4 * kDim : 0) + feat;
+          const float bnd = (c4b[0] + c4b[kDim]) + (c4b[2 * kDim] + c4b[3 * kDim]);
+          const int t0 = kSub * J + 4 * part;
+          float mr[4], dr[4], p[4];
           const int off = umma::tile16_off(feat, t0, kDim);
-          read8(mulT, off, mr);
-          read8(divT, off, dr);
+          read4(mulT, off, mr);
+          read4(divT, off, dr);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) p[j] = J == 0 ? pr[0][j] : J == 1 ? pr[1][j] : J == 2 ? pr[2][j] : pr[3][j];
+          for (int j = 0; j < 4; ++j) p[j] = J == 0 ? pr[0][j] : J == 1 ? pr[1][j] : J == 2 ? pr[2][j] : pr[3][j];
           const float pprev0 = J == 0 ? pp0[0] : J == 1 ? pp0[1] : J == 2 ? pp0[2] : pp0[3];
-          float o1[8], o2[8], rg[8], V[8], B3[8], pre[8];
+          umma::tmem_ld_wait();
+          float o1[4], o2[4], rg[4], V[4], B3[4], pre[4];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < 4; ++j) {
             o1[j] = p[j] * r0v[j];
             rg[j] = __fdividef(1.f, p[j]);
             o2[j] = (r1v[j] + r2v[j]) * rg[j];
@@ -575,57 +571,131 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
             B3[j] = dr[j] * r2v[j];
           }
 #pragma unroll
-          for (int j = 6; j >= 0; --j) V[j] += V[j + 1];          // inclusive suffix over my 8 steps
+          for (int j = 2; j >= 0; --j) V[j] += V[j + 1];          // inclusive suffix over my 4 steps
           float run = 0.f;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) { pre[j] = run; run += B3[j]; }   // exclusive prefix
+          for (int j = 0; j < 4; ++j) { pre[j] = run; run += B3[j]; }   // exclusive prefix
           xc[threadIdx.x] = V[0];
-          xc[kT + threadIdx.x] = run;
-          umma::named_barrier(1 + qd, 64);       // the two warps that share this feature quarter
-          const float oV = xc[threadIdx.x ^ 128], oB = xc[kT + (threadIdx.x ^ 128)];
-          const float addV = half ? 0.f : oV;    // steps 8..15 lie after steps 0..7
-          const float addB = half ? oB : 0.f;
+          xc[kTW + threadIdx.x] = run;
+          umma::named_barrier(1 + qd, 32 * kParts);   // the four warps that share this lane quarter
+          float addV = 0.f, addB = 0.f;
+#pragma unroll
+          for (int pp = 0; pp < kParts; ++pp) {
+            const int o = (pp * 4 + qd) * 32 + lane;
+            const float tv = xc[o], tbv = xc[kTW + o];
+            addV += (pp > part) ? tv : 0.f;          // later steps
+            addB += (pp < part) ? tbv : 0.f;         // earlier steps
+          }
           T *s1 = stg + (side ? 3 : 1) * kSub * kStgLd, *s2 = stg + (side ? 4 : 2) * kSub * kStgLd;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float H = V[j] + addV + pre[j] + addB + c4;
+          for (int j = 0; j < 4; ++j) {
+            const float H = V[j] + addV + pre[j] + addB + bnd;
             const float pprev = j ? p[j - 1] : pprev0;
-            const int lr = 8 * half + j;
+            const int lr = 4 * part + j;
             if (!side) stg[lr * kStgLd + feat] = (T)o1[j];
             s1[lr * kStgLd + feat] = (T)o2[j];
             s2[lr * kStgLd + feat] = (T)(H * pprev * rg[j]);
           }
+          umma::fence_before_sync();
+          __threadfence_block();
+          bar_arrive(kBarB + (I & 1), kTAll);
         }
-        sync_all();     // staging complete
-        PROF(8);
-        const int n_fix = fix_n[J] < kFixCap ? fix_n[J] : kFixCap;
-        if (n_fix > 0) {
-          if (threadIdx.x < n_fix) {
-            const int code = fix_code[J * kFixCap + threadIdx.x];
-            const int ds = code >> 16, t = (code >> 8) & 0xff, col = code & 0xff;
-            stg[((ds ? 4 : 2) * kSub + t) * kStgLd + col] = (T)fix_val[(J & 1) * kFixCap + threadIdx.x];
+        PROF(6);
+        if (I >= 0) wait_mma();     // the MMAs of block I
+        PROF(7);
+      } else {
+        if (I >= 0) {
+          umma::named_barrier(kBarA, kTAll);
+          umma::fence_after_sync();
+          if (lane == 0) {
+            const int cres = (I & 1) ? cTs : cRes0;
+            const uint32_t zI = aZ + I * 2 * kTileS, pI = aP + I * 2 * kTileS;
+            if (hw == 0) {
+              // dOt Qt^T of this block first: the next (earlier) sub-block needs it soonest
+              if (I > 0)
+                gemm3<false, false, kDim, kDim, 1, kDim, false>(dB + cS + 64 * (I - 1), dlo<false, kDim>(aO, 0, I),
+                                                                dlo<false, kDim>(aQ, 0, I));
+              // TQ = S0^T dOt + Kt Z^T
+              gemm3<true, true, kDim, kDim, 4, kSub, false>(dA + cres, dlo<true, kDim>(aS, 0, 0), dlo<true, kDim>(aO, r0, 0));
+              gemm3<false, false, kDim, kSub, 1, kSub, true>(dA + cres, dlo<false, kDim>(aK, 0, I), dlo<false, kSub>(zI, 0, 0));
+            } else if (hw == 1) {
+              // T7 = R~^T Xt ;  T2 = Qt Z
+              gemm3<true, true, kDim, kDim, 4, kSub, false>(dA + cres + 32, dlo<true, kDim>(aR, 0, 0), dlo<true, kDim>(aX, r0, 0));
+              gemm3<false, true, kDim, kSub, 1, kSub, false>(dA + cres + 16, dlo<false, kDim>(aQ, 0, I), dlo<true, kSub>(zI, 0, 0));
+            } else if (hw == 2) {
+              // TO = S0 Qt + Xt P^T
+              gemm3<false, true, kDim, kDim, 4, kSub, false>(dB + cres, dlo<false, kDim>(aS, 0, 0), dlo<true, kDim>(aQ, r0, 0));
+              gemm3<false, false, kDim, kSub, 1, kSub, true>(dB + cres, dlo<false, kDim>(aX, 0, I), dlo<false, kSub>(pI, 0, 0));
+            } else {
+              // T8 = R~ Kt ;  T4 = dOt P
+              gemm3<false, true, kDim, kDim, 4, kSub, false>(dB + cres + 32, dlo<false, kDim>(aR, 0, 0), dlo<true, kDim>(aK, r0, 0));
+              gemm3<false, true, kDim, kSub, 1, kSub, false>(dB + cres + 16, dlo<false, kDim>(aO, 0, I), dlo<true, kSub>(pI, 0, 0));
+            }
+            umma::mma_commit(&barM);
           }
-          __syncthreads();
+          __syncwarp();
+
+          // ---- exact gate gradients of block I where the gate is too small for the cancelling
+          //      form (needs only the tiles, so it runs under the MMAs):
+          //   dg_t[k] = (1/g_t) sum_d M[d] N[d],  M = S0[d][k] + sum_{i<t} Xt_i[d] Kt_i[k],
+          //                                       N = R~[d][k] + sum_{s>=t} dOt_s[d] Qt_s[k]
+          // every entry is spread over the four helper warps: 16 values of d per warp, M in the
+          // lower half warp and N in the upper one
+          const int n_fix = fix_n[I] < kFixCap ? fix_n[I] : kFixCap;
+          for (int e = 0; e < n_fix; ++e) {
+            const int code = fix_code[I * kFixCap + e];
+            const int ds = code >> 16, t = (code >> 8) & 0xff, col = code & 0xff;
+            const int o = 16 * hw + (lane & 15), wh = lane >> 4;
+            // k-side entry: the fixed feature is a column of S0 / R~, the X / dO rows vary with
+            // the lane, the K / Q row of the fixed feature is shared; d side: roles exchanged
+            const unsigned char *var = sm + (wh ? (ds ? oQ : oO) : (ds ? oK : oX));
+            const unsigned char *fix = sm + (wh ? (ds ? oO : oQ) : (ds ? oX : oK));
+            const unsigned char *st0 = sm + (wh ? oR : oS);
+            float val = ds ? rd1(st0, col, o) : rd1(st0, o, col);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              float a[8], bb[8];
+              read8(var, umma::tile16_off(o, r0 + 8 * h, kDim), a);
+              read8(fix, umma::tile16_off(col, r0 + 8 * h, kDim), bb);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const bool use = wh ? (8 * h + i >= t) : (8 * h + i < t);
+                val = fmaf(a[i], use ? bb[i] : 0.f, val);
+              }
+            }
+            float mn = val * __shfl_xor_sync(0xffffffffu, val, 16);
+#pragma unroll
+            for (int sft = 8; sft > 0; sft >>= 1) mn += __shfl_xor_sync(0xffffffffu, mn, sft);
+            if (lane == 0) atomicAdd(&fix_val[(I & 1) * kFixCap + e], mn);
+          }
+          __threadfence_block();
+          bar_arrive(kBarY, kTAll);
         }
-        // ---- coalesced write of the five 16 x 64 result tiles ----------------------------------
-        if (worker) {
+        if (I < kNSub - 1) {
+          umma::named_barrier(kBarB + (I & 1), kTAll);
+          const int n_fix = fix_n[J] < kFixCap ? fix_n[J] : kFixCap;
+          if (ht < n_fix) {
+            const int code = fix_code[J * kFixCap + ht];
+            const int ds = code >> 16, t = (code >> 8) & 0xff, col = code & 0xff;
+            stg[((ds ? 4 : 2) * kSub + t) * kStgLd + col] =
+                (T)(fix_val[(J & 1) * kFixCap + ht] * fix_rg[J * kFixCap + ht]);
+            fix_val[(J & 1) * kFixCap + ht] = 0.f;      // ready for the next accumulation
+          }
+          if (n_fix > 0) umma::named_barrier(kBarH, 32 * kHelpers);
+          // ---- coalesced write of the five 16 x 64 result tiles --------------------------------
           T *dst[5] = {dq, dk, dfk, dx, df};
-          for (int idx = threadIdx.x; idx < 5 * kSub * 8; idx += kT) {
+          const int rJ = kSub * J;
+          for (int idx = ht; idx < 5 * kSub * 8; idx += 32 * kHelpers) {
             const int it = idx >> 7, r = (idx >> 3) & 15, ch = idx & 7;
-            if (r0 + r < nvalid) {
+            if (rJ + r < nvalid) {
               const uint4 val = *reinterpret_cast<const uint4 *>(stg + (it * kSub + r) * kStgLd + ch * 8);
-              *reinterpret_cast<uint4 *>(dst[it] + base + (size_t)(r0 + r) * kDim + ch * 8) = val;
+              *reinterpret_cast<uint4 *>(dst[it] + base + (size_t)(rJ + r) * kDim + ch * 8) = val;
             }
           }
         }
-        PROF(9);
       }
-
-      if (I >= 0) wait_mma();     // the MMAs of block I
-      sync_all();                 // also: everything of block I+1 consumed
-      PROF(10);
-      if (s_fail) break;
     }
+    sync_all();     // the helpers have written the last block out; nothing of this chunk is in use
     if (s_fail) break;
   }
   if (s_fail && threadIdx.x == 0) {
@@ -664,7 +734,7 @@ int lfw_chunk_bwd_main_umma(const void *go, const void *x, const void *f, const 
   do {                                                                                                \
     T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_chunk_bwd_umma_kernel<TT>,                               \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));        \
-    lfw_chunk_bwd_umma_kernel<TT><<<grid, kTAll, kSmem, st>>>(                                           \
+    lfw_chunk_bwd_umma_kernel<TT><<<grid, kTAll, kSmem, st>>>(                                        \
         (const TT *)go, (const TT *)x, (const TT *)f, (const TT *)q, (const TT *)k, (const TT *)fk,   \
         (const TT *)state, (const TT *)ckpt, Rend, (TT *)dx, (TT *)df, (TT *)dq, (TT *)dk, (TT *)dfk, \
         rowflag, status, T_, nc, total);                                                              \

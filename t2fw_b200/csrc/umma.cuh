@@ -184,6 +184,15 @@ __device__ __forceinline__ void tmem_ld8(uint32_t addr, float (&v)[8]) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_ld4(uint32_t addr, float (&v)[4]) {
+  uint32_t r[4];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr)
+               : "memory");
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(r[i]);
+}
 // accumulator stores: thread i of the warp writes lane (lane field of addr) + i, 16 columns
 __device__ __forceinline__ void tmem_st16(uint32_t addr, const float *v) {
   asm volatile(
