@@ -52,8 +52,17 @@ __device__ long long g_prof[32];
       tprev = now_;                                                \
     }                                                              \
   } while (0)
+#define PROFH(i)                                                   \
+  do {                                                             \
+    if (threadIdx.x == 512 && blockIdx.x == 0) {                   \
+      const long long now_ = clock64();                            \
+      g_prof[16 + i] += now_ - hprev;                              \
+      hprev = now_;                                                \
+    }                                                              \
+  } while (0)
 #else
 #define PROF(i) do { } while (0)
+#define PROFH(i) do { } while (0)
 #endif
 
 namespace {
@@ -87,15 +96,14 @@ constexpr int oFixRg = oFixCode + kNSub * kFixCap * 4;   // [4][kFixCap] float: 
 constexpr int oFixVal = oFixRg + kNSub * kFixCap * 4;    // [2][kFixCap] float: exact gradients
 constexpr int oStg = oFixVal + 2 * kFixCap * 4;   // [2 buffers] 5 tiles [16][kStgLd] 16-bit
 constexpr int oRaw = oStg + 2 * kStgBytes;        // x, f, q, k, fk, dO raw blocks
-constexpr int oS0 = oRaw + 6 * kRawBytes;         // start-of-chunk state [64][64] 16-bit
-constexpr int oRe = oS0 + kRawBytes;              // end-of-chunk state gradient [64][64] fp32
-constexpr int kSmem = oRe + kDim * kDim * 4;
+constexpr int kSmem = oRaw + 6 * kRawBytes;
 static_assert(kSmem + 256 <= 227 * 1024, "shared memory budget");
 static_assert(oRaw % 128 == 0 && oStg % 16 == 0, "alignment of the bulk-copy and staging areas");
 
 // tensor-memory columns.  Lanes A = lanes 0-15 of every quarter, lanes B = lanes 16-31.
-constexpr int cS = 0;        // A: S[0..3] at 64*I;  B: dOt Qt^T of block I+1 at 64*I
-constexpr int cTs = 256;     // A: chain accumulator; afterwards result buffer 1
+constexpr int cS = 0;        // A: S[0..3] at 64*I (1..3 first hold Xt Kt^T of the block before);
+                             // B: dOt Qt^T of block I+1 at 64*I
+constexpr int cTs = 256;     // result buffer 1
 constexpr int cRes0 = 320;   // result buffer 0: +0 TQ|TO, +16 T2|T4, +32 T7|T8
 constexpr int cPZ = 384;     // A: P, B: Z (whole chunk)
 
@@ -271,17 +279,14 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
     const int nv = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
     const uint32_t vb = (uint32_t)nv * kDim * sizeof(T);
     const size_t base = ((size_t)b * T_ + t0) * kDim;
-    const T *s0 = (c == 0) ? state + (size_t)b * kDim * kDim : ckpt + ((size_t)b * nc + (c - 1)) * kDim * kDim;
     unsigned char *r = sm + oRaw;
-    acp::mbar_expect_tx(&barRaw, 6 * vb + kRawBytes + kDim * kDim * 4);
+    acp::mbar_expect_tx(&barRaw, 6 * vb);
     acp::bulk_g2s(r, x + base, vb, &barRaw);
     acp::bulk_g2s(r + kRawBytes, f + base, vb, &barRaw);
     acp::bulk_g2s(r + 2 * kRawBytes, q + base, vb, &barRaw);
     acp::bulk_g2s(r + 3 * kRawBytes, k + base, vb, &barRaw);
     acp::bulk_g2s(r + 4 * kRawBytes, fk + base, vb, &barRaw);
     acp::bulk_g2s(r + 5 * kRawBytes, go + base, vb, &barRaw);
-    acp::bulk_g2s(sm + oS0, s0, kRawBytes, &barRaw);
-    acp::bulk_g2s(sm + oRe, Rend + (size_t)ci * kDim * kDim, kDim * kDim * 4, &barRaw);
   };
 
   bool raw_pending = false;   // thread 0: a prefetch has been issued and not yet awaited
@@ -314,8 +319,33 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
     umma::fence_after_sync();
   };
 
+  // Row `feat`, columns 16*part .. +15 of the start-of-chunk state (side 0; 16 packed 16-bit
+  // values in the first 8 words) or of the end-of-chunk state gradient (side 1; 16 floats), as
+  // raw bits.  Requested one chunk ahead, while R is not live, so the latency is hidden.
+  float Rreg[16];   // side 0: S[0] row part (transient); side 1: R~ (persistent over the chunk)
+  auto prefetch_rows = [&](int64_t ci) {
+    const int64_t b = ci / nc, c = ci % nc;
+    if (side == 0) {
+      const T *s0 = (c == 0) ? state + (size_t)b * kDim * kDim : ckpt + ((size_t)b * nc + (c - 1)) * kDim * kDim;
+      const uint4 *src = reinterpret_cast<const uint4 *>(s0 + feat * kDim + 16 * part);
+      const uint4 u0 = src[0], u1 = src[1];
+      Rreg[0] = __uint_as_float(u0.x); Rreg[1] = __uint_as_float(u0.y);
+      Rreg[2] = __uint_as_float(u0.z); Rreg[3] = __uint_as_float(u0.w);
+      Rreg[4] = __uint_as_float(u1.x); Rreg[5] = __uint_as_float(u1.y);
+      Rreg[6] = __uint_as_float(u1.z); Rreg[7] = __uint_as_float(u1.w);
+    } else {
+      const float4 *src = reinterpret_cast<const float4 *>(Rend + (size_t)ci * kDim * kDim + feat * kDim + 16 * part);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 v = src[j];
+        Rreg[4 * j] = v.x; Rreg[4 * j + 1] = v.y; Rreg[4 * j + 2] = v.z; Rreg[4 * j + 3] = v.w;
+      }
+    }
+  };
+  if (worker && (int64_t)blockIdx.x < total) prefetch_rows(blockIdx.x);
+
 #ifdef T2FW_BWD_PROFILE
-  long long tprev = clock64();
+  long long tprev = clock64(), hprev = tprev;
 #endif
   for (int64_t ci = blockIdx.x; ci < total; ci += gridDim.x) {
     const int64_t b = ci / nc, c = ci % nc, t0c = c * kC;
@@ -332,33 +362,19 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
 
     // start-of-chunk state (side 0) / end-of-chunk state gradient (side 1): row feat, columns
     // 16*part .. +15
-    float Rreg[16];   // side 0: S[0] row part (transient); side 1: R~ (persistent over the chunk)
     float pr[kNSub][4], pp0[kNSub];   // this thread's prefix products, kept for the epilogues
     if (worker) {
-      if (side == 0) {
-        const uint4 *Sc = reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(sm + oS0) + feat * kDim + 16 * part);
+      if (side == 0) {     // unpack the 16 prefetched 16-bit values, last word first
 #pragma unroll
-        for (int j8 = 0; j8 < 2; ++j8) {
-          const uint4 u = Sc[j8];
-          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 v = Pair<T>::ld(reinterpret_cast<const T *>(&w[j]));
-            Rreg[8 * j8 + 2 * j] = v.x;
-            Rreg[8 * j8 + 2 * j + 1] = v.y;
-          }
-        }
-      } else {
-        const float *Rc = reinterpret_cast<const float *>(sm + oRe) + feat * kDim + 16 * part;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float4 v = *reinterpret_cast<const float4 *>(Rc + 4 * j);
-          Rreg[4 * j] = v.x; Rreg[4 * j + 1] = v.y; Rreg[4 * j + 2] = v.z; Rreg[4 * j + 3] = v.w;
+        for (int j = 7; j >= 0; --j) {
+          const uint32_t w = __float_as_uint(Rreg[j]);
+          const float2 v = Pair<T>::ld(reinterpret_cast<const T *>(&w));
+          Rreg[2 * j] = v.x;
+          Rreg[2 * j + 1] = v.y;
         }
       }
       // S[0] into tensor memory (lanes A; lanes B receive values that are never read)
       umma::tmem_st16(tl + cS + 16 * part, Rreg);
-      umma::tmem_st16(tl + cTs + 16 * part, Rreg);
       PROF(11);
 
       // ---- operand tiles: thread = (side, feature, step quarter); prefix products restart per block
@@ -421,18 +437,19 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
     PROF(2);
 
     // ---- round 1: P = Qt^T Kt (lanes A), Z = dOt^T Xt (lanes B) for the whole chunk, and the
-    //      first link of the state chain: accumulator (= S[0]) += Xt_0 Kt_0^T ------------------
+    //      local state increments U_J = Xt_J Kt_J^T of blocks 0..2 into the slots of S[1..3] --------
     if (issuer) {
       if (hw == 0) {
-        gemm3<false, false, kDim, kDim, 1, kDim, true>(dA + cTs, dlo<false, kDim>(aX, 0, 0), dlo<false, kDim>(aK, 0, 0));
         gemm3<true, true, kDim, kDim, 4, kDim, false>(dA + cPZ, dlo<true, kDim>(aQ, 0, 0), dlo<true, kDim>(aK, 0, 0));
-        umma::mma_commit(&barM);
       } else if (hw == 1) {
         gemm3<true, true, kDim, kDim, 4, kDim, false>(dB + cPZ, dlo<true, kDim>(aO, 0, 0), dlo<true, kDim>(aX, 0, 0));
-        umma::mma_commit(&barM);
+      } else if (hw == 2) {
+        gemm3<false, false, kDim, kDim, 1, kDim, false>(dA + cS + 64, dlo<false, kDim>(aX, 0, 0), dlo<false, kDim>(aK, 0, 0));
+        gemm3<false, false, kDim, kDim, 1, kDim, false>(dA + cS + 128, dlo<false, kDim>(aX, 0, 1), dlo<false, kDim>(aK, 0, 1));
       } else {
-        mbar_arrive(&barM);
+        gemm3<false, false, kDim, kDim, 1, kDim, false>(dA + cS + 192, dlo<false, kDim>(aX, 0, 2), dlo<false, kDim>(aK, 0, 2));
       }
+      umma::mma_commit(&barM);
     }
     if (worker) wait_mma();
     sync_all();
@@ -442,48 +459,34 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
       // diagonal 16 x 16 block of sub-block qd: row fl, columns 4*part .. +3; keep column <= row
       float v[4];
       umma::tmem_ld4(tl + cPZ + 16 * qd + 4 * part, v);
+      // forward states at the starts of sub-blocks 1..3 (lanes A), kept in tensor memory:
+      // S[J+1] = decay_J .* (S[J] + U_J); lanes B compute on values that are never read
+      float u0[16], u1[16], u2[16], sv[16];
+      umma::tmem_ld16(tl + cS + 64 + 16 * part, u0);
+      umma::tmem_ld16(tl + cS + 128 + 16 * part, u1);
+      umma::tmem_ld16(tl + cS + 192 + 16 * part, u2);
       umma::tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 4; ++j) v[j] = (4 * part + j <= fl) ? v[j] : 0.f;
       unsigned char *pt = sm + (side ? oZ : oP) + qd * 2 * kTileS;
       write4<kTileS>(pt, (fl & 7) * 16 + (fl >> 3) * kRGs + (part >> 1) * kCG + (part & 1) * 8, v);
-    }
-
-    // ---- forward states at the starts of sub-blocks 1..3 (lanes A), kept in tensor memory -----
-#pragma unroll 1
-    for (int J = 0; J + 1 < kNSub; ++J) {
-      if (J > 0) {
-        if (issuer) {
-          if (hw == 0) {
-            // chain accumulator += Xt_J Kt_J^T  (contraction over the 16 steps of block J)
-            gemm3<false, false, kDim, kDim, 1, kDim, true>(dA + cTs, dlo<false, kDim>(aX, 0, J),
-                                                           dlo<false, kDim>(aK, 0, J));
-            umma::mma_commit(&barM);
-          } else {
-            mbar_arrive(&barM);
-          }
-        }
-        if (worker) wait_mma();
-        sync_all();
-        if (s_fail) break;
-      }
-      if (worker) {
-        float v[16];
-        umma::tmem_ld16(tl + cTs + 16 * part, v);
-        umma::tmem_ld_wait();
-        const float ar = aI[J * kDim + feat];
+      const float a0 = aI[feat], a1 = aI[kDim + feat], a2 = aI[2 * kDim + feat];
 #pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          const float4 g4 = *reinterpret_cast<const float4 *>(gI + J * kDim + 16 * part + 4 * j4);
-          v[4 * j4] *= ar * g4.x; v[4 * j4 + 1] *= ar * g4.y; v[4 * j4 + 2] *= ar * g4.z; v[4 * j4 + 3] *= ar * g4.w;
-        }
-        umma::tmem_st16(tl + cS + 64 * (J + 1) + 16 * part, v);
-        if (J + 2 < kNSub) umma::tmem_st16(tl + cTs + 16 * part, v);
-        umma::tmem_st_wait();
+      for (int j = 0; j < 16; ++j) {
+        const int kc = 16 * part + j;
+        sv[j] = (Rreg[j] + u0[j]) * (a0 * gI[kc]);
+        u0[j] = sv[j];
+        sv[j] = (sv[j] + u1[j]) * (a1 * gI[kDim + kc]);
+        u1[j] = sv[j];
+        u2[j] = (sv[j] + u2[j]) * (a2 * gI[2 * kDim + kc]);
       }
-      umma::fence_async_smem();      // (J == 0: the P / Z diagonal blocks written above)
-      sync_all();
+      umma::tmem_st16(tl + cS + 64 + 16 * part, u0);
+      umma::tmem_st16(tl + cS + 128 + 16 * part, u1);
+      umma::tmem_st16(tl + cS + 192 + 16 * part, u2);
+      umma::tmem_st_wait();
     }
+    umma::fence_async_smem();      // the P / Z diagonal blocks written above
+    sync_all();
     if (s_fail) break;
     PROF(4);
 
@@ -502,6 +505,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
           umma::named_barrier(kBarY, kTAll);
           umma::fence_after_sync();
         }
+        if (I < 0 && ci + gridDim.x < total) prefetch_rows(ci + gridDim.x);   // R is no longer live
         if (I >= 0) {
           // lanes A: S[I];  lanes B: dOt Qt^T of block I+1 (the part of R that block added)
           float v[16];
@@ -605,8 +609,10 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
         PROF(7);
       } else {
         if (I >= 0) {
+          PROFH(5);
           umma::named_barrier(kBarA, kTAll);
           umma::fence_after_sync();
+          PROFH(0);
           if (lane == 0) {
             const int cres = (I & 1) ? cTs : cRes0;
             const uint32_t zI = aZ + I * 2 * kTileS, pI = aP + I * 2 * kTileS;
@@ -634,6 +640,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
             umma::mma_commit(&barM);
           }
           __syncwarp();
+          PROFH(1);
 
           // ---- exact gate gradients of block I where the gate is too small for the cancelling
           //      form (needs only the tiles, so it runs under the MMAs):
@@ -670,9 +677,11 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
           }
           __threadfence_block();
           bar_arrive(kBarY, kTAll);
+          PROFH(2);
         }
         if (I < kNSub - 1) {
           umma::named_barrier(kBarB + (I & 1), kTAll);
+          PROFH(3);
           const int n_fix = fix_n[J] < kFixCap ? fix_n[J] : kFixCap;
           if (ht < n_fix) {
             const int code = fix_code[J * kFixCap + ht];
@@ -692,6 +701,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
               *reinterpret_cast<uint4 *>(dst[it] + base + (size_t)(rJ + r) * kDim + ch * 8) = val;
             }
           }
+          PROFH(4);
         }
       }
     }
