@@ -429,9 +429,13 @@ def run_ours(args):
     else:
         which, alg, dur = "forward call (all kernels of t2fw_lfw_forward)", fb, f_ms
     achieved = alg / (dur * 1e-3) / 1e9
+    # DRAM bytes (read + write) per call from the committed ncu captures of exactly this workload
+    # (profiles/): sum over the kernels of the timed call; None where no capture exists.
+    traffic = {("train", "backward"): 220.3e6, ("decode", "forward"): 37.0e6}.get(
+        (args.workload, which.split()[0]))
     roofline = {
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-        "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind + " copy bandwidth",
+        "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind + " copy bandwidth",
         "kernel": which, "algorithmic_bytes_per_launch": alg, "avg_ms": dur,
         "fwd_ms": f_ms, "bwd_ms": b_ms,
         "whole_step_frac": ((fb + (0 if decode else bb)) / ((f_ms + b_ms) * 1e-3) / 1e9) / peak,
