@@ -80,8 +80,8 @@ constexpr int kStgBytes = 5 * kSub * kStgLd * 2;
 constexpr int kFixCap = 64;     // tiny-gate entries per sub-block
 constexpr float kTinyGate = 9.765625e-4f;   // 2^-10
 constexpr int kRawBytes = kC * kDim * 2;
-constexpr float kBlockLo = 8.673617e-19f, kBlockHi = 1.152922e+18f;   // 2^-60, 2^60
-constexpr float kDivHi = 7.205759e+16f;                               // 2^56
+constexpr float kBlockLo = 7.888609e-31f, kBlockHi = 1.267651e+30f;   // 2^-100, 2^100
+constexpr float kDivProdHi = 1.329228e+36f;                           // 2^120
 
 // shared-memory map (bytes); the lo tile of every pair directly follows its hi tile
 constexpr int oQ = 0, oK = 2 * kTile, oX = 4 * kTile, oO = 6 * kTile, oS = 8 * kTile, oR = 10 * kTile;
@@ -252,6 +252,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int s_fail;
   __shared__ int fix_n[kNSub];
+  __shared__ unsigned div_max[2];   // largest |divided operand| of the chunk: k side, d side
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool worker = warp < 4 * kParts;
@@ -353,6 +354,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
     const size_t base = ((size_t)b * T_ + t0c) * kDim;
     PROF(0);
     if (threadIdx.x < kNSub) fix_n[threadIdx.x] = 0;
+    if (threadIdx.x < 2) div_max[threadIdx.x] = 0u;
     if (!acp::mbar_wait(&barRaw, praw)) s_fail = 1;
     praw ^= 1u;
     raw_pending = false;
@@ -379,6 +381,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
 
       // ---- operand tiles: thread = (side, feature, step quarter); prefix products restart per block
       bool out_of_range = false;
+      float div_hi = 0.f;
 #pragma unroll
       for (int I = 0; I < kNSub; ++I) {
         float p = 1.f;
@@ -409,8 +412,9 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
             }
           }
         }
-        // the ratio operands need the sub-block prefix products within [2^-60, 2^60] and the
-        // divided operands below 2^56, so that no product of two of them overflows
+        // the ratio operands need the sub-block prefix products within [2^-100, 2^100], and the
+        // largest divided operand of the k side times that of the d side (they meet in
+        // Xt Kt^T) must stay below 2^120: the maxima are collected per side in shared memory
         float plo = fabsf(pr[I][0]), phi = plo, dhi = fabsf(dv[0]);
 #pragma unroll
         for (int j = 1; j < 4; ++j) {
@@ -418,7 +422,8 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
           phi = fmaxf(phi, fabsf(pr[I][j]));
           dhi = fmaxf(dhi, fabsf(dv[j]));
         }
-        out_of_range |= !(plo >= kBlockLo && phi <= kBlockHi && dhi <= kDivHi);
+        out_of_range |= !(plo >= kBlockLo && phi <= kBlockHi);
+        div_hi = fmaxf(div_hi, dhi);
         const int off = umma::tile16_off(feat, t0, kDim);
         write4<kTile>(mulT, off, mv);
         write4<kTile>(divT, off, dv);
@@ -426,6 +431,15 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
       }
       PROF(12);
       if (out_of_range) atomicExch(rowflag + b, 1);   // the scan kernels redo this batch row
+      {
+        const unsigned bits = __float_as_uint(div_hi);     // non-negative floats order like integers
+        const unsigned mk = __reduce_max_sync(0xffffffffu, side ? 0u : bits);
+        const unsigned md = __reduce_max_sync(0xffffffffu, side ? bits : 0u);
+        if (lane == 0) {
+          atomicMax(&div_max[0], mk);
+          atomicMax(&div_max[1], md);
+        }
+      }
       umma::tmem_st_wait();
     }
     umma::fence_async_smem();
@@ -434,6 +448,8 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
       issue_raw(ci + gridDim.x);
       raw_pending = true;
     }
+    if (threadIdx.x == 0 && !(__uint_as_float(div_max[0]) * __uint_as_float(div_max[1]) <= kDivProdHi))
+      atomicExch(rowflag + b, 1);
     PROF(2);
 
     // ---- round 1: P = Qt^T Kt (lanes A), Z = dOt^T Xt (lanes B) for the whole chunk, and the
