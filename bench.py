@@ -41,8 +41,9 @@ WORKLOADS = {
     "train": (96, 1024, 64, 64),     # single layer, GPT-2-small shape, fwd + bwd
     "decode": (4096, 1, 64, 64),     # T=1 decode step, GPT-2-medium heads x batch 256
     "long": (16, 16384, 128, 128),   # long-sequence prefill + backward
+    "dfw": (96, 1024, 64, 64),       # delta rule (DFWFunction), GPT-2-small shape, fwd + bwd
 }
-CPU_SAMPLE_ROWS = {"train": 16, "decode": 4096, "long": 1}
+CPU_SAMPLE_ROWS = {"train": 16, "decode": 4096, "long": 1, "dfw": 16}
 
 
 def parse_args():
@@ -63,6 +64,12 @@ def parse_args():
 
 def make_inputs(torch, B, T, D, K, gates, seed, workload):
     g = torch.Generator().manual_seed(seed)
+    if workload == "dfw":      # q, k, v, zero state, upstream gradients
+        q = torch.randn(B, T, K, generator=g) / math.sqrt(K)
+        k = torch.randn(B, T, K, generator=g) / math.sqrt(K)
+        v = torch.randn(B, T, D, generator=g)
+        return [q, k, v, torch.zeros(B, D, K), torch.randn(B, T, D, generator=g),
+                torch.randn(B, D, K, generator=g)]
     x = torch.randn(B, T, D, generator=g)
     q = torch.randn(B, T, K, generator=g) / math.sqrt(K)
     k = torch.randn(B, T, K, generator=g) / math.sqrt(K)
@@ -87,6 +94,14 @@ def algorithmic_bytes(B, T, D, K, e=2):
     n = B * T
     fwd = e * (n * (2 * D + 3 * K) + n * D + 2 * B * D * K)
     bwd = e * (n * D + 2 * n * (2 * D + 3 * K) + 3 * B * D * K)
+    return fwd, bwd
+
+
+def algorithmic_bytes_dfw(B, T, D, M, e=2):
+    """Delta rule: q, k [N,M], v [N,D] in, outputs out, state in/out; the saved delta is not counted."""
+    n = B * T
+    fwd = e * (n * (2 * M + D) + n * D + 2 * B * D * M)
+    bwd = e * (n * D + 2 * n * (2 * M + D) + 3 * B * D * M)
     return fwd, bwd
 
 
@@ -168,12 +183,15 @@ def cpu_reference_run(workload, gates, steps, warmup, seed):
     rows = min(B, CPU_SAMPLE_ROWS[workload])
     # launchers such as torchrun pin OMP_NUM_THREADS=1; the CPU baseline uses every host core
     torch.set_num_threads(max(1, os.cpu_count() or 1))
-    x, f, q, k, fk, s, go, gs = [t[:rows].contiguous() for t in
-                                 make_inputs(torch, rows, T, D, K, gates, seed, workload)]
+    ins = [t[:rows].contiguous() for t in make_inputs(torch, rows, T, D, K, gates, seed, workload)]
+    if workload != "dfw":
+        x, f, q, k, fk, s, go, gs = ins
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        if workload == "decode":
+        if workload == "dfw":
+            torch_port.dfw_fwd_bwd(*ins)
+        elif workload == "decode":
             with torch.no_grad():
                 torch_port.lfw_loop(x, f, q, k, fk, s)
         else:
@@ -217,10 +235,15 @@ def run_reference(args):
 
 def metric_name(workload):
     return {"train": "lfw_fwd_bwd_tokens_per_s", "decode": "lfw_decode_tokens_per_s",
-            "long": "lfw_fwd_bwd_tokens_per_s"}[workload]
+            "long": "lfw_fwd_bwd_tokens_per_s", "dfw": "dfw_fwd_bwd_tokens_per_s"}[workload]
 
 
 def workload_config(args, B, T, D, K):
+    if args.workload == "dfw":
+        return {"workload": "dfw: DFW (delta rule) forward+backward, B*H=%d per GPU, T=%d, D=M=%d, fp16 I/O, "
+                            "fp32 state arithmetic" % (B, T, D),
+                "inputs": "q, k ~ N(0,1)/sqrt(M), v ~ N(0,1), zero initial state",
+                "sharding": "batch*head rows split across GPUs, no collective"}
     return {
         "workload": "%s: LFW %s, B*H=%d per GPU, T=%d, D=K=%d, fp16 I/O, fp32 state arithmetic"
                     % (args.workload, "forward (decode step)" if args.workload == "decode"
@@ -246,12 +269,14 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     from t2fw_b200 import _lib, cabi
+    from t2fw_b200.functional_dfw import DFWFunction
     from t2fw_b200.functional_lfw import LFWFunction
     from t2fw_b200.parallel import job_throughput, max_over_ranks
 
     lib = _lib.load_core()
     B, T, D, K = WORKLOADS[args.workload]
     decode = args.workload == "decode"
+    dfw = args.workload == "dfw"
     dtype = torch.float16
 
     # Rotating input sets so that consecutive steps never find their data in the 126 MB L2.
@@ -263,20 +288,35 @@ def run_ours(args):
     sets = [base] + [[t.roll(i, 0).contiguous() for t in base] for i in range(1, n_sets)]
 
     C = cabi.ckpt_every_for(T, D, K, dtype)
-    slots = int(lib.t2fw_lfw_ckpt_slots(T, C))
-    outs = [torch.empty(B, T, D, dtype=dtype, device=dev) for _ in range(n_sets)]
-    ckpts = [torch.empty(B, slots, D, K, dtype=dtype, device=dev) for _ in range(n_sets)]
-    grads = None if decode else [[torch.empty_like(t) for t in s[:6]] for s in sets]
     code = cabi.dtype_code(base[0])
-    fsb = lib.t2fw_lfw_forward_scratch_bytes(B, T, D, K, code, C)
-    bsb = lib.t2fw_lfw_backward_scratch_bytes(B, T, D, K, code, C)
-    fscr = torch.empty(max(fsb, 1), dtype=torch.uint8, device=dev)
-    bscr = torch.empty(max(bsb, 1), dtype=torch.uint8, device=dev)
+    if not dfw:
+        slots = int(lib.t2fw_lfw_ckpt_slots(T, C))
+        outs = [torch.empty(B, T, D, dtype=dtype, device=dev) for _ in range(n_sets)]
+        ckpts = [torch.empty(B, slots, D, K, dtype=dtype, device=dev) for _ in range(n_sets)]
+        grads = None if decode else [[torch.empty_like(t) for t in s[:6]] for s in sets]
+        fsb = lib.t2fw_lfw_forward_scratch_bytes(B, T, D, K, code, C)
+        bsb = lib.t2fw_lfw_backward_scratch_bytes(B, T, D, K, code, C)
+        fscr = torch.empty(max(fsb, 1), dtype=torch.uint8, device=dev)
+        bscr = torch.empty(max(bsb, 1), dtype=torch.uint8, device=dev)
+    else:
+        bsb = lib.t2fw_dfw_backward_scratch_bytes(B, T, D, K, code)
+        bscr = torch.empty(max(bsb, 1), dtype=torch.uint8, device=dev)
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
     fwd_ms, bwd_ms = [], []
 
-    if decode:
+    if dfw:
+        def step(i, record=None):
+            q, k, v, s, go, gs = sets[i % n_sets]
+            if record:
+                record[0].record()
+            _, fin, delta = cabi.dfw_forward(q, k, v, s)
+            if record:
+                record[1].record()
+            cabi.dfw_backward(go, gs, q, k, delta, fin, scratch=bscr)
+            if record:
+                record[2].record()
+    elif decode:
         # chained decode: each set's state advances every time the set comes round; the new
         # state is written to the set's other buffer (inputs are never overwritten in place)
         state_a = [s[5] for s in sets]
@@ -372,15 +412,31 @@ def run_ours(args):
         e2e_steps = max(3, min(args.steps, 10))
         host = [t.to(dtype).pin_memory() for t in
                 make_inputs(torch, B, T, D, K, args.gates, args.seed + 1000 * rank, args.workload)]
-        n_res = 2 if decode else 8
-        res_host = None
-        h2d = sum(t.numel() * t.element_size() for t in (host[:6] if decode else host))
+        srcs = host[:6] if decode else host
+        h2d = sum(t.numel() * t.element_size() for t in srcs)
         d2h = 0
+        # three streams: inputs in, compute, results out; two sets of pinned result buffers, so
+        # that step i's device->host copy overlaps step i+1's host->device copy and compute
+        s_cmp = torch.cuda.current_stream(dev)
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        res_host, out_done = [None, None], [None, None]
 
-        def e2e_step():
-            nonlocal res_host, d2h
-            devs = [t.to(dev, non_blocking=True) for t in (host[:6] if decode else host)]
-            if decode:
+        def e2e_step(i):
+            nonlocal d2h
+            slot = i & 1
+            with torch.cuda.stream(s_in):
+                devs = [t.to(dev, non_blocking=True) for t in srcs]
+                ev_in = torch.cuda.Event()
+                ev_in.record(s_in)
+            s_cmp.wait_event(ev_in)
+            for t in devs:
+                t.record_stream(s_cmp)
+            if dfw:
+                leaves = [t.requires_grad_(True) for t in devs[:4]]
+                out, nxt = DFWFunction.apply(*leaves)
+                g = torch.autograd.grad([out, nxt], leaves, [devs[4], devs[5]])
+                results = [out, nxt] + list(g)
+            elif decode:
                 with torch.no_grad():
                     out, nxt = LFWFunction.apply(*devs[:6])
                 results = [out, nxt]
@@ -389,21 +445,37 @@ def run_ours(args):
                 out, nxt = LFWFunction.apply(*leaves)
                 g = torch.autograd.grad([out, nxt], leaves, [devs[6], devs[7]])
                 results = [out, nxt] + list(g)
-            if res_host is None:
-                res_host = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in results]
+            ev_c = torch.cuda.Event()
+            ev_c.record(s_cmp)
+            if res_host[slot] is None:
+                res_host[slot] = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in results]
                 d2h = sum(r.numel() * r.element_size() for r in results)
-            for h, r in zip(res_host, results):
-                h.copy_(r, non_blocking=True)
-            torch.cuda.synchronize()
+            if out_done[slot] is not None:
+                out_done[slot].synchronize()      # the host is done with this set's previous results
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_c)
+                for h, r in zip(res_host[slot], results):
+                    r.record_stream(s_out)
+                    h.copy_(r, non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(s_out)
+            out_done[slot] = done
 
-        for _ in range(3):
-            e2e_step()
+        def e2e_drain():
+            s_cmp.wait_stream(s_in)
+            s_cmp.wait_stream(s_out)
+
+        for i in range(4):
+            e2e_step(i)
+        e2e_drain()
+        torch.cuda.synchronize()
         barrier()
         t0 = time.perf_counter()
         e0, e1 = ev(), ev()
         e0.record()
-        for _ in range(e2e_steps):
-            e2e_step()
+        for i in range(e2e_steps):
+            e2e_step(i)
+        e2e_drain()
         e1.record()
         barrier()
         wall = time.perf_counter() - t0
@@ -411,7 +483,9 @@ def run_ours(args):
         e2e_ms = max_over_ranks(e2e_ms, dev)
         e2e = {"value": B * T * e2e_steps * world / (e2e_ms * 1e-3), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-               "ms_per_step": e2e_ms / e2e_steps, "api": "LFWFunction.apply + autograd, pinned host buffers",
+               "ms_per_step": e2e_ms / e2e_steps,
+               "api": ("DFWFunction" if dfw else "LFWFunction") + ".apply + autograd; pinned host buffers; H2D, compute and D2H on three "
+                      "streams with two result sets (step i's D2H overlaps step i+1's H2D)",
                "wall_ms_per_step": wall * 1e3 / e2e_steps}
 
     if rank != 0:
@@ -420,14 +494,14 @@ def run_ours(args):
         return
 
     # ---- roofline of the slower call -------------------------------------------------------
-    fb, bb = algorithmic_bytes(B, T, D, K)
+    fb, bb = algorithmic_bytes_dfw(B, T, D, K) if dfw else algorithmic_bytes(B, T, D, K)
     peak, peak_kind = measured_hbm_peak()
     f_ms = statistics.mean(fwd_ms)
     b_ms = statistics.mean(bwd_ms) if bwd_ms else 0.0
     if b_ms >= f_ms and not decode:
-        which, alg, dur = "backward call (all kernels of t2fw_lfw_backward)", bb, b_ms
+        which, alg, dur = "backward call (all kernels of t2fw_%s_backward)" % ("dfw" if dfw else "lfw"), bb, b_ms
     else:
-        which, alg, dur = "forward call (all kernels of t2fw_lfw_forward)", fb, f_ms
+        which, alg, dur = "forward call (all kernels of t2fw_%s_forward)" % ("dfw" if dfw else "lfw"), fb, f_ms
     achieved = alg / (dur * 1e-3) / 1e9
     # DRAM bytes (read + write) per call from the committed ncu captures of exactly this workload
     # (profiles/): sum over the kernels of the timed call; None where no capture exists.
