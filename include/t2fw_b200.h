@@ -72,6 +72,7 @@ size_t t2fw_lfw_forward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K
                                       int64_t ckpt_every);
 size_t t2fw_lfw_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K, int dtype,
                                        int64_t ckpt_every);
+size_t t2fw_dfw_forward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t M, int dtype);
 size_t t2fw_dfw_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t M, int dtype);
 
 /*
@@ -110,6 +111,18 @@ int t2fw_lfw_backward(const void *grad_output, const void *grad_state,
 int t2fw_dfw_forward(const void *q, const void *k, const void *v, const void *state,
                      void *outputs, void *final_state, void *delta,
                      int64_t B, int64_t T, int64_t D, int64_t M, int dtype, void *stream);
+
+/*
+ * Delta rule forward with caller-provided scratch (t2fw_dfw_forward_scratch_bytes): same
+ * inputs, outputs and reference interface as t2fw_dfw_forward.  With scratch the library can run
+ * the chunked tensor-core kernels (D = M = 64, 16-bit storage: per-chunk triangular solves in
+ * fp32, chunk contractions on the tensor cores) instead of the step-by-step scan; the saved
+ * `delta` is the same quantity either way, so either forward can be paired with the backward.
+ */
+int t2fw_dfw_forward_ws(const void *q, const void *k, const void *v, const void *state,
+                        void *outputs, void *final_state, void *delta,
+                        int64_t B, int64_t T, int64_t D, int64_t M, int dtype,
+                        void *scratch, size_t scratch_bytes, void *stream);
 
 /*
  * Delta rule backward: d_query, d_key, d_value, d_state.

@@ -20,6 +20,7 @@ EXPORTS = (
     "t2fw_lfw_forward_scratch_bytes", "t2fw_lfw_backward_scratch_bytes",
     "t2fw_dfw_backward_scratch_bytes",
     "t2fw_lfw_forward", "t2fw_lfw_backward", "t2fw_dfw_forward", "t2fw_dfw_backward",
+    "t2fw_dfw_forward_ws", "t2fw_dfw_forward_scratch_bytes",
     "t2fw_dfw_backward_noalloc_max_elems", "t2fw_dfw_backward_noalloc",
 )
 
@@ -56,6 +57,10 @@ def load_core():
         fn.argtypes = [_i64, _i64, _i64, _i64, _int, _i64]
     lib.t2fw_dfw_backward_scratch_bytes.restype = _sz
     lib.t2fw_dfw_backward_scratch_bytes.argtypes = [_i64, _i64, _i64, _i64, _int]
+    lib.t2fw_dfw_forward_scratch_bytes.restype = _sz
+    lib.t2fw_dfw_forward_scratch_bytes.argtypes = [_i64, _i64, _i64, _i64, _int]
+    lib.t2fw_dfw_forward_ws.restype = _int
+    lib.t2fw_dfw_forward_ws.argtypes = [_vp] * 7 + [_i64] * 4 + [_int, _vp, _sz, _vp]
     lib.t2fw_lfw_forward.restype = _int
     lib.t2fw_lfw_forward.argtypes = [_vp] * 8 + [_i64] * 4 + [_int, _i64, _vp, _sz, _vp]
     lib.t2fw_lfw_backward.restype = _int

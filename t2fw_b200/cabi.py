@@ -102,8 +102,9 @@ def _acc_dtype(t):
     return torch.float64 if t.dtype == torch.float64 else torch.float32
 
 
-def dfw_forward(q, k, v, state):
-    """Returns (outputs [B,T,D], final_state [B,D,M], delta [B,T,D] in float/double)."""
+def dfw_forward(q, k, v, state, scratch=None, use_scratch=True):
+    """Returns (outputs [B,T,D], final_state [B,D,M], delta [B,T,D] in float/double).
+    use_scratch=False calls the scratch-free entry point (step-by-step scan kernels)."""
     lib = _lib.load_core()
     _dev(q, k, v, state)
     B, T, D = v.shape
@@ -111,10 +112,21 @@ def dfw_forward(q, k, v, state):
     out = torch.empty_like(v)
     fin = torch.empty_like(state)
     delta = torch.empty(B, T, D, dtype=_acc_dtype(v), device=v.device)
-    rc = lib.t2fw_dfw_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), state.data_ptr(),
-                              out.data_ptr(), fin.data_ptr(), delta.data_ptr(), B, T, D, M,
-                              dtype_code(v), _stream())
-    _check(rc, "t2fw_dfw_forward")
+    if not use_scratch:
+        rc = lib.t2fw_dfw_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), state.data_ptr(),
+                                  out.data_ptr(), fin.data_ptr(), delta.data_ptr(), B, T, D, M,
+                                  dtype_code(v), _stream())
+        _check(rc, "t2fw_dfw_forward")
+        return out, fin, delta
+    nb = lib.t2fw_dfw_forward_scratch_bytes(B, T, D, M, dtype_code(v))
+    if scratch is None:
+        scratch, nb = _scratch(nb, v)
+    sp = scratch.data_ptr() if scratch is not None else None
+    rc = lib.t2fw_dfw_forward_ws(q.data_ptr(), k.data_ptr(), v.data_ptr(), state.data_ptr(),
+                                 out.data_ptr(), fin.data_ptr(), delta.data_ptr(), B, T, D, M,
+                                 dtype_code(v), sp, scratch.numel() if scratch is not None else 0,
+                                 _stream())
+    _check(rc, "t2fw_dfw_forward_ws")
     return out, fin, delta
 
 

@@ -86,11 +86,32 @@ size_t t2fw_lfw_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t 
   return 0;
 }
 
-size_t t2fw_dfw_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t M, int dtype) {
-  (void)M;
+static bool dfw_chunk_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("T2FW_DISABLE_DFW_CHUNK");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
+
+size_t t2fw_dfw_forward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t M, int dtype) {
+  if (dfw_chunk_enabled() && dfw_chunk_supported(D, M, dtype)) return dfw_chunk_scratch_bytes(B, T);
+  return 0;
+}
+
+static size_t dfw_scan_backward_scratch(int64_t B, int64_t T, int64_t D, int dtype) {
   // d_value is kept in float next to its 16-bit output for the column pass
   if (dtype == T2FW_F16 || dtype == T2FW_BF16) return align_up((size_t)B * T * D * sizeof(float), 256);
   return 0;
+}
+
+size_t t2fw_dfw_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t M, int dtype) {
+  const size_t scan = dfw_scan_backward_scratch(B, T, D, dtype);
+  if (dfw_chunk_enabled() && dfw_chunk_supported(D, M, dtype)) {
+    const size_t ch = dfw_chunk_scratch_bytes(B, T);
+    return ch > scan ? ch : scan;
+  }
+  return scan;
 }
 
 static int check_common(int64_t B, int64_t T, int64_t D, int64_t K, int dtype) {
@@ -190,6 +211,26 @@ int t2fw_dfw_forward(const void *q, const void *k, const void *v, const void *st
                           static_cast<cudaStream_t>(stream));
 }
 
+int t2fw_dfw_forward_ws(const void *q, const void *k, const void *v, const void *state,
+                        void *outputs, void *final_state, void *delta, int64_t B, int64_t T,
+                        int64_t D, int64_t M, int dtype, void *scratch, size_t scratch_bytes,
+                        void *stream) {
+  int rc = check_common(B, T, D, M, dtype);
+  if (rc != T2FW_OK) return rc;
+  T2FW_CHECK_ARG(q && k && v && state && outputs && final_state && delta, "null pointer argument");
+  const size_t need = t2fw_dfw_forward_scratch_bytes(B, T, D, M, dtype);
+  if (need != 0) {
+    if (scratch == nullptr || scratch_bytes < need) {
+      set_error("dfw forward needs %zu bytes of scratch, got %zu", need, scratch_bytes);
+      return T2FW_ERR_SCRATCH;
+    }
+    return dfw_chunk_forward(q, k, v, state, outputs, final_state, delta, B, T, dtype, scratch,
+                             static_cast<cudaStream_t>(stream));
+  }
+  return dfw_scan_forward(q, k, v, state, outputs, final_state, delta, B, T, D, M, dtype,
+                          static_cast<cudaStream_t>(stream));
+}
+
 int t2fw_dfw_backward(const void *grad_output, const void *grad_state, const void *q,
                       const void *k, const void *delta, const void *final_state, void *d_q,
                       void *d_k, void *d_v, void *d_state, int64_t B, int64_t T, int64_t D,
@@ -208,6 +249,9 @@ int t2fw_dfw_backward(const void *grad_output, const void *grad_state, const voi
     }
     dv_acc = scratch;
   }
+  if (dfw_chunk_enabled() && dfw_chunk_supported(D, M, dtype))
+    return dfw_chunk_backward(grad_output, grad_state, q, k, delta, final_state, d_q, d_k, d_v, d_state,
+                              B, T, dtype, scratch, static_cast<cudaStream_t>(stream));
   return dfw_scan_backward(grad_output, grad_state, q, k, delta, final_state, d_q, d_k, d_v,
                            d_state, dv_acc, B, T, D, M, dtype, static_cast<cudaStream_t>(stream));
 }

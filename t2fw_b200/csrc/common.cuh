@@ -131,6 +131,15 @@ bool lfw_decode_supported(int64_t D, int64_t K, int dtype);
 int lfw_decode_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,
                        const void *state, void *out, void *new_state, int64_t B, int64_t D,
                        int64_t K, int dtype, cudaStream_t st);
+// chunked delta rule (dfw_chunk.cu): D = M = 64, 16-bit storage
+bool dfw_chunk_supported(int64_t D, int64_t M, int dtype);
+size_t dfw_chunk_scratch_bytes(int64_t B, int64_t T);
+int dfw_chunk_forward(const void *q, const void *k, const void *v, const void *state, void *out,
+                      void *final_state, void *delta, int64_t B, int64_t T, int dtype, void *scratch,
+                      cudaStream_t st);
+int dfw_chunk_backward(const void *go, const void *gs, const void *q, const void *k, const void *delta,
+                       const void *final_state, void *dq, void *dk, void *dv, void *ds, int64_t B, int64_t T,
+                       int dtype, void *scratch, cudaStream_t st);
 int dfw_scan_forward(const void *q, const void *k, const void *v, const void *state, void *out,
                      void *fin, void *delta, int64_t B, int64_t T, int64_t D, int64_t M, int dtype,
                      cudaStream_t st);

@@ -1,0 +1,492 @@
+// Delta rule in chunked form (D = M = 64, 16-bit storage): chunks of 64 steps, the contractions
+// of a chunk on the tensor cores (mma.sync TF32, fp32 accumulation), the state carried in fp32.
+//
+// Replaces, for these shapes, the step-by-step scans of t2fw/csrc/dfw_kernel.cu:105-384.
+//
+// With K, Q [64 x M], V, dO [64 x D] the rows of one chunk, S0 the state before the chunk and
+// L = strict_lower(K K^T):
+//   delta rule per step:  d_t = v_t - S_{t-1} k_t,  S_t = S_{t-1} + d_t k_t^T,  o_t = S_{t-1} q_t
+//   chunk form:           (I + L) Dl = V - K S0^T   =>  Dl = U - W S0^T,  W = (I+L)^-1 K,  U = (I+L)^-1 V
+//                         O = Q S0^T + strict_lower(Q K^T) Dl ,   S_end = S0 + Dl^T K
+// Backward (R = gradient of the state, walking the chunks in reverse; e_t = d_value_t = R_t k_t):
+//                         (I + L^T) E = K R_end^T + strict_upper(K Q^T) dO
+//                                   =>  E = Ub + Wb R_end^T,  Wb = (I+L^T)^-1 K,  Ub = (I+L^T)^-1 strict_upper(K Q^T) dO
+//   d_value = E
+//   d_query = dO S0 + strict_lower(dO Dl^T) K
+//   d_key   = Dl R_end + strict_upper(Dl dO^T) Q - (strict_upper(X) + strict_lower(X^T)) K - E S0,   X = Dl E^T
+//   R_start = R_end + dO^T Q - E^T K ,   S0 = S_end - Dl^T K   (the state is walked back from
+//   final_state with the saved Dl, as the reference's backward does step by step)
+//
+// Kernels:
+//   dfw_chunk_prep_kernel<T, kBwd>   (batch row, chunk): W, U (or Wb, Ub) by forward (backward)
+//       substitution in fp32, one thread per column, no inverse is ever formed
+//   dfw_chunk_fwd_kernel<T>          one CTA per batch row, sequential over chunks
+//   dfw_chunk_bwd_kernel<T>          one CTA per batch row, sequential over chunks in reverse
+#include <type_traits>
+
+#include "lfw_chunk.cuh"
+
+namespace t2fw {
+
+using namespace chunk;
+
+namespace {
+
+constexpr int kLdS = 65;          // row stride of the prep kernel's fp32 tiles (conflict-free columns)
+constexpr int kSeqThreads = 256;  // 8 warps: warp w owns rows 16*(w&3), columns 32*(w>>2) of a product
+
+// ---- prep: W, U (forward) or Wb, Ub (backward) --------------------------------------------------
+// grid = B * nc, 128 threads.  Output tiles are fp32 [64][64] row-major, rows beyond the end of
+// the sequence are zero.
+template <typename T, bool kBwd>
+__global__ void __launch_bounds__(128)
+dfw_chunk_prep_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v_or_go,
+                      float *__restrict__ Wout, float *__restrict__ Uout, int64_t T_, int64_t nc) {
+  extern __shared__ __align__(16) float sm[];
+  float *Ks = sm, *Ls = Ks + kC * kLdS, *Vs = Ls + kC * kLdS, *Qs = Vs + kC * kLdS;   // Qs: backward only
+  const int64_t b = blockIdx.x / nc, c = blockIdx.x % nc, t0 = c * kC;
+  const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
+  const size_t base = ((size_t)b * T_ + t0) * kDim;
+  const int tid = threadIdx.x;
+
+  for (int idx = tid; idx < kC * (kDim / 2); idx += 128) {
+    const int r = idx / (kDim / 2), c2 = (idx % (kDim / 2)) * 2;
+    float2 kk = make_float2(0.f, 0.f), vv = kk, qq = kk;
+    if (r < nvalid) {
+      kk = Pair<T>::ld(k + base + (size_t)r * kDim + c2);
+      vv = Pair<T>::ld(v_or_go + base + (size_t)r * kDim + c2);
+      if (kBwd) qq = Pair<T>::ld(q + base + (size_t)r * kDim + c2);
+    }
+    Ks[r * kLdS + c2] = kk.x; Ks[r * kLdS + c2 + 1] = kk.y;
+    Vs[r * kLdS + c2] = vv.x; Vs[r * kLdS + c2 + 1] = vv.y;
+    if (kBwd) { Qs[r * kLdS + c2] = qq.x; Qs[r * kLdS + c2 + 1] = qq.y; }
+  }
+  __syncthreads();
+
+  // Ls[t][s] = k_t . k_s  (forward: used for s < t; backward: for s > t; symmetric, so all of it)
+  for (int idx = tid; idx < kC * kC; idx += 128) {
+    const int t = idx / kC, s = idx % kC;
+    float acc = 0.f;
+#pragma unroll 16
+    for (int m = 0; m < kDim; ++m) acc = fmaf(Ks[t * kLdS + m], Ks[s * kLdS + m], acc);
+    Ls[t * kLdS + s] = acc;
+  }
+  if (kBwd) {
+    // right-hand side of the d side: rhs[t][d] = sum_{s>t} (k_t . q_s) dO[s][d]; first the scores
+    // into registers is too much state, so they go through shared memory in place of Q
+    __syncthreads();
+    float sc[32];        // this thread's 32 scores: entries idx = tid + 128*j
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int idx = tid + 128 * j, t = idx / kC, s = idx % kC;
+      float acc = 0.f;
+      if (s > t) {
+#pragma unroll 16
+        for (int m = 0; m < kDim; ++m) acc = fmaf(Ks[t * kLdS + m], Qs[s * kLdS + m], acc);
+      }
+      sc[j] = acc;
+    }
+    __syncthreads();     // every thread has read Q
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int idx = tid + 128 * j;
+      Qs[(idx / kC) * kLdS + idx % kC] = sc[j];
+    }
+  }
+  __syncthreads();
+
+  // substitution: thread = one column of [K | V] (forward) or [K | rhs] (backward)
+  const int col = tid & 63;
+  const bool second = tid >= 64;
+  float x[kC];
+  if (!kBwd) {
+#pragma unroll
+    for (int t = 0; t < kC; ++t) {
+      float acc = second ? Vs[t * kLdS + col] : Ks[t * kLdS + col];
+#pragma unroll
+      for (int i = 0; i < t; ++i) acc = fmaf(-Ls[t * kLdS + i], x[i], acc);
+      x[t] = acc;
+    }
+  } else {
+#pragma unroll
+    for (int t = kC - 1; t >= 0; --t) {
+      float acc;
+      if (second) {
+        acc = 0.f;
+#pragma unroll
+        for (int s = t + 1; s < kC; ++s) acc = fmaf(Qs[t * kLdS + s], Vs[s * kLdS + col], acc);
+      } else {
+        acc = Ks[t * kLdS + col];
+      }
+#pragma unroll
+      for (int s = t + 1; s < kC; ++s) acc = fmaf(-Ls[t * kLdS + s], x[s], acc);
+      x[t] = acc;
+    }
+  }
+  float *dst = (second ? Uout : Wout) + (size_t)blockIdx.x * kC * kDim + col;
+#pragma unroll
+  for (int t = 0; t < kC; ++t) dst[t * kDim] = x[t];
+}
+
+// ---- helpers of the sequential kernels -------------------------------------------------------------
+// acc[nt][.] (rows m0 + {g, g+8}, columns n0 + 8*nt + {2tq, 2tq+1}) += A * B over a contraction of 64.
+//   AT: the tile holds A transposed (A[m][k] = tA[k][m]);  BT: the tile holds B as [n][k]
+template <bool AT, bool BT>
+__device__ __forceinline__ void gemm64(float (&acc)[4][4], const float *tA, const float *tB, int m0, int n0,
+                                       int g, int tq) {
+#pragma unroll 2
+  for (int k0 = 0; k0 < kC; k0 += 8) {
+    uint32_t a[4];
+    if (AT) lda_t(a, tA, kLd, m0, k0, g, tq); else lda(a, tA, kLd, m0, k0, g, tq);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      uint32_t bf[2];
+      if (BT) ldb_t(bf, tB, kLd, k0, n0 + 8 * nt, g, tq); else ldb(bf, tB, kLd, k0, n0 + 8 * nt, g, tq);
+      mma_tf32(acc[nt], a, bf);
+    }
+  }
+}
+__device__ __forceinline__ void zero(float (&acc)[4][4]) {
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+}
+// accumulator fragment -> fp32 tile (values rounded to TF32 so that the tile can feed an MMA)
+__device__ __forceinline__ void store_acc(float *t, const float (&acc)[4][4], int m0, int n0, int g, int tq) {
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    const int cc = n0 + 8 * nt + 2 * tq;
+    *reinterpret_cast<float2 *>(t + (m0 + g) * kLd + cc) = make_float2(round_tf32(acc[nt][0]), round_tf32(acc[nt][1]));
+    *reinterpret_cast<float2 *>(t + (m0 + g + 8) * kLd + cc) = make_float2(round_tf32(acc[nt][2]), round_tf32(acc[nt][3]));
+  }
+}
+// 16-bit [64][64] block of global memory -> TF32 tile; rows >= nvalid become zero
+template <typename T>
+__device__ __forceinline__ void load_tile16(float *t, const T *src, int nvalid, int tid) {
+  for (int idx = tid; idx < kC * (kDim / 8); idx += kSeqThreads) {
+    const int r = idx >> 3, c8 = (idx & 7) * 8;
+    float vals[8];
+    if (r < nvalid) {
+      const uint4 u = *reinterpret_cast<const uint4 *>(src + (size_t)r * kDim + c8);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 p = Pair<T>::ld(reinterpret_cast<const T *>(&w[j]));
+        vals[2 * j] = round_tf32(p.x);
+        vals[2 * j + 1] = round_tf32(p.y);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) vals[j] = 0.f;
+    }
+    *reinterpret_cast<float4 *>(t + r * kLd + c8) = make_float4(vals[0], vals[1], vals[2], vals[3]);
+    *reinterpret_cast<float4 *>(t + r * kLd + c8 + 4) = make_float4(vals[4], vals[5], vals[6], vals[7]);
+  }
+}
+// fp32 [64][64] block -> TF32 tile
+__device__ __forceinline__ void load_tile32(float *t, const float *src, int nrows, int tid) {
+  for (int idx = tid; idx < kC * (kDim / 4); idx += kSeqThreads) {
+    const int r = idx >> 4, c4 = (idx & 15) * 4;
+    float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < nrows) v4 = *reinterpret_cast<const float4 *>(src + (size_t)r * kDim + c4);
+    *reinterpret_cast<float4 *>(t + r * kLd + c4) =
+        make_float4(round_tf32(v4.x), round_tf32(v4.y), round_tf32(v4.z), round_tf32(v4.w));
+  }
+}
+
+// ---- forward: one CTA per batch row, chunks in order ---------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kSeqThreads, 1)
+dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ state,
+                     const float *__restrict__ W, const float *__restrict__ U, T *__restrict__ out,
+                     T *__restrict__ final_state, float *__restrict__ delta, int64_t T_, int64_t nc) {
+  extern __shared__ __align__(16) float sm[];
+  float *Qs = sm, *Ks = Qs + kC * kLd, *Ws = Ks + kC * kLd, *Ds = Ws + kC * kLd, *Ss = Ds + kC * kLd,
+        *As = Ss + kC * kLd;
+  const int64_t b = blockIdx.x;
+  const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
+  const int m0 = 16 * (w & 3), n0 = 32 * (w >> 2);
+
+  // the state: this warp's 16 x 32 tile in accumulator-fragment layout, fp32
+  float S[4][4];
+  {
+    const T *sp = state + (size_t)b * kDim * kDim;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int cc = n0 + 8 * nt + 2 * tq;
+      const float2 lo = Pair<T>::ld(sp + (m0 + g) * kDim + cc), hi = Pair<T>::ld(sp + (m0 + g + 8) * kDim + cc);
+      S[nt][0] = lo.x; S[nt][1] = lo.y; S[nt][2] = hi.x; S[nt][3] = hi.y;
+    }
+  }
+  for (int64_t c = 0; c < nc; ++c) {
+    const int64_t t0 = c * kC;
+    const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
+    const size_t base = ((size_t)b * T_ + t0) * kDim;
+    const size_t tile = ((size_t)b * nc + c) * kC * kDim;
+    load_tile16<T>(Qs, q + base, nvalid, tid);
+    load_tile16<T>(Ks, k + base, nvalid, tid);
+    load_tile32(Ws, W + tile, kC, tid);
+    store_acc(Ss, S, m0, n0, g, tq);
+    __syncthreads();
+
+    float acc[4][4], accO[4][4];
+    // Dl = U - W S^T   (rows t, columns d)
+    zero(acc);
+    gemm64<false, true>(acc, Ws, Ss, m0, n0, g, tq);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int cc = n0 + 8 * nt + 2 * tq;
+      float2 u0 = *reinterpret_cast<const float2 *>(U + tile + (size_t)(m0 + g) * kDim + cc);
+      float2 u1 = *reinterpret_cast<const float2 *>(U + tile + (size_t)(m0 + g + 8) * kDim + cc);
+      acc[nt][0] = u0.x - acc[nt][0]; acc[nt][1] = u0.y - acc[nt][1];
+      acc[nt][2] = u1.x - acc[nt][2]; acc[nt][3] = u1.y - acc[nt][3];
+      if (m0 + g < nvalid)
+        *reinterpret_cast<float2 *>(delta + base + (size_t)(m0 + g) * kDim + cc) = make_float2(acc[nt][0], acc[nt][1]);
+      if (m0 + g + 8 < nvalid)
+        *reinterpret_cast<float2 *>(delta + base + (size_t)(m0 + g + 8) * kDim + cc) = make_float2(acc[nt][2], acc[nt][3]);
+    }
+    // scores A = strict_lower(Q K^T)   (rows t, columns i)
+    float sc[4][4];
+    zero(sc);
+    gemm64<false, true>(sc, Qs, Ks, m0, n0, g, tq);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int cc = n0 + 8 * nt + 2 * tq;
+      sc[nt][0] = (cc < m0 + g) ? sc[nt][0] : 0.f;
+      sc[nt][1] = (cc + 1 < m0 + g) ? sc[nt][1] : 0.f;
+      sc[nt][2] = (cc < m0 + g + 8) ? sc[nt][2] : 0.f;
+      sc[nt][3] = (cc + 1 < m0 + g + 8) ? sc[nt][3] : 0.f;
+    }
+    // O = Q S^T ...
+    zero(accO);
+    gemm64<false, true>(accO, Qs, Ss, m0, n0, g, tq);
+    store_acc(Ds, acc, m0, n0, g, tq);
+    store_acc(As, sc, m0, n0, g, tq);
+    __syncthreads();
+    // ... + A Dl
+    gemm64<false, false>(accO, As, Ds, m0, n0, g, tq);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int cc = n0 + 8 * nt + 2 * tq;
+      if (m0 + g < nvalid) Pair<T>::st(out + base + (size_t)(m0 + g) * kDim + cc, accO[nt][0], accO[nt][1]);
+      if (m0 + g + 8 < nvalid) Pair<T>::st(out + base + (size_t)(m0 + g + 8) * kDim + cc, accO[nt][2], accO[nt][3]);
+    }
+    // S += Dl^T K   (rows d, columns m)
+    gemm64<true, false>(S, Ds, Ks, m0, n0, g, tq);
+    __syncthreads();               // tiles are rewritten by the next chunk
+  }
+  T *fp = final_state + (size_t)b * kDim * kDim;
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    const int cc = n0 + 8 * nt + 2 * tq;
+    Pair<T>::st(fp + (m0 + g) * kDim + cc, S[nt][0], S[nt][1]);
+    Pair<T>::st(fp + (m0 + g + 8) * kDim + cc, S[nt][2], S[nt][3]);
+  }
+}
+
+// ---- backward: one CTA per batch row, chunks in reverse -------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kSeqThreads, 1)
+dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T *__restrict__ q,
+                     const T *__restrict__ k, const float *__restrict__ delta,
+                     const T *__restrict__ final_state, const float *__restrict__ Wb,
+                     const float *__restrict__ Ub, T *__restrict__ dq, T *__restrict__ dk,
+                     T *__restrict__ dv, T *__restrict__ ds, int64_t T_, int64_t nc) {
+  extern __shared__ __align__(16) float sm[];
+  float *Qs = sm, *Ks = Qs + kC * kLd, *Gs = Ks + kC * kLd, *Ds = Gs + kC * kLd, *Ws = Ds + kC * kLd,
+        *Es = Ws + kC * kLd, *Rs = Es + kC * kLd, *Ss = Rs + kC * kLd, *X1s = Ss + kC * kLd,
+        *X2s = X1s + kC * kLd;
+  const int64_t b = blockIdx.x;
+  const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
+  const int m0 = 16 * (w & 3), n0 = 32 * (w >> 2);
+
+  float R[4][4], S[4][4];     // state gradient and state (walked back), fp32 fragments
+  {
+    const T *rp = gs + (size_t)b * kDim * kDim, *sp = final_state + (size_t)b * kDim * kDim;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int cc = n0 + 8 * nt + 2 * tq;
+      float2 lo = Pair<T>::ld(rp + (m0 + g) * kDim + cc), hi = Pair<T>::ld(rp + (m0 + g + 8) * kDim + cc);
+      R[nt][0] = lo.x; R[nt][1] = lo.y; R[nt][2] = hi.x; R[nt][3] = hi.y;
+      lo = Pair<T>::ld(sp + (m0 + g) * kDim + cc); hi = Pair<T>::ld(sp + (m0 + g + 8) * kDim + cc);
+      S[nt][0] = lo.x; S[nt][1] = lo.y; S[nt][2] = hi.x; S[nt][3] = hi.y;
+    }
+  }
+  for (int64_t c = nc - 1; c >= 0; --c) {
+    const int64_t t0 = c * kC;
+    const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
+    const size_t base = ((size_t)b * T_ + t0) * kDim;
+    const size_t tile = ((size_t)b * nc + c) * kC * kDim;
+    load_tile16<T>(Qs, q + base, nvalid, tid);
+    load_tile16<T>(Ks, k + base, nvalid, tid);
+    load_tile16<T>(Gs, go + base, nvalid, tid);
+    load_tile32(Ds, delta + base, nvalid, tid);
+    load_tile32(Ws, Wb + tile, kC, tid);
+    store_acc(Rs, R, m0, n0, g, tq);
+    __syncthreads();
+
+    float acc[4][4], acc2[4][4];
+    // S0 = S_end - Dl^T K
+    zero(acc);
+    gemm64<true, false>(acc, Ds, Ks, m0, n0, g, tq);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) S[nt][e] -= acc[nt][e];
+    store_acc(Ss, S, m0, n0, g, tq);
+    // E = Ub + Wb R_end^T = d_value
+    zero(acc);
+    gemm64<false, true>(acc, Ws, Rs, m0, n0, g, tq);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int cc = n0 + 8 * nt + 2 * tq;
+      const float2 u0 = *reinterpret_cast<const float2 *>(Ub + tile + (size_t)(m0 + g) * kDim + cc);
+      const float2 u1 = *reinterpret_cast<const float2 *>(Ub + tile + (size_t)(m0 + g + 8) * kDim + cc);
+      acc[nt][0] += u0.x; acc[nt][1] += u0.y; acc[nt][2] += u1.x; acc[nt][3] += u1.y;
+      if (m0 + g < nvalid) Pair<T>::st(dv + base + (size_t)(m0 + g) * kDim + cc, acc[nt][0], acc[nt][1]);
+      if (m0 + g + 8 < nvalid) Pair<T>::st(dv + base + (size_t)(m0 + g + 8) * kDim + cc, acc[nt][2], acc[nt][3]);
+    }
+    store_acc(Es, acc, m0, n0, g, tq);
+    // X1 = strict_lower(dO Dl^T)
+    zero(acc);
+    gemm64<false, true>(acc, Gs, Ds, m0, n0, g, tq);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int cc = n0 + 8 * nt + 2 * tq;
+      acc[nt][0] = (cc < m0 + g) ? acc[nt][0] : 0.f;
+      acc[nt][1] = (cc + 1 < m0 + g) ? acc[nt][1] : 0.f;
+      acc[nt][2] = (cc < m0 + g + 8) ? acc[nt][2] : 0.f;
+      acc[nt][3] = (cc + 1 < m0 + g + 8) ? acc[nt][3] : 0.f;
+    }
+    store_acc(X1s, acc, m0, n0, g, tq);
+    __syncthreads();               // S0, E, X1 tiles complete
+
+    // X2 = strict_upper(Dl E^T)
+    zero(acc);
+    gemm64<false, true>(acc, Ds, Es, m0, n0, g, tq);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int cc = n0 + 8 * nt + 2 * tq;
+      acc[nt][0] = (cc > m0 + g) ? acc[nt][0] : 0.f;
+      acc[nt][1] = (cc + 1 > m0 + g) ? acc[nt][1] : 0.f;
+      acc[nt][2] = (cc > m0 + g + 8) ? acc[nt][2] : 0.f;
+      acc[nt][3] = (cc + 1 > m0 + g + 8) ? acc[nt][3] : 0.f;
+    }
+    store_acc(X2s, acc, m0, n0, g, tq);
+    // d_query = dO S0 + X1 K
+    zero(acc);
+    gemm64<false, false>(acc, Gs, Ss, m0, n0, g, tq);
+    gemm64<false, false>(acc, X1s, Ks, m0, n0, g, tq);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int cc = n0 + 8 * nt + 2 * tq;
+      if (m0 + g < nvalid) Pair<T>::st(dq + base + (size_t)(m0 + g) * kDim + cc, acc[nt][0], acc[nt][1]);
+      if (m0 + g + 8 < nvalid) Pair<T>::st(dq + base + (size_t)(m0 + g + 8) * kDim + cc, acc[nt][2], acc[nt][3]);
+    }
+    __syncthreads();               // X2 tile complete
+
+    // d_key = Dl R_end + X1^T Q - (X2 + X2^T) K - E S0
+    zero(acc);
+    gemm64<false, false>(acc, Ds, Rs, m0, n0, g, tq);
+    gemm64<true, false>(acc, X1s, Qs, m0, n0, g, tq);
+    zero(acc2);
+    gemm64<false, false>(acc2, X2s, Ks, m0, n0, g, tq);
+    gemm64<true, false>(acc2, X2s, Ks, m0, n0, g, tq);
+    gemm64<false, false>(acc2, Es, Ss, m0, n0, g, tq);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int cc = n0 + 8 * nt + 2 * tq;
+      if (m0 + g < nvalid)
+        Pair<T>::st(dk + base + (size_t)(m0 + g) * kDim + cc, acc[nt][0] - acc2[nt][0], acc[nt][1] - acc2[nt][1]);
+      if (m0 + g + 8 < nvalid)
+        Pair<T>::st(dk + base + (size_t)(m0 + g + 8) * kDim + cc, acc[nt][2] - acc2[nt][2], acc[nt][3] - acc2[nt][3]);
+    }
+    // R_start = R_end + dO^T Q - E^T K
+    gemm64<true, false>(R, Gs, Qs, m0, n0, g, tq);
+    zero(acc2);
+    gemm64<true, false>(acc2, Es, Ks, m0, n0, g, tq);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) R[nt][e] -= acc2[nt][e];
+    __syncthreads();               // tiles are rewritten by the next chunk
+  }
+  T *dp = ds + (size_t)b * kDim * kDim;
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    const int cc = n0 + 8 * nt + 2 * tq;
+    Pair<T>::st(dp + (m0 + g) * kDim + cc, R[nt][0], R[nt][1]);
+    Pair<T>::st(dp + (m0 + g + 8) * kDim + cc, R[nt][2], R[nt][3]);
+  }
+}
+
+constexpr size_t kTileBytes = (size_t)kC * kLd * sizeof(float);
+constexpr size_t kPrepTile = (size_t)kC * kLdS * sizeof(float);
+
+inline size_t wu_floats(int64_t B, int64_t nc) { return (size_t)B * nc * kC * kDim; }
+
+}  // namespace
+
+bool dfw_chunk_supported(int64_t D, int64_t M, int dtype) {
+  return D == kDim && M == kDim && (dtype == T2FW_F16 || dtype == T2FW_BF16);
+}
+
+// W and U (forward) or Wb and Ub (backward): two fp32 [B][n_chunks][64][64] arrays
+size_t dfw_chunk_scratch_bytes(int64_t B, int64_t T_) {
+  return align_up(2 * wu_floats(B, ceil_div64(T_, kC)) * sizeof(float), 256);
+}
+
+template <typename T>
+static int dfw_chunk_forward_typed(const void *q, const void *k, const void *v, const void *state, void *out,
+                                   void *final_state, void *delta, int64_t B, int64_t T_, void *scratch,
+                                   cudaStream_t st) {
+  const int64_t nc = ceil_div64(T_, kC);
+  float *W = static_cast<float *>(scratch), *U = W + wu_floats(B, nc);
+  T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_prep_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(3 * kPrepTile)));
+  dfw_chunk_prep_kernel<T, false><<<(unsigned)(B * nc), 128, 3 * kPrepTile, st>>>(
+      (const T *)q, (const T *)k, (const T *)v, W, U, T_, nc);
+  T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_fwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(6 * kTileBytes)));
+  dfw_chunk_fwd_kernel<T><<<(unsigned)B, kSeqThreads, 6 * kTileBytes, st>>>(
+      (const T *)q, (const T *)k, (const T *)state, W, U, (T *)out, (T *)final_state, (float *)delta, T_, nc);
+  T2FW_CHECK_LAUNCH(2);
+  return T2FW_OK;
+}
+
+int dfw_chunk_forward(const void *q, const void *k, const void *v, const void *state, void *out,
+                      void *final_state, void *delta, int64_t B, int64_t T_, int dtype, void *scratch,
+                      cudaStream_t st) {
+  if (dtype == T2FW_F16)
+    return dfw_chunk_forward_typed<__half>(q, k, v, state, out, final_state, delta, B, T_, scratch, st);
+  return dfw_chunk_forward_typed<__nv_bfloat16>(q, k, v, state, out, final_state, delta, B, T_, scratch, st);
+}
+
+template <typename T>
+static int dfw_chunk_backward_typed(const void *go, const void *gs, const void *q, const void *k,
+                                    const void *delta, const void *final_state, void *dq, void *dk, void *dv,
+                                    void *ds, int64_t B, int64_t T_, void *scratch, cudaStream_t st) {
+  const int64_t nc = ceil_div64(T_, kC);
+  float *Wb = static_cast<float *>(scratch), *Ub = Wb + wu_floats(B, nc);
+  T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_prep_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(4 * kPrepTile)));
+  dfw_chunk_prep_kernel<T, true><<<(unsigned)(B * nc), 128, 4 * kPrepTile, st>>>(
+      (const T *)q, (const T *)k, (const T *)go, Wb, Ub, T_, nc);
+  T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(10 * kTileBytes)));
+  dfw_chunk_bwd_kernel<T><<<(unsigned)B, kSeqThreads, 10 * kTileBytes, st>>>(
+      (const T *)go, (const T *)gs, (const T *)q, (const T *)k, (const float *)delta, (const T *)final_state, Wb,
+      Ub, (T *)dq, (T *)dk, (T *)dv, (T *)ds, T_, nc);
+  T2FW_CHECK_LAUNCH(2);
+  return T2FW_OK;
+}
+
+int dfw_chunk_backward(const void *go, const void *gs, const void *q, const void *k, const void *delta,
+                       const void *final_state, void *dq, void *dk, void *dv, void *ds, int64_t B, int64_t T_,
+                       int dtype, void *scratch, cudaStream_t st) {
+  if (dtype == T2FW_F16)
+    return dfw_chunk_backward_typed<__half>(go, gs, q, k, delta, final_state, dq, dk, dv, ds, B, T_, scratch, st);
+  return dfw_chunk_backward_typed<__nv_bfloat16>(go, gs, q, k, delta, final_state, dq, dk, dv, ds, B, T_, scratch,
+                                                 st);
+}
+
+}  // namespace t2fw

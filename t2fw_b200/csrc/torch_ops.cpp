@@ -157,9 +157,13 @@ std::vector<at::Tensor> dfw_forward(at::Tensor query, at::Tensor key, at::Tensor
   at::Tensor final_state = at::empty_like(state);
   at::Tensor delta = at::empty({B, T, D}, value.options().dtype(acc_type(value)));
   auto stream = at::cuda::getCurrentCUDAStream();
-  check_status(t2fw_dfw_forward(query.data_ptr(), key.data_ptr(), value.data_ptr(),
-                                state.data_ptr(), outputs.data_ptr(), final_state.data_ptr(),
-                                delta.data_ptr(), B, T, D, M, dt, stream.stream()),
+  const size_t sb = t2fw_dfw_forward_scratch_bytes(B, T, D, M, dt);
+  at::Tensor scratch;
+  if (sb) scratch = at::empty({(int64_t)sb}, value.options().dtype(at::kByte));
+  check_status(t2fw_dfw_forward_ws(query.data_ptr(), key.data_ptr(), value.data_ptr(),
+                                   state.data_ptr(), outputs.data_ptr(), final_state.data_ptr(),
+                                   delta.data_ptr(), B, T, D, M, dt, sb ? scratch.data_ptr() : nullptr, sb,
+                                   stream.stream()),
                "dfw.forward");
   return {outputs, final_state, delta};
 }

@@ -99,3 +99,34 @@ def test_autograd_wrapper(cuda):
     assert torch.equal(out, out2) and torch.equal(fin, fin2)
     for a, b in zip(grads, grads2):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,T,keys,state_std", [
+    (3, 1, "scaled", 0.5), (2, 37, "scaled", 0.3), (2, 64, "softmax", 1.0), (3, 129, "scaled", 0.1),
+    (2, 200, "softmax", 0.5), (1, 1000, "scaled", 0.0), (2, 1024, "softmax", 0.2)])
+def test_chunked_path_lengths(cuda, dtype, B, T, keys, state_std):
+    """D = M = 64 in 16-bit storage runs on the chunked tensor-core kernels: whole and partial
+    chunks, sequences shorter than a chunk, non-zero initial state, both key distributions."""
+    cpu = dfw_inputs(B, T, 64, 64, keys, state_std, 20 + T)
+    dev = to_dev(cpu, dtype, cuda)
+    got = run_cabi(*dev)
+    assert all(torch.isfinite(t).all() for t in (got[0], got[1], *got[2]))
+    check_against_oracle(dev, got, dtype)
+
+
+def test_scan_forward_pairs_with_chunked_backward(cuda):
+    """The scratch-free forward (scan kernels) and the forward with scratch (chunked kernels) save
+    the same delta, so either can feed the backward."""
+    from t2fw_b200 import cabi
+
+    cpu = dfw_inputs(2, 300, 64, 64, "scaled", 0.2, 31)
+    dev = to_dev(cpu, torch.float16, cuda)
+    q, k, v, s, go, gs = dev
+    out_a, fin_a, delta_a = cabi.dfw_forward(q, k, v, s, use_scratch=False)
+    out_b, fin_b, delta_b = cabi.dfw_forward(q, k, v, s)
+    assert max_rel_err(out_b, out_a) <= 2e-3 and max_rel_err(fin_b, fin_a) <= 2e-3
+    assert max_rel_err(delta_b, delta_a) <= 2e-3
+    grads = cabi.dfw_backward(go, gs, q, k, delta_a, fin_a)
+    torch.cuda.synchronize()
+    check_against_oracle(dev, (out_a, fin_a, grads), torch.float16)
