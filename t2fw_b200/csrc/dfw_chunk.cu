@@ -32,22 +32,58 @@ using namespace chunk;
 
 namespace {
 
-constexpr int kLdS = 65;          // row stride of the prep kernel's fp32 tiles (conflict-free columns)
-constexpr int kSeqThreads = 256;  // 8 warps: warp w owns rows 16*(w&3), columns 32*(w>>2) of a product
+constexpr int kSeqThreads = 512;  // 16 warps: warp w owns rows 16*(w&3), columns 16*(w>>2) of a product
+constexpr int kNT = 2;            // 8-column accumulator tiles per warp
 
 // ---- prep: W, U (forward) or Wb, Ub (backward) --------------------------------------------------
-// grid = B * nc, 128 threads.  Output tiles are fp32 [64][64] row-major, rows beyond the end of
-// the sequence are zero.
+// grid = B * nc, 128 threads (4 warps).  Output tiles are fp32 [64][64] row-major, rows beyond the
+// end of the sequence are zero.  The Gram matrices K K^T and K Q^T come from the tensor cores and
+// are exact up to fp32 summation order (16-bit inputs are exactly representable in TF32); the
+// triangular solves run in fp32 on CUDA cores, one thread per right-hand-side column.
+// warp w owns rows 16*w .. +15 of a 64 x 64 product
+template <bool BT>
+__device__ __forceinline__ void prep_gemm(float (&acc)[8][4], const float *tA, const float *tB, int m0, int g,
+                                          int tq) {
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+#pragma unroll 2
+  for (int k0 = 0; k0 < kC; k0 += 8) {
+    uint32_t a[4];
+    lda(a, tA, kLd, m0, k0, g, tq);
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      uint32_t bf[2];
+      if (BT) ldb_t(bf, tB, kLd, k0, 8 * nt, g, tq); else ldb(bf, tB, kLd, k0, 8 * nt, g, tq);
+      mma_tf32(acc[nt], a, bf);
+    }
+  }
+}
+// mode 0: store as is; 1: keep column > row, TF32-rounded (feeds an MMA)
+template <int MODE>
+__device__ __forceinline__ void prep_store(float *t, const float (&acc)[8][4], int m0, int g, int tq) {
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+    const int cc = 8 * nt + 2 * tq, r0 = m0 + g, r1 = m0 + g + 8;
+    float v0 = acc[nt][0], v1 = acc[nt][1], v2 = acc[nt][2], v3 = acc[nt][3];
+    if (MODE == 1) {
+      v0 = (cc > r0) ? round_tf32(v0) : 0.f; v1 = (cc + 1 > r0) ? round_tf32(v1) : 0.f;
+      v2 = (cc > r1) ? round_tf32(v2) : 0.f; v3 = (cc + 1 > r1) ? round_tf32(v3) : 0.f;
+    }
+    *reinterpret_cast<float2 *>(t + r0 * kLd + cc) = make_float2(v0, v1);
+    *reinterpret_cast<float2 *>(t + r1 * kLd + cc) = make_float2(v2, v3);
+  }
+}
+
 template <typename T, bool kBwd>
 __global__ void __launch_bounds__(128)
 dfw_chunk_prep_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v_or_go,
                       float *__restrict__ Wout, float *__restrict__ Uout, int64_t T_, int64_t nc) {
   extern __shared__ __align__(16) float sm[];
-  float *Ks = sm, *Ls = Ks + kC * kLdS, *Vs = Ls + kC * kLdS, *Qs = Vs + kC * kLdS;   // Qs: backward only
+  float *Ks = sm, *Ls = Ks + kC * kLd, *Vs = Ls + kC * kLd, *Qs = Vs + kC * kLd;   // Qs: backward only
   const int64_t b = blockIdx.x / nc, c = blockIdx.x % nc, t0 = c * kC;
   const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
   const size_t base = ((size_t)b * T_ + t0) * kDim;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
 
   for (int idx = tid; idx < kC * (kDim / 2); idx += 128) {
     const int r = idx / (kDim / 2), c2 = (idx % (kDim / 2)) * 2;
@@ -57,70 +93,60 @@ dfw_chunk_prep_kernel(const T *__restrict__ q, const T *__restrict__ k, const T 
       vv = Pair<T>::ld(v_or_go + base + (size_t)r * kDim + c2);
       if (kBwd) qq = Pair<T>::ld(q + base + (size_t)r * kDim + c2);
     }
-    Ks[r * kLdS + c2] = kk.x; Ks[r * kLdS + c2 + 1] = kk.y;
-    Vs[r * kLdS + c2] = vv.x; Vs[r * kLdS + c2 + 1] = vv.y;
-    if (kBwd) { Qs[r * kLdS + c2] = qq.x; Qs[r * kLdS + c2 + 1] = qq.y; }
+    *reinterpret_cast<float2 *>(Ks + r * kLd + c2) = kk;
+    *reinterpret_cast<float2 *>(Vs + r * kLd + c2) = vv;
+    if (kBwd) *reinterpret_cast<float2 *>(Qs + r * kLd + c2) = qq;
   }
   __syncthreads();
 
-  // Ls[t][s] = k_t . k_s  (forward: used for s < t; backward: for s > t; symmetric, so all of it)
-  for (int idx = tid; idx < kC * kC; idx += 128) {
-    const int t = idx / kC, s = idx % kC;
-    float acc = 0.f;
-#pragma unroll 16
-    for (int m = 0; m < kDim; ++m) acc = fmaf(Ks[t * kLdS + m], Ks[s * kLdS + m], acc);
-    Ls[t * kLdS + s] = acc;
-  }
+  float acc[8][4];
+  // Ls[t][s] = k_t . k_s  (forward uses s < t, backward s > t)
+  prep_gemm<true>(acc, Ks, Ks, 16 * w, g, tq);
+  prep_store<0>(Ls, acc, 16 * w, g, tq);
   if (kBwd) {
-    // right-hand side of the d side: rhs[t][d] = sum_{s>t} (k_t . q_s) dO[s][d]; first the scores
-    // into registers is too much state, so they go through shared memory in place of Q
+    // right-hand side of the d side: rhs[t][d] = sum_{s>t} (k_t . q_s) dO[s][d]
+    prep_gemm<true>(acc, Ks, Qs, 16 * w, g, tq);
+    __syncthreads();                         // every warp has read Q
+    prep_store<1>(Qs, acc, 16 * w, g, tq);   // strict upper part of K Q^T
     __syncthreads();
-    float sc[32];        // this thread's 32 scores: entries idx = tid + 128*j
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const int idx = tid + 128 * j, t = idx / kC, s = idx % kC;
-      float acc = 0.f;
-      if (s > t) {
-#pragma unroll 16
-        for (int m = 0; m < kDim; ++m) acc = fmaf(Ks[t * kLdS + m], Qs[s * kLdS + m], acc);
-      }
-      sc[j] = acc;
-    }
-    __syncthreads();     // every thread has read Q
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const int idx = tid + 128 * j;
-      Qs[(idx / kC) * kLdS + idx % kC] = sc[j];
-    }
+    prep_gemm<false>(acc, Qs, Vs, 16 * w, g, tq);
+    __syncthreads();                         // every warp has read the scores
+    prep_store<0>(Qs, acc, 16 * w, g, tq);   // rhs
   }
   __syncthreads();
 
   // substitution: thread = one column of [K | V] (forward) or [K | rhs] (backward)
   const int col = tid & 63;
   const bool second = tid >= 64;
+  const float *rhs = second ? (kBwd ? Qs : Vs) : Ks;
   float x[kC];
   if (!kBwd) {
 #pragma unroll
     for (int t = 0; t < kC; ++t) {
-      float acc = second ? Vs[t * kLdS + col] : Ks[t * kLdS + col];
+      float a0 = rhs[t * kLd + col], a1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < t; ++i) acc = fmaf(-Ls[t * kLdS + i], x[i], acc);
-      x[t] = acc;
+      for (int i4 = 0; i4 < t; i4 += 4) {
+        const float4 l4 = *reinterpret_cast<const float4 *>(Ls + t * kLd + i4);
+        a0 = fmaf(-l4.x, x[i4], a0);
+        if (i4 + 1 < t) a1 = fmaf(-l4.y, x[i4 + 1], a1);
+        if (i4 + 2 < t) a0 = fmaf(-l4.z, x[i4 + 2], a0);
+        if (i4 + 3 < t) a1 = fmaf(-l4.w, x[i4 + 3], a1);
+      }
+      x[t] = a0 + a1;
     }
   } else {
 #pragma unroll
     for (int t = kC - 1; t >= 0; --t) {
-      float acc;
-      if (second) {
-        acc = 0.f;
+      float a0 = rhs[t * kLd + col], a1 = 0.f;
 #pragma unroll
-        for (int s = t + 1; s < kC; ++s) acc = fmaf(Qs[t * kLdS + s], Vs[s * kLdS + col], acc);
-      } else {
-        acc = Ks[t * kLdS + col];
+      for (int s4 = ((t + 1) & ~3); s4 < kC; s4 += 4) {
+        const float4 l4 = *reinterpret_cast<const float4 *>(Ls + t * kLd + s4);
+        if (s4 > t) a0 = fmaf(-l4.x, x[s4], a0);
+        if (s4 + 1 > t) a1 = fmaf(-l4.y, x[s4 + 1], a1);
+        if (s4 + 2 > t) a0 = fmaf(-l4.z, x[s4 + 2], a0);
+        if (s4 + 3 > t) a1 = fmaf(-l4.w, x[s4 + 3], a1);
       }
-#pragma unroll
-      for (int s = t + 1; s < kC; ++s) acc = fmaf(-Ls[t * kLdS + s], x[s], acc);
-      x[t] = acc;
+      x[t] = a0 + a1;
     }
   }
   float *dst = (second ? Uout : Wout) + (size_t)blockIdx.x * kC * kDim + col;
@@ -132,28 +158,28 @@ dfw_chunk_prep_kernel(const T *__restrict__ q, const T *__restrict__ k, const T 
 // acc[nt][.] (rows m0 + {g, g+8}, columns n0 + 8*nt + {2tq, 2tq+1}) += A * B over a contraction of 64.
 //   AT: the tile holds A transposed (A[m][k] = tA[k][m]);  BT: the tile holds B as [n][k]
 template <bool AT, bool BT>
-__device__ __forceinline__ void gemm64(float (&acc)[4][4], const float *tA, const float *tB, int m0, int n0,
+__device__ __forceinline__ void gemm64(float (&acc)[kNT][4], const float *tA, const float *tB, int m0, int n0,
                                        int g, int tq) {
 #pragma unroll 2
   for (int k0 = 0; k0 < kC; k0 += 8) {
     uint32_t a[4];
     if (AT) lda_t(a, tA, kLd, m0, k0, g, tq); else lda(a, tA, kLd, m0, k0, g, tq);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < kNT; ++nt) {
       uint32_t bf[2];
       if (BT) ldb_t(bf, tB, kLd, k0, n0 + 8 * nt, g, tq); else ldb(bf, tB, kLd, k0, n0 + 8 * nt, g, tq);
       mma_tf32(acc[nt], a, bf);
     }
   }
 }
-__device__ __forceinline__ void zero(float (&acc)[4][4]) {
+__device__ __forceinline__ void zero(float (&acc)[kNT][4]) {
 #pragma unroll
-  for (int nt = 0; nt < 4; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+  for (int nt = 0; nt < kNT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 }
 // accumulator fragment -> fp32 tile (values rounded to TF32 so that the tile can feed an MMA)
-__device__ __forceinline__ void store_acc(float *t, const float (&acc)[4][4], int m0, int n0, int g, int tq) {
+__device__ __forceinline__ void store_acc(float *t, const float (&acc)[kNT][4], int m0, int n0, int g, int tq) {
 #pragma unroll
-  for (int nt = 0; nt < 4; ++nt) {
+  for (int nt = 0; nt < kNT; ++nt) {
     const int cc = n0 + 8 * nt + 2 * tq;
     *reinterpret_cast<float2 *>(t + (m0 + g) * kLd + cc) = make_float2(round_tf32(acc[nt][0]), round_tf32(acc[nt][1]));
     *reinterpret_cast<float2 *>(t + (m0 + g + 8) * kLd + cc) = make_float2(round_tf32(acc[nt][2]), round_tf32(acc[nt][3]));
@@ -204,14 +230,14 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
         *As = Ss + kC * kLd;
   const int64_t b = blockIdx.x;
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
-  const int m0 = 16 * (w & 3), n0 = 32 * (w >> 2);
+  const int m0 = 16 * (w & 3), n0 = 8 * kNT * (w >> 2);
 
   // the state: this warp's 16 x 32 tile in accumulator-fragment layout, fp32
-  float S[4][4];
+  float S[kNT][4];
   {
     const T *sp = state + (size_t)b * kDim * kDim;
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
       const float2 lo = Pair<T>::ld(sp + (m0 + g) * kDim + cc), hi = Pair<T>::ld(sp + (m0 + g + 8) * kDim + cc);
       S[nt][0] = lo.x; S[nt][1] = lo.y; S[nt][2] = hi.x; S[nt][3] = hi.y;
@@ -228,12 +254,12 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
     store_acc(Ss, S, m0, n0, g, tq);
     __syncthreads();
 
-    float acc[4][4], accO[4][4];
+    float acc[kNT][4], accO[kNT][4];
     // Dl = U - W S^T   (rows t, columns d)
     zero(acc);
     gemm64<false, true>(acc, Ws, Ss, m0, n0, g, tq);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
       float2 u0 = *reinterpret_cast<const float2 *>(U + tile + (size_t)(m0 + g) * kDim + cc);
       float2 u1 = *reinterpret_cast<const float2 *>(U + tile + (size_t)(m0 + g + 8) * kDim + cc);
@@ -245,11 +271,11 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
         *reinterpret_cast<float2 *>(delta + base + (size_t)(m0 + g + 8) * kDim + cc) = make_float2(acc[nt][2], acc[nt][3]);
     }
     // scores A = strict_lower(Q K^T)   (rows t, columns i)
-    float sc[4][4];
+    float sc[kNT][4];
     zero(sc);
     gemm64<false, true>(sc, Qs, Ks, m0, n0, g, tq);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
       sc[nt][0] = (cc < m0 + g) ? sc[nt][0] : 0.f;
       sc[nt][1] = (cc + 1 < m0 + g) ? sc[nt][1] : 0.f;
@@ -265,7 +291,7 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
     // ... + A Dl
     gemm64<false, false>(accO, As, Ds, m0, n0, g, tq);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
       if (m0 + g < nvalid) Pair<T>::st(out + base + (size_t)(m0 + g) * kDim + cc, accO[nt][0], accO[nt][1]);
       if (m0 + g + 8 < nvalid) Pair<T>::st(out + base + (size_t)(m0 + g + 8) * kDim + cc, accO[nt][2], accO[nt][3]);
@@ -276,7 +302,7 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
   }
   T *fp = final_state + (size_t)b * kDim * kDim;
 #pragma unroll
-  for (int nt = 0; nt < 4; ++nt) {
+  for (int nt = 0; nt < kNT; ++nt) {
     const int cc = n0 + 8 * nt + 2 * tq;
     Pair<T>::st(fp + (m0 + g) * kDim + cc, S[nt][0], S[nt][1]);
     Pair<T>::st(fp + (m0 + g + 8) * kDim + cc, S[nt][2], S[nt][3]);
@@ -297,13 +323,13 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
         *X2s = X1s + kC * kLd;
   const int64_t b = blockIdx.x;
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
-  const int m0 = 16 * (w & 3), n0 = 32 * (w >> 2);
+  const int m0 = 16 * (w & 3), n0 = 8 * kNT * (w >> 2);
 
-  float R[4][4], S[4][4];     // state gradient and state (walked back), fp32 fragments
+  float R[kNT][4], S[kNT][4];     // state gradient and state (walked back), fp32 fragments
   {
     const T *rp = gs + (size_t)b * kDim * kDim, *sp = final_state + (size_t)b * kDim * kDim;
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
       float2 lo = Pair<T>::ld(rp + (m0 + g) * kDim + cc), hi = Pair<T>::ld(rp + (m0 + g + 8) * kDim + cc);
       R[nt][0] = lo.x; R[nt][1] = lo.y; R[nt][2] = hi.x; R[nt][3] = hi.y;
@@ -324,12 +350,12 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
     store_acc(Rs, R, m0, n0, g, tq);
     __syncthreads();
 
-    float acc[4][4], acc2[4][4];
+    float acc[kNT][4], acc2[kNT][4];
     // S0 = S_end - Dl^T K
     zero(acc);
     gemm64<true, false>(acc, Ds, Ks, m0, n0, g, tq);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
+    for (int nt = 0; nt < kNT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) S[nt][e] -= acc[nt][e];
     store_acc(Ss, S, m0, n0, g, tq);
@@ -337,7 +363,7 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
     zero(acc);
     gemm64<false, true>(acc, Ws, Rs, m0, n0, g, tq);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
       const float2 u0 = *reinterpret_cast<const float2 *>(Ub + tile + (size_t)(m0 + g) * kDim + cc);
       const float2 u1 = *reinterpret_cast<const float2 *>(Ub + tile + (size_t)(m0 + g + 8) * kDim + cc);
@@ -350,7 +376,7 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
     zero(acc);
     gemm64<false, true>(acc, Gs, Ds, m0, n0, g, tq);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
       acc[nt][0] = (cc < m0 + g) ? acc[nt][0] : 0.f;
       acc[nt][1] = (cc + 1 < m0 + g) ? acc[nt][1] : 0.f;
@@ -364,7 +390,7 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
     zero(acc);
     gemm64<false, true>(acc, Ds, Es, m0, n0, g, tq);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
       acc[nt][0] = (cc > m0 + g) ? acc[nt][0] : 0.f;
       acc[nt][1] = (cc + 1 > m0 + g) ? acc[nt][1] : 0.f;
@@ -377,7 +403,7 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
     gemm64<false, false>(acc, Gs, Ss, m0, n0, g, tq);
     gemm64<false, false>(acc, X1s, Ks, m0, n0, g, tq);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
       if (m0 + g < nvalid) Pair<T>::st(dq + base + (size_t)(m0 + g) * kDim + cc, acc[nt][0], acc[nt][1]);
       if (m0 + g + 8 < nvalid) Pair<T>::st(dq + base + (size_t)(m0 + g + 8) * kDim + cc, acc[nt][2], acc[nt][3]);
@@ -393,7 +419,7 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
     gemm64<true, false>(acc2, X2s, Ks, m0, n0, g, tq);
     gemm64<false, false>(acc2, Es, Ss, m0, n0, g, tq);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
       if (m0 + g < nvalid)
         Pair<T>::st(dk + base + (size_t)(m0 + g) * kDim + cc, acc[nt][0] - acc2[nt][0], acc[nt][1] - acc2[nt][1]);
@@ -405,14 +431,14 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
     zero(acc2);
     gemm64<true, false>(acc2, Es, Ks, m0, n0, g, tq);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
+    for (int nt = 0; nt < kNT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) R[nt][e] -= acc2[nt][e];
     __syncthreads();               // tiles are rewritten by the next chunk
   }
   T *dp = ds + (size_t)b * kDim * kDim;
 #pragma unroll
-  for (int nt = 0; nt < 4; ++nt) {
+  for (int nt = 0; nt < kNT; ++nt) {
     const int cc = n0 + 8 * nt + 2 * tq;
     Pair<T>::st(dp + (m0 + g) * kDim + cc, R[nt][0], R[nt][1]);
     Pair<T>::st(dp + (m0 + g + 8) * kDim + cc, R[nt][2], R[nt][3]);
@@ -420,7 +446,7 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
 }
 
 constexpr size_t kTileBytes = (size_t)kC * kLd * sizeof(float);
-constexpr size_t kPrepTile = (size_t)kC * kLdS * sizeof(float);
+constexpr size_t kPrepTile = kTileBytes;
 
 inline size_t wu_floats(int64_t B, int64_t nc) { return (size_t)B * nc * kC * kDim; }
 
