@@ -42,6 +42,8 @@ WORKLOADS = {
     "decode": (4096, 1, 64, 64),     # T=1 decode step, GPT-2-medium heads x batch 256
     "long": (16, 16384, 128, 128),   # long-sequence prefill + backward
     "dfw": (96, 1024, 64, 64),       # delta rule (DFWFunction), GPT-2-small shape, fwd + bwd
+    "gpt2": (96, 1024, 64, 64),      # GPT-2-small, every attention replaced by a fast-weight layer:
+                                     # batch 8 x 12 heads per GPU, whole training step (run_gpt2)
 }
 CPU_SAMPLE_ROWS = {"train": 16, "decode": 4096, "long": 1, "dfw": 16}
 
@@ -57,6 +59,8 @@ def parse_args():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--rule", default="dfw", choices=["dfw", "lfw"],
+                   help="recurrence inside the gpt2 workload's attention replacement")
     p.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                    help="replay the K timed steps as one CUDA graph (auto: on)")
     return p.parse_args()
@@ -212,9 +216,129 @@ def cpu_reference_run(workload, gates, steps, warmup, seed):
     return value, desc
 
 
+def run_gpt2(args):
+    """BASELINE config 5: GPT-2-small (12 layers, d_model 768, 12 heads, 124 M parameters, random
+    init), every attention replaced by a fast-weight layer, fp16, sequence 1024, batch 8 per GPU,
+    random token ids; one step = forward + backward + DDP gradient all-reduce + AdamW update."""
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the kernels have no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from t2fw_b200 import _lib
+    from t2fw_b200.gpt2_fw import GPT2FW, GPT2FWConfig
+    from t2fw_b200.parallel import job_throughput, max_over_ranks
+
+    lib = _lib.load_core()
+    torch.manual_seed(args.seed)                       # same initial weights on every rank
+    cfg = GPT2FWConfig(rule=args.rule)
+    model = GPT2FW(cfg).half().to(dev)
+    n_params = model.n_params()
+    net = model
+    if world > 1:
+        net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_as_bucket_view=True)
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-4, eps=1e-4, fused=True)
+    bsz, T = 8, cfg.n_positions
+    g = torch.Generator().manual_seed(args.seed + 1 + rank)
+    host_ids = [torch.randint(0, cfg.vocab_size, (bsz, T + 1), generator=g).pin_memory() for _ in range(4)]
+    dev_ids = [h.to(dev) for h in host_ids]
+
+    def step(ids):
+        loss = net(ids[:, :-1], targets=ids[:, 1:])
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    first = None
+    for i in range(args.warmup):
+        loss = step(dev_ids[i % 4])
+        first = float(loss.detach()) if first is None else first
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.t2fw_launch_count()
+    t0, t1 = ev(), ev()
+    t0.record()
+    for i in range(args.steps):
+        loss = step(dev_ids[(args.warmup + i) % 4])
+    t1.record()
+    barrier()
+    launches = lib.t2fw_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = max_over_ranks(t0.elapsed_time(t1), dev)
+    value = job_throughput(bsz * T * args.steps, world, total_ms)
+    last = float(loss.detach())
+
+    # end to end: token ids come from pinned host memory and the loss is read back every step
+    e2e_steps = max(3, min(args.steps, 10))
+    e0, e1 = ev(), ev()
+    barrier()
+    e0.record()
+    for i in range(e2e_steps):
+        ids = host_ids[i % 4].to(dev, non_blocking=True)
+        loss_host = step(ids).item()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1), dev)
+    e2e = {"value": bsz * T * e2e_steps * world / (e2e_ms * 1e-3), "unit": "tokens/s",
+           "h2d_bytes_per_step": host_ids[0].numel() * 8, "d2h_bytes_per_step": 4, "steps": e2e_steps,
+           "ms_per_step": e2e_ms / e2e_steps, "api": "GPT2FW forward + loss.backward() + AdamW step"}
+    if rank != 0:
+        dist.destroy_process_group()
+        return
+    flops = 6.0 * n_params * bsz * T                      # matrix-multiply work of the dense layers
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            peak, peak_kind = float(json.load(fh)["bf16_tflops_sustained"]), "measured sustained cuBLAS bf16"
+    except Exception:
+        peak, peak_kind = 1400.0, "fallback sustained cuBLAS bf16"
+    ms = total_ms / args.steps
+    achieved = flops / (ms * 1e-3) / 1e12
+    line = {
+        "metric": "gpt2_small_fw_train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 parameters and activations, f32 recurrence state",
+        "data": "synthetic",
+        "config": {"workload": "gpt2: GPT-2-small (12 layers, d_model 768, 12 heads, %.1f M parameters, random init), "
+                               "every attention replaced by a %s layer, seq 1024, batch 8 per GPU, uniform random "
+                               "token ids; forward + backward + AdamW" % (n_params / 1e6, args.rule.upper()),
+                   "parallelism": "dp%d (DistributedDataParallel, NCCL all-reduce of gradients)" % world,
+                   "l2": "activations of a step (several GB) are larger than L2",
+                   "loss_first": first, "loss_last": last},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "whole training step, counted as 6 x parameters x tokens dense FLOPs"},
+        "cpu_baseline": None,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
+        return
+    if args.workload == "gpt2":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference ships no model: BASELINE "
+                          "config 5 has no reference implementation and no CPU baseline"}))
         return
     steps = max(1, min(args.steps, 5))
     warmup = max(2, min(args.warmup, 3))
@@ -539,6 +663,8 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "gpt2":
+        run_gpt2(args)
     else:
         run_ours(args)
 
