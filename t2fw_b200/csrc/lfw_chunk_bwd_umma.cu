@@ -75,7 +75,7 @@ constexpr int kCG = umma::kColGroupBytes16;                // 144
 constexpr int kTile = umma::tile16_bytes(kDim, kDim);      // 9216
 constexpr int kRGs = umma::tile16_row_group_bytes(kSub);   // 288
 constexpr int kTileS = umma::tile16_bytes(kSub, kSub);     // 576
-constexpr int kStgLd = 72;      // elements per row of the 16-bit output staging tiles
+constexpr int kStgLd = 64;      // dense rows: a staging tile leaves as one bulk copy
 constexpr int kStgBytes = 5 * kSub * kStgLd * 2;
 constexpr int kFixCap = 64;     // tiny-gate entries per sub-block
 constexpr float kTinyGate = 9.765625e-4f;   // 2^-10
@@ -616,6 +616,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
             s1[lr * kStgLd + feat] = (T)o2[j];
             s2[lr * kStgLd + feat] = (T)(H * pprev * rg[j]);
           }
+          umma::fence_async_smem();      // the staging tiles are read by the bulk-copy engine
           umma::fence_before_sync();
           __threadfence_block();
           bar_arrive(kBarB + (I & 1), kTAll);
@@ -691,6 +692,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
             for (int sft = 8; sft > 0; sft >>= 1) mn += __shfl_xor_sync(0xffffffffu, mn, sft);
             if (lane == 0) atomicAdd(&fix_val[(I & 1) * kFixCap + e], mn);
           }
+          if (ht == 0) acp::bulk_wait_read<0>();   // the earlier write-outs have left shared memory
           __threadfence_block();
           bar_arrive(kBarY, kTAll);
           PROFH(2);
@@ -706,24 +708,35 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
                 (T)(fix_val[(J & 1) * kFixCap + ht] * fix_rg[J * kFixCap + ht]);
             fix_val[(J & 1) * kFixCap + ht] = 0.f;      // ready for the next accumulation
           }
-          if (n_fix > 0) umma::named_barrier(kBarH, 32 * kHelpers);
-          // ---- coalesced write of the five 16 x 64 result tiles --------------------------------
-          T *dst[5] = {dq, dk, dfk, dx, df};
-          const int rJ = kSub * J;
-          for (int idx = ht; idx < 5 * kSub * 8; idx += 32 * kHelpers) {
-            const int it = idx >> 7, r = (idx >> 3) & 15, ch = idx & 7;
-            if (rJ + r < nvalid) {
-              const uint4 val = *reinterpret_cast<const uint4 *>(stg + (it * kSub + r) * kStgLd + ch * 8);
-              *reinterpret_cast<uint4 *>(dst[it] + base + (size_t)(rJ + r) * kDim + ch * 8) = val;
+          if (n_fix > 0) {
+            umma::fence_async_smem();
+            umma::named_barrier(kBarH, 32 * kHelpers);
+          }
+          // ---- the five 16 x 64 result tiles leave as one bulk copy each (rows are contiguous
+          //      both in the staging buffer and in the [T][64] output arrays)
+          if (ht == 0) {
+            const int rJ = kSub * J;
+            const int rows = nvalid - rJ < kSub ? nvalid - rJ : kSub;
+            if (rows > 0) {
+              const uint32_t bytes = (uint32_t)rows * kDim * sizeof(T);
+              const size_t o = base + (size_t)rJ * kDim;
+              acp::bulk_s2g(dq + o, stg, bytes);
+              acp::bulk_s2g(dk + o, stg + kSub * kStgLd, bytes);
+              acp::bulk_s2g(dfk + o, stg + 2 * kSub * kStgLd, bytes);
+              acp::bulk_s2g(dx + o, stg + 3 * kSub * kStgLd, bytes);
+              acp::bulk_s2g(df + o, stg + 4 * kSub * kStgLd, bytes);
             }
+            acp::bulk_commit();
           }
           PROFH(4);
         }
       }
     }
-    sync_all();     // the helpers have written the last block out; nothing of this chunk is in use
+    if (ht == 0) acp::bulk_wait_read<0>();   // the last write-out has left the staging buffer
+    sync_all();     // nothing of this chunk is in use any more
     if (s_fail) break;
   }
+  if (ht == 0) acp::bulk_wait_all();         // every result is in global memory
   if (s_fail && threadIdx.x == 0) {
     atomicExch(status, 1);
     if (raw_pending) acp::mbar_wait(&barRaw, praw);   // bounded: let the copies in flight land
