@@ -185,37 +185,52 @@ __device__ __forceinline__ void store_acc(float *t, const float (&acc)[kNT][4], 
     *reinterpret_cast<float2 *>(t + (m0 + g + 8) * kLd + cc) = make_float2(round_tf32(acc[nt][2]), round_tf32(acc[nt][3]));
   }
 }
-// 16-bit [64][64] block of global memory -> TF32 tile; rows >= nvalid become zero
+// Global loads are split in two, so that the loads of the next chunk are in flight while the
+// current chunk is computed: piece `tid` of the 512 16-byte pieces of a 16-bit block ...
+static_assert(kSeqThreads == 512, "one 16-byte piece of a 16-bit block per thread");
 template <typename T>
-__device__ __forceinline__ void load_tile16(float *t, const T *src, int nvalid, int tid) {
-  for (int idx = tid; idx < kC * (kDim / 8); idx += kSeqThreads) {
-    const int r = idx >> 3, c8 = (idx & 7) * 8;
-    float vals[8];
-    if (r < nvalid) {
-      const uint4 u = *reinterpret_cast<const uint4 *>(src + (size_t)r * kDim + c8);
-      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+__device__ __forceinline__ uint4 fetch16(const T *src, int nvalid, int tid) {
+  const int r = tid >> 3, c8 = (tid & 7) * 8;
+  return r < nvalid ? *reinterpret_cast<const uint4 *>(src + (size_t)r * kDim + c8) : make_uint4(0u, 0u, 0u, 0u);
+}
+template <typename T>
+__device__ __forceinline__ void commit16(float *t, const uint4 &u, int tid) {
+  const int r = tid >> 3, c8 = (tid & 7) * 8;
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+  float vals[8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 p = Pair<T>::ld(reinterpret_cast<const T *>(&w[j]));
-        vals[2 * j] = round_tf32(p.x);
-        vals[2 * j + 1] = round_tf32(p.y);
-      }
-    } else {
+  for (int j = 0; j < 4; ++j) {
+    const float2 p = Pair<T>::ld(reinterpret_cast<const T *>(&w[j]));
+    vals[2 * j] = round_tf32(p.x);
+    vals[2 * j + 1] = round_tf32(p.y);
+  }
+  *reinterpret_cast<float4 *>(t + r * kLd + c8) = make_float4(vals[0], vals[1], vals[2], vals[3]);
+  *reinterpret_cast<float4 *>(t + r * kLd + c8 + 4) = make_float4(vals[4], vals[5], vals[6], vals[7]);
+}
+// ... and pieces `tid`, `tid + 512` of the 1024 16-byte pieces of an fp32 block
+__device__ __forceinline__ void fetch32(float4 (&r)[2], const float *src, int nrows, int tid) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) vals[j] = 0.f;
-    }
-    *reinterpret_cast<float4 *>(t + r * kLd + c8) = make_float4(vals[0], vals[1], vals[2], vals[3]);
-    *reinterpret_cast<float4 *>(t + r * kLd + c8 + 4) = make_float4(vals[4], vals[5], vals[6], vals[7]);
+  for (int j = 0; j < 2; ++j) {
+    const int idx = tid + kSeqThreads * j, row = idx >> 4, c4 = (idx & 15) * 4;
+    r[j] = row < nrows ? *reinterpret_cast<const float4 *>(src + (size_t)row * kDim + c4)
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
   }
 }
-// fp32 [64][64] block -> TF32 tile
-__device__ __forceinline__ void load_tile32(float *t, const float *src, int nrows, int tid) {
-  for (int idx = tid; idx < kC * (kDim / 4); idx += kSeqThreads) {
-    const int r = idx >> 4, c4 = (idx & 15) * 4;
-    float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r < nrows) v4 = *reinterpret_cast<const float4 *>(src + (size_t)r * kDim + c4);
-    *reinterpret_cast<float4 *>(t + r * kLd + c4) =
-        make_float4(round_tf32(v4.x), round_tf32(v4.y), round_tf32(v4.z), round_tf32(v4.w));
+__device__ __forceinline__ void commit32(float *t, const float4 (&r)[2], int tid) {
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int idx = tid + kSeqThreads * j, row = idx >> 4, c4 = (idx & 15) * 4;
+    *reinterpret_cast<float4 *>(t + row * kLd + c4) =
+        make_float4(round_tf32(r[j].x), round_tf32(r[j].y), round_tf32(r[j].z), round_tf32(r[j].w));
+  }
+}
+// this thread's accumulator-fragment positions of an fp32 [64][64] block
+__device__ __forceinline__ void fetch_frag(float2 (&r)[kNT][2], const float *src, int m0, int n0, int g, int tq) {
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) {
+    const int cc = n0 + 8 * nt + 2 * tq;
+    r[nt][0] = *reinterpret_cast<const float2 *>(src + (size_t)(m0 + g) * kDim + cc);
+    r[nt][1] = *reinterpret_cast<const float2 *>(src + (size_t)(m0 + g + 8) * kDim + cc);
   }
 }
 
@@ -243,16 +258,33 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
       S[nt][0] = lo.x; S[nt][1] = lo.y; S[nt][2] = hi.x; S[nt][3] = hi.y;
     }
   }
+  // global loads of a chunk, into registers: issued one chunk ahead
+  uint4 rq, rk;
+  float4 rw[2];
+  float2 ru[kNT][2];
+  auto fetch = [&](int64_t c) {
+    const int64_t t0 = c * kC;
+    const int nv = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
+    const size_t base = ((size_t)b * T_ + t0) * kDim, tile = ((size_t)b * nc + c) * kC * kDim;
+    rq = fetch16<T>(q + base, nv, tid);
+    rk = fetch16<T>(k + base, nv, tid);
+    fetch32(rw, W + tile, kC, tid);
+    fetch_frag(ru, U + tile, m0, n0, g, tq);
+  };
+  fetch(0);
   for (int64_t c = 0; c < nc; ++c) {
     const int64_t t0 = c * kC;
     const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
     const size_t base = ((size_t)b * T_ + t0) * kDim;
-    const size_t tile = ((size_t)b * nc + c) * kC * kDim;
-    load_tile16<T>(Qs, q + base, nvalid, tid);
-    load_tile16<T>(Ks, k + base, nvalid, tid);
-    load_tile32(Ws, W + tile, kC, tid);
+    commit16<T>(Qs, rq, tid);
+    commit16<T>(Ks, rk, tid);
+    commit32(Ws, rw, tid);
+    float2 uf[kNT][2];
+#pragma unroll
+    for (int nt = 0; nt < kNT; ++nt) { uf[nt][0] = ru[nt][0]; uf[nt][1] = ru[nt][1]; }
     store_acc(Ss, S, m0, n0, g, tq);
     __syncthreads();
+    if (c + 1 < nc) fetch(c + 1);
 
     float acc[kNT][4], accO[kNT][4];
     // Dl = U - W S^T   (rows t, columns d)
@@ -261,8 +293,7 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
-      float2 u0 = *reinterpret_cast<const float2 *>(U + tile + (size_t)(m0 + g) * kDim + cc);
-      float2 u1 = *reinterpret_cast<const float2 *>(U + tile + (size_t)(m0 + g + 8) * kDim + cc);
+      const float2 u0 = uf[nt][0], u1 = uf[nt][1];
       acc[nt][0] = u0.x - acc[nt][0]; acc[nt][1] = u0.y - acc[nt][1];
       acc[nt][2] = u1.x - acc[nt][2]; acc[nt][3] = u1.y - acc[nt][3];
       if (m0 + g < nvalid)
@@ -337,18 +368,37 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
       S[nt][0] = lo.x; S[nt][1] = lo.y; S[nt][2] = hi.x; S[nt][3] = hi.y;
     }
   }
+  // global loads of a chunk, into registers: issued one chunk ahead
+  uint4 rq, rk, rg;
+  float4 rd[2], rw[2];
+  float2 ru[kNT][2];
+  auto fetch = [&](int64_t c) {
+    const int64_t t0 = c * kC;
+    const int nv = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
+    const size_t base = ((size_t)b * T_ + t0) * kDim, tile = ((size_t)b * nc + c) * kC * kDim;
+    rq = fetch16<T>(q + base, nv, tid);
+    rk = fetch16<T>(k + base, nv, tid);
+    rg = fetch16<T>(go + base, nv, tid);
+    fetch32(rd, delta + base, nv, tid);
+    fetch32(rw, Wb + tile, kC, tid);
+    fetch_frag(ru, Ub + tile, m0, n0, g, tq);
+  };
+  fetch(nc - 1);
   for (int64_t c = nc - 1; c >= 0; --c) {
     const int64_t t0 = c * kC;
     const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
     const size_t base = ((size_t)b * T_ + t0) * kDim;
-    const size_t tile = ((size_t)b * nc + c) * kC * kDim;
-    load_tile16<T>(Qs, q + base, nvalid, tid);
-    load_tile16<T>(Ks, k + base, nvalid, tid);
-    load_tile16<T>(Gs, go + base, nvalid, tid);
-    load_tile32(Ds, delta + base, nvalid, tid);
-    load_tile32(Ws, Wb + tile, kC, tid);
+    commit16<T>(Qs, rq, tid);
+    commit16<T>(Ks, rk, tid);
+    commit16<T>(Gs, rg, tid);
+    commit32(Ds, rd, tid);
+    commit32(Ws, rw, tid);
+    float2 uf[kNT][2];
+#pragma unroll
+    for (int nt = 0; nt < kNT; ++nt) { uf[nt][0] = ru[nt][0]; uf[nt][1] = ru[nt][1]; }
     store_acc(Rs, R, m0, n0, g, tq);
     __syncthreads();
+    if (c > 0) fetch(c - 1);
 
     float acc[kNT][4], acc2[kNT][4];
     // S0 = S_end - Dl^T K
@@ -365,8 +415,7 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
-      const float2 u0 = *reinterpret_cast<const float2 *>(Ub + tile + (size_t)(m0 + g) * kDim + cc);
-      const float2 u1 = *reinterpret_cast<const float2 *>(Ub + tile + (size_t)(m0 + g + 8) * kDim + cc);
+      const float2 u0 = uf[nt][0], u1 = uf[nt][1];
       acc[nt][0] += u0.x; acc[nt][1] += u0.y; acc[nt][2] += u1.x; acc[nt][3] += u1.y;
       if (m0 + g < nvalid) Pair<T>::st(dv + base + (size_t)(m0 + g) * kDim + cc, acc[nt][0], acc[nt][1]);
       if (m0 + g + 8 < nvalid) Pair<T>::st(dv + base + (size_t)(m0 + g + 8) * kDim + cc, acc[nt][2], acc[nt][3]);
