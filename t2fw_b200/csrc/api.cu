@@ -95,7 +95,7 @@ static bool dfw_chunk_enabled() {
 }
 
 size_t t2fw_dfw_forward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t M, int dtype) {
-  if (dfw_chunk_enabled() && dfw_chunk_supported(D, M, dtype)) return dfw_chunk_scratch_bytes(B, T);
+  if (dfw_chunk_enabled() && dfw_chunk_supported(D, M, dtype)) return dfw_chunk_scratch_bytes(B, T, false);
   return 0;
 }
 
@@ -108,7 +108,7 @@ static size_t dfw_scan_backward_scratch(int64_t B, int64_t T, int64_t D, int dty
 size_t t2fw_dfw_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t M, int dtype) {
   const size_t scan = dfw_scan_backward_scratch(B, T, D, dtype);
   if (dfw_chunk_enabled() && dfw_chunk_supported(D, M, dtype)) {
-    const size_t ch = dfw_chunk_scratch_bytes(B, T);
+    const size_t ch = dfw_chunk_scratch_bytes(B, T, true);
     return ch > scan ? ch : scan;
   }
   return scan;

@@ -133,7 +133,7 @@ int lfw_decode_forward(const void *x, const void *f, const void *q, const void *
                        int64_t K, int dtype, cudaStream_t st);
 // chunked delta rule (dfw_chunk.cu): D = M = 64, 16-bit storage
 bool dfw_chunk_supported(int64_t D, int64_t M, int dtype);
-size_t dfw_chunk_scratch_bytes(int64_t B, int64_t T);
+size_t dfw_chunk_scratch_bytes(int64_t B, int64_t T, bool backward);
 int dfw_chunk_forward(const void *q, const void *k, const void *v, const void *state, void *out,
                       void *final_state, void *delta, int64_t B, int64_t T, int dtype, void *scratch,
                       cudaStream_t st);

@@ -21,7 +21,8 @@
 //   dfw_chunk_prep_kernel<T, kBwd>   (batch row, chunk): W, U (or Wb, Ub) by forward (backward)
 //       substitution in fp32, one thread per column, no inverse is ever formed
 //   dfw_chunk_fwd_kernel<T>          one CTA per batch row, sequential over chunks
-//   dfw_chunk_bwd_kernel<T>          one CTA per batch row, sequential over chunks in reverse
+//   dfw_chunk_bwd_seq_kernel<T>      one CTA per batch row, chunks in reverse: state walk-back, E, R
+//   dfw_chunk_bwd_par_kernel<T>      (batch row, chunk): d_query and d_key from the stored S0, R_end, E
 #include <type_traits>
 
 #include "lfw_chunk.cuh"
@@ -340,18 +341,30 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
   }
 }
 
-// ---- backward: one CTA per batch row, chunks in reverse -------------------------------------------
+// this thread's accumulator-fragment positions -> fp32 [64][64] block in global memory
+__device__ __forceinline__ void store_frag(float *dst, const float (&acc)[kNT][4], int m0, int n0, int g, int tq) {
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) {
+    const int cc = n0 + 8 * nt + 2 * tq;
+    *reinterpret_cast<float2 *>(dst + (size_t)(m0 + g) * kDim + cc) = make_float2(acc[nt][0], acc[nt][1]);
+    *reinterpret_cast<float2 *>(dst + (size_t)(m0 + g + 8) * kDim + cc) = make_float2(acc[nt][2], acc[nt][3]);
+  }
+}
+
+// ---- backward, sequential part: one CTA per batch row, chunks in reverse ------------------------
+// Only what depends on the chunk after it: the walked-back state S0, E = d_value and the state
+// gradient R.  S0, R_end and E of every chunk go to scratch for the chunk-parallel kernel below.
 template <typename T>
 __global__ void __launch_bounds__(kSeqThreads, 1)
-dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T *__restrict__ q,
-                     const T *__restrict__ k, const float *__restrict__ delta,
-                     const T *__restrict__ final_state, const float *__restrict__ Wb,
-                     const float *__restrict__ Ub, T *__restrict__ dq, T *__restrict__ dk,
-                     T *__restrict__ dv, T *__restrict__ ds, int64_t T_, int64_t nc) {
+dfw_chunk_bwd_seq_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T *__restrict__ q,
+                         const T *__restrict__ k, const float *__restrict__ delta,
+                         const T *__restrict__ final_state, const float *__restrict__ Wb,
+                         const float *__restrict__ Ub, float *__restrict__ Sc, float *__restrict__ Rc,
+                         float *__restrict__ Ec, T *__restrict__ dv, T *__restrict__ ds, int64_t T_,
+                         int64_t nc) {
   extern __shared__ __align__(16) float sm[];
   float *Qs = sm, *Ks = Qs + kC * kLd, *Gs = Ks + kC * kLd, *Ds = Gs + kC * kLd, *Ws = Ds + kC * kLd,
-        *Es = Ws + kC * kLd, *Rs = Es + kC * kLd, *Ss = Rs + kC * kLd, *X1s = Ss + kC * kLd,
-        *X2s = X1s + kC * kLd;
+        *Es = Ws + kC * kLd, *Rs = Es + kC * kLd;
   const int64_t b = blockIdx.x;
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
   const int m0 = 16 * (w & 3), n0 = 8 * kNT * (w >> 2);
@@ -387,7 +400,7 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
   for (int64_t c = nc - 1; c >= 0; --c) {
     const int64_t t0 = c * kC;
     const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
-    const size_t base = ((size_t)b * T_ + t0) * kDim;
+    const size_t base = ((size_t)b * T_ + t0) * kDim, tile = ((size_t)b * nc + c) * kC * kDim;
     commit16<T>(Qs, rq, tid);
     commit16<T>(Ks, rk, tid);
     commit16<T>(Gs, rg, tid);
@@ -397,10 +410,11 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt) { uf[nt][0] = ru[nt][0]; uf[nt][1] = ru[nt][1]; }
     store_acc(Rs, R, m0, n0, g, tq);
+    store_frag(Rc + tile, R, m0, n0, g, tq);
     __syncthreads();
     if (c > 0) fetch(c - 1);
 
-    float acc[kNT][4], acc2[kNT][4];
+    float acc[kNT][4];
     // S0 = S_end - Dl^T K
     zero(acc);
     gemm64<true, false>(acc, Ds, Ks, m0, n0, g, tq);
@@ -408,7 +422,7 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
     for (int nt = 0; nt < kNT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) S[nt][e] -= acc[nt][e];
-    store_acc(Ss, S, m0, n0, g, tq);
+    store_frag(Sc + tile, S, m0, n0, g, tq);
     // E = Ub + Wb R_end^T = d_value
     zero(acc);
     gemm64<false, true>(acc, Ws, Rs, m0, n0, g, tq);
@@ -421,68 +435,16 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
       if (m0 + g + 8 < nvalid) Pair<T>::st(dv + base + (size_t)(m0 + g + 8) * kDim + cc, acc[nt][2], acc[nt][3]);
     }
     store_acc(Es, acc, m0, n0, g, tq);
-    // X1 = strict_lower(dO Dl^T)
-    zero(acc);
-    gemm64<false, true>(acc, Gs, Ds, m0, n0, g, tq);
-#pragma unroll
-    for (int nt = 0; nt < kNT; ++nt) {
-      const int cc = n0 + 8 * nt + 2 * tq;
-      acc[nt][0] = (cc < m0 + g) ? acc[nt][0] : 0.f;
-      acc[nt][1] = (cc + 1 < m0 + g) ? acc[nt][1] : 0.f;
-      acc[nt][2] = (cc < m0 + g + 8) ? acc[nt][2] : 0.f;
-      acc[nt][3] = (cc + 1 < m0 + g + 8) ? acc[nt][3] : 0.f;
-    }
-    store_acc(X1s, acc, m0, n0, g, tq);
-    __syncthreads();               // S0, E, X1 tiles complete
-
-    // X2 = strict_upper(Dl E^T)
-    zero(acc);
-    gemm64<false, true>(acc, Ds, Es, m0, n0, g, tq);
-#pragma unroll
-    for (int nt = 0; nt < kNT; ++nt) {
-      const int cc = n0 + 8 * nt + 2 * tq;
-      acc[nt][0] = (cc > m0 + g) ? acc[nt][0] : 0.f;
-      acc[nt][1] = (cc + 1 > m0 + g) ? acc[nt][1] : 0.f;
-      acc[nt][2] = (cc > m0 + g + 8) ? acc[nt][2] : 0.f;
-      acc[nt][3] = (cc + 1 > m0 + g + 8) ? acc[nt][3] : 0.f;
-    }
-    store_acc(X2s, acc, m0, n0, g, tq);
-    // d_query = dO S0 + X1 K
-    zero(acc);
-    gemm64<false, false>(acc, Gs, Ss, m0, n0, g, tq);
-    gemm64<false, false>(acc, X1s, Ks, m0, n0, g, tq);
-#pragma unroll
-    for (int nt = 0; nt < kNT; ++nt) {
-      const int cc = n0 + 8 * nt + 2 * tq;
-      if (m0 + g < nvalid) Pair<T>::st(dq + base + (size_t)(m0 + g) * kDim + cc, acc[nt][0], acc[nt][1]);
-      if (m0 + g + 8 < nvalid) Pair<T>::st(dq + base + (size_t)(m0 + g + 8) * kDim + cc, acc[nt][2], acc[nt][3]);
-    }
-    __syncthreads();               // X2 tile complete
-
-    // d_key = Dl R_end + X1^T Q - (X2 + X2^T) K - E S0
-    zero(acc);
-    gemm64<false, false>(acc, Ds, Rs, m0, n0, g, tq);
-    gemm64<true, false>(acc, X1s, Qs, m0, n0, g, tq);
-    zero(acc2);
-    gemm64<false, false>(acc2, X2s, Ks, m0, n0, g, tq);
-    gemm64<true, false>(acc2, X2s, Ks, m0, n0, g, tq);
-    gemm64<false, false>(acc2, Es, Ss, m0, n0, g, tq);
-#pragma unroll
-    for (int nt = 0; nt < kNT; ++nt) {
-      const int cc = n0 + 8 * nt + 2 * tq;
-      if (m0 + g < nvalid)
-        Pair<T>::st(dk + base + (size_t)(m0 + g) * kDim + cc, acc[nt][0] - acc2[nt][0], acc[nt][1] - acc2[nt][1]);
-      if (m0 + g + 8 < nvalid)
-        Pair<T>::st(dk + base + (size_t)(m0 + g + 8) * kDim + cc, acc[nt][2] - acc2[nt][2], acc[nt][3] - acc2[nt][3]);
-    }
+    store_frag(Ec + tile, acc, m0, n0, g, tq);
+    __syncthreads();               // E tile complete
     // R_start = R_end + dO^T Q - E^T K
     gemm64<true, false>(R, Gs, Qs, m0, n0, g, tq);
-    zero(acc2);
-    gemm64<true, false>(acc2, Es, Ks, m0, n0, g, tq);
+    zero(acc);
+    gemm64<true, false>(acc, Es, Ks, m0, n0, g, tq);
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) R[nt][e] -= acc2[nt][e];
+      for (int e = 0; e < 4; ++e) R[nt][e] -= acc[nt][e];
     __syncthreads();               // tiles are rewritten by the next chunk
   }
   T *dp = ds + (size_t)b * kDim * kDim;
@@ -491,6 +453,90 @@ dfw_chunk_bwd_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T
     const int cc = n0 + 8 * nt + 2 * tq;
     Pair<T>::st(dp + (m0 + g) * kDim + cc, R[nt][0], R[nt][1]);
     Pair<T>::st(dp + (m0 + g + 8) * kDim + cc, R[nt][2], R[nt][3]);
+  }
+}
+
+// ---- backward, chunk-parallel part: d_query and d_key of one (batch row, chunk) ------------------
+template <typename T>
+__global__ void __launch_bounds__(kSeqThreads, 1)
+dfw_chunk_bwd_par_kernel(const T *__restrict__ go, const T *__restrict__ q, const T *__restrict__ k,
+                         const float *__restrict__ delta, const float *__restrict__ Sc,
+                         const float *__restrict__ Rc, const float *__restrict__ Ec, T *__restrict__ dq,
+                         T *__restrict__ dk, int64_t T_, int64_t nc) {
+  extern __shared__ __align__(16) float sm[];
+  float *Qs = sm, *Ks = Qs + kC * kLd, *Gs = Ks + kC * kLd, *Ds = Gs + kC * kLd, *Es = Ds + kC * kLd,
+        *Rs = Es + kC * kLd, *Ss = Rs + kC * kLd, *X1s = Ss + kC * kLd, *X2s = X1s + kC * kLd;
+  const int64_t b = blockIdx.x / nc, c = blockIdx.x % nc, t0 = c * kC;
+  const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
+  const size_t base = ((size_t)b * T_ + t0) * kDim, tile = (size_t)blockIdx.x * kC * kDim;
+  const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
+  const int m0 = 16 * (w & 3), n0 = 8 * kNT * (w >> 2);
+  {
+    const uint4 rq = fetch16<T>(q + base, nvalid, tid), rk = fetch16<T>(k + base, nvalid, tid),
+                rg = fetch16<T>(go + base, nvalid, tid);
+    float4 rd[2], re[2], rs[2], rr[2];
+    fetch32(rd, delta + base, nvalid, tid);
+    fetch32(re, Ec + tile, kC, tid);
+    fetch32(rs, Sc + tile, kC, tid);
+    fetch32(rr, Rc + tile, kC, tid);
+    commit16<T>(Qs, rq, tid);
+    commit16<T>(Ks, rk, tid);
+    commit16<T>(Gs, rg, tid);
+    commit32(Ds, rd, tid);
+    commit32(Es, re, tid);
+    commit32(Ss, rs, tid);
+    commit32(Rs, rr, tid);
+  }
+  __syncthreads();
+  float acc[kNT][4], acc2[kNT][4];
+  // X1 = strict_lower(dO Dl^T)
+  zero(acc);
+  gemm64<false, true>(acc, Gs, Ds, m0, n0, g, tq);
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) {
+    const int cc = n0 + 8 * nt + 2 * tq;
+    acc[nt][0] = (cc < m0 + g) ? acc[nt][0] : 0.f;
+    acc[nt][1] = (cc + 1 < m0 + g) ? acc[nt][1] : 0.f;
+    acc[nt][2] = (cc < m0 + g + 8) ? acc[nt][2] : 0.f;
+    acc[nt][3] = (cc + 1 < m0 + g + 8) ? acc[nt][3] : 0.f;
+  }
+  store_acc(X1s, acc, m0, n0, g, tq);
+  // X2 = strict_upper(Dl E^T)
+  zero(acc);
+  gemm64<false, true>(acc, Ds, Es, m0, n0, g, tq);
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) {
+    const int cc = n0 + 8 * nt + 2 * tq;
+    acc[nt][0] = (cc > m0 + g) ? acc[nt][0] : 0.f;
+    acc[nt][1] = (cc + 1 > m0 + g) ? acc[nt][1] : 0.f;
+    acc[nt][2] = (cc > m0 + g + 8) ? acc[nt][2] : 0.f;
+    acc[nt][3] = (cc + 1 > m0 + g + 8) ? acc[nt][3] : 0.f;
+  }
+  store_acc(X2s, acc, m0, n0, g, tq);
+  // d_query = dO S0 + X1 K ;  d_key = Dl R_end + X1^T Q - (X2 + X2^T) K - E S0
+  zero(acc);
+  gemm64<false, false>(acc, Gs, Ss, m0, n0, g, tq);
+  zero(acc2);
+  gemm64<false, false>(acc2, Es, Ss, m0, n0, g, tq);
+  float acck[kNT][4];
+  zero(acck);
+  gemm64<false, false>(acck, Ds, Rs, m0, n0, g, tq);
+  __syncthreads();                 // X1, X2 tiles complete
+  gemm64<false, false>(acc, X1s, Ks, m0, n0, g, tq);
+  gemm64<true, false>(acck, X1s, Qs, m0, n0, g, tq);
+  gemm64<false, false>(acc2, X2s, Ks, m0, n0, g, tq);
+  gemm64<true, false>(acc2, X2s, Ks, m0, n0, g, tq);
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) {
+    const int cc = n0 + 8 * nt + 2 * tq;
+    if (m0 + g < nvalid) {
+      Pair<T>::st(dq + base + (size_t)(m0 + g) * kDim + cc, acc[nt][0], acc[nt][1]);
+      Pair<T>::st(dk + base + (size_t)(m0 + g) * kDim + cc, acck[nt][0] - acc2[nt][0], acck[nt][1] - acc2[nt][1]);
+    }
+    if (m0 + g + 8 < nvalid) {
+      Pair<T>::st(dq + base + (size_t)(m0 + g + 8) * kDim + cc, acc[nt][2], acc[nt][3]);
+      Pair<T>::st(dk + base + (size_t)(m0 + g + 8) * kDim + cc, acck[nt][2] - acc2[nt][2], acck[nt][3] - acc2[nt][3]);
+    }
   }
 }
 
@@ -505,9 +551,9 @@ bool dfw_chunk_supported(int64_t D, int64_t M, int dtype) {
   return D == kDim && M == kDim && (dtype == T2FW_F16 || dtype == T2FW_BF16);
 }
 
-// W and U (forward) or Wb and Ub (backward): two fp32 [B][n_chunks][64][64] arrays
-size_t dfw_chunk_scratch_bytes(int64_t B, int64_t T_) {
-  return align_up(2 * wu_floats(B, ceil_div64(T_, kC)) * sizeof(float), 256);
+// fp32 [B][n_chunks][64][64] arrays: W and U (forward); Wb, Ub and the per-chunk S0, R_end, E (backward)
+size_t dfw_chunk_scratch_bytes(int64_t B, int64_t T_, bool backward) {
+  return align_up((backward ? 5 : 2) * wu_floats(B, ceil_div64(T_, kC)) * sizeof(float), 256);
 }
 
 template <typename T>
@@ -546,12 +592,17 @@ static int dfw_chunk_backward_typed(const void *go, const void *gs, const void *
                                        (int)(4 * kPrepTile)));
   dfw_chunk_prep_kernel<T, true><<<(unsigned)(B * nc), 128, 4 * kPrepTile, st>>>(
       (const T *)q, (const T *)k, (const T *)go, Wb, Ub, T_, nc);
-  T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)(10 * kTileBytes)));
-  dfw_chunk_bwd_kernel<T><<<(unsigned)B, kSeqThreads, 10 * kTileBytes, st>>>(
+  float *Sc = Ub + wu_floats(B, nc), *Rc = Sc + wu_floats(B, nc), *Ec = Rc + wu_floats(B, nc);
+  T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_seq_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(7 * kTileBytes)));
+  dfw_chunk_bwd_seq_kernel<T><<<(unsigned)B, kSeqThreads, 7 * kTileBytes, st>>>(
       (const T *)go, (const T *)gs, (const T *)q, (const T *)k, (const float *)delta, (const T *)final_state, Wb,
-      Ub, (T *)dq, (T *)dk, (T *)dv, (T *)ds, T_, nc);
-  T2FW_CHECK_LAUNCH(2);
+      Ub, Sc, Rc, Ec, (T *)dv, (T *)ds, T_, nc);
+  T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_par_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(9 * kTileBytes)));
+  dfw_chunk_bwd_par_kernel<T><<<(unsigned)(B * nc), kSeqThreads, 9 * kTileBytes, st>>>(
+      (const T *)go, (const T *)q, (const T *)k, (const float *)delta, Sc, Rc, Ec, (T *)dq, (T *)dk, T_, nc);
+  T2FW_CHECK_LAUNCH(3);
   return T2FW_OK;
 }
 
