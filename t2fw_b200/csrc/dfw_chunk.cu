@@ -155,21 +155,29 @@ dfw_chunk_prep_kernel(const T *__restrict__ q, const T *__restrict__ k, const T 
   for (int t = 0; t < kC; ++t) dst[t * kDim] = x[t];
 }
 
-// ---- helpers of the sequential kernels -------------------------------------------------------------
-// acc[nt][.] (rows m0 + {g, g+8}, columns n0 + 8*nt + {2tq, 2tq+1}) += A * B over a contraction of 64.
-//   AT: the tile holds A transposed (A[m][k] = tA[k][m]);  BT: the tile holds B as [n][k]
-template <bool AT, bool BT>
+// ---- helpers of the chunk kernels ----------------------------------------------------------------
+// Every product has the form D[m][n] = sum_k A[m][k] B[n][k] with both tiles stored [row][k];
+// operands that arise the other way round are stored transposed at the moment they are written.
+// Within 16 values of k, thread tq of a fragment group uses the physical columns 4tq .. 4tq+3 for
+// the logical k indices (tq, tq+4) of two consecutive MMAs - the sum over k does not depend on
+// the order as long as A and B agree - so every fragment is one 16-byte load.
+constexpr int kLdV = 80;   // row stride in floats: the 16-byte loads of a quarter warp hit 32 distinct banks
+
 __device__ __forceinline__ void gemm64(float (&acc)[kNT][4], const float *tA, const float *tB, int m0, int n0,
                                        int g, int tq) {
-#pragma unroll 2
-  for (int k0 = 0; k0 < kC; k0 += 8) {
-    uint32_t a[4];
-    if (AT) lda_t(a, tA, kLd, m0, k0, g, tq); else lda(a, tA, kLd, m0, k0, g, tq);
+#pragma unroll
+  for (int k0 = 0; k0 < kC; k0 += 16) {
+    const float4 lo = *reinterpret_cast<const float4 *>(tA + (m0 + g) * kLdV + k0 + 4 * tq);
+    const float4 hi = *reinterpret_cast<const float4 *>(tA + (m0 + g + 8) * kLdV + k0 + 4 * tq);
+    const uint32_t a1[4] = {__float_as_uint(lo.x), __float_as_uint(hi.x), __float_as_uint(lo.y), __float_as_uint(hi.y)};
+    const uint32_t a2[4] = {__float_as_uint(lo.z), __float_as_uint(hi.z), __float_as_uint(lo.w), __float_as_uint(hi.w)};
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt) {
-      uint32_t bf[2];
-      if (BT) ldb_t(bf, tB, kLd, k0, n0 + 8 * nt, g, tq); else ldb(bf, tB, kLd, k0, n0 + 8 * nt, g, tq);
-      mma_tf32(acc[nt], a, bf);
+      const float4 bv = *reinterpret_cast<const float4 *>(tB + (n0 + 8 * nt + g) * kLdV + k0 + 4 * tq);
+      const uint32_t b1[2] = {__float_as_uint(bv.x), __float_as_uint(bv.y)};
+      const uint32_t b2[2] = {__float_as_uint(bv.z), __float_as_uint(bv.w)};
+      mma_tf32(acc[nt], a1, b1);
+      mma_tf32(acc[nt], a2, b2);
     }
   }
 }
@@ -177,61 +185,131 @@ __device__ __forceinline__ void zero(float (&acc)[kNT][4]) {
 #pragma unroll
   for (int nt = 0; nt < kNT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 }
-// accumulator fragment -> fp32 tile (values rounded to TF32 so that the tile can feed an MMA)
+// keep the strictly lower (LOWER) or strictly upper part of this warp's accumulator tile
+template <bool LOWER>
+__device__ __forceinline__ void mask_tri(float (&acc)[kNT][4], int m0, int n0, int g, int tq) {
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) {
+    const int cc = n0 + 8 * nt + 2 * tq, r0 = m0 + g, r1 = m0 + g + 8;
+    acc[nt][0] = (LOWER ? cc < r0 : cc > r0) ? acc[nt][0] : 0.f;
+    acc[nt][1] = (LOWER ? cc + 1 < r0 : cc + 1 > r0) ? acc[nt][1] : 0.f;
+    acc[nt][2] = (LOWER ? cc < r1 : cc > r1) ? acc[nt][2] : 0.f;
+    acc[nt][3] = (LOWER ? cc + 1 < r1 : cc + 1 > r1) ? acc[nt][3] : 0.f;
+  }
+}
+// accumulator fragment -> TF32 tile, as is ([m][n]) or transposed ([n][m])
 __device__ __forceinline__ void store_acc(float *t, const float (&acc)[kNT][4], int m0, int n0, int g, int tq) {
 #pragma unroll
   for (int nt = 0; nt < kNT; ++nt) {
     const int cc = n0 + 8 * nt + 2 * tq;
-    *reinterpret_cast<float2 *>(t + (m0 + g) * kLd + cc) = make_float2(round_tf32(acc[nt][0]), round_tf32(acc[nt][1]));
-    *reinterpret_cast<float2 *>(t + (m0 + g + 8) * kLd + cc) = make_float2(round_tf32(acc[nt][2]), round_tf32(acc[nt][3]));
+    *reinterpret_cast<float2 *>(t + (m0 + g) * kLdV + cc) = make_float2(round_tf32(acc[nt][0]), round_tf32(acc[nt][1]));
+    *reinterpret_cast<float2 *>(t + (m0 + g + 8) * kLdV + cc) = make_float2(round_tf32(acc[nt][2]), round_tf32(acc[nt][3]));
   }
 }
-// Global loads are split in two, so that the loads of the next chunk are in flight while the
-// current chunk is computed: piece `tid` of the 512 16-byte pieces of a 16-bit block ...
-static_assert(kSeqThreads == 512, "one 16-byte piece of a 16-bit block per thread");
-template <typename T>
-__device__ __forceinline__ uint4 fetch16(const T *src, int nvalid, int tid) {
-  const int r = tid >> 3, c8 = (tid & 7) * 8;
-  return r < nvalid ? *reinterpret_cast<const uint4 *>(src + (size_t)r * kDim + c8) : make_uint4(0u, 0u, 0u, 0u);
-}
-template <typename T>
-__device__ __forceinline__ void commit16(float *t, const uint4 &u, int tid) {
-  const int r = tid >> 3, c8 = (tid & 7) * 8;
-  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-  float vals[8];
+__device__ __forceinline__ void store_acc_t(float *t, const float (&acc)[kNT][4], int m0, int n0, int g, int tq) {
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 p = Pair<T>::ld(reinterpret_cast<const T *>(&w[j]));
-    vals[2 * j] = round_tf32(p.x);
-    vals[2 * j + 1] = round_tf32(p.y);
+  for (int nt = 0; nt < kNT; ++nt) {
+    const int cc = n0 + 8 * nt + 2 * tq;
+    t[cc * kLdV + m0 + g] = round_tf32(acc[nt][0]);
+    t[(cc + 1) * kLdV + m0 + g] = round_tf32(acc[nt][1]);
+    t[cc * kLdV + m0 + g + 8] = round_tf32(acc[nt][2]);
+    t[(cc + 1) * kLdV + m0 + g + 8] = round_tf32(acc[nt][3]);
   }
-  *reinterpret_cast<float4 *>(t + r * kLd + c8) = make_float4(vals[0], vals[1], vals[2], vals[3]);
-  *reinterpret_cast<float4 *>(t + r * kLd + c8 + 4) = make_float4(vals[4], vals[5], vals[6], vals[7]);
 }
-// ... and pieces `tid`, `tid + 512` of the 1024 16-byte pieces of an fp32 block
-__device__ __forceinline__ void fetch32(float4 (&r)[2], const float *src, int nrows, int tid) {
+// accumulator fragment <-> fp32 [64][64] block in global memory, as is or transposed
+__device__ __forceinline__ void store_frag(float *dst, const float (&acc)[kNT][4], int m0, int n0, int g, int tq) {
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const int idx = tid + kSeqThreads * j, row = idx >> 4, c4 = (idx & 15) * 4;
-    r[j] = row < nrows ? *reinterpret_cast<const float4 *>(src + (size_t)row * kDim + c4)
-                       : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int nt = 0; nt < kNT; ++nt) {
+    const int cc = n0 + 8 * nt + 2 * tq;
+    *reinterpret_cast<float2 *>(dst + (size_t)(m0 + g) * kDim + cc) = make_float2(acc[nt][0], acc[nt][1]);
+    *reinterpret_cast<float2 *>(dst + (size_t)(m0 + g + 8) * kDim + cc) = make_float2(acc[nt][2], acc[nt][3]);
   }
 }
-__device__ __forceinline__ void commit32(float *t, const float4 (&r)[2], int tid) {
+__device__ __forceinline__ void store_frag_t(float *dst, const float (&acc)[kNT][4], int m0, int n0, int g, int tq) {
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const int idx = tid + kSeqThreads * j, row = idx >> 4, c4 = (idx & 15) * 4;
-    *reinterpret_cast<float4 *>(t + row * kLd + c4) =
-        make_float4(round_tf32(r[j].x), round_tf32(r[j].y), round_tf32(r[j].z), round_tf32(r[j].w));
+  for (int nt = 0; nt < kNT; ++nt) {
+    const int cc = n0 + 8 * nt + 2 * tq;
+    dst[(size_t)cc * kDim + m0 + g] = acc[nt][0];
+    dst[(size_t)(cc + 1) * kDim + m0 + g] = acc[nt][1];
+    dst[(size_t)cc * kDim + m0 + g + 8] = acc[nt][2];
+    dst[(size_t)(cc + 1) * kDim + m0 + g + 8] = acc[nt][3];
   }
 }
-// this thread's accumulator-fragment positions of an fp32 [64][64] block
 __device__ __forceinline__ void fetch_frag(float2 (&r)[kNT][2], const float *src, int m0, int n0, int g, int tq) {
 #pragma unroll
   for (int nt = 0; nt < kNT; ++nt) {
     const int cc = n0 + 8 * nt + 2 * tq;
     r[nt][0] = *reinterpret_cast<const float2 *>(src + (size_t)(m0 + g) * kDim + cc);
     r[nt][1] = *reinterpret_cast<const float2 *>(src + (size_t)(m0 + g + 8) * kDim + cc);
+  }
+}
+
+// Global loads are split in two (fetch into registers, commit to a shared-memory tile) so that the
+// loads of the next chunk are in flight while the current chunk is computed.  A [64][64] block
+// is 512 (16-bit) or 1024 (fp32) 16-byte pieces.  Piece mapping ROWS: consecutive threads take
+// consecutive pieces of a row (coalesced; for tiles kept as they are).  Piece mapping COLS:
+// consecutive threads take the same piece of consecutive rows, which makes the transposed
+// shared-memory stores conflict-free (for tiles kept transposed).
+static_assert(kSeqThreads == 512, "one 16-byte piece of a 16-bit block per thread");
+template <typename T, bool COLS>
+__device__ __forceinline__ uint4 fetch16(const T *src, int nvalid, int tid) {
+  const int r = COLS ? (tid & 63) : (tid >> 3), c8 = (COLS ? (tid >> 6) : (tid & 7)) * 8;
+  return r < nvalid ? *reinterpret_cast<const uint4 *>(src + (size_t)r * kDim + c8) : make_uint4(0u, 0u, 0u, 0u);
+}
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4 &u, float (&vals)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 p = Pair<T>::ld(reinterpret_cast<const T *>(&w[j]));
+    vals[2 * j] = round_tf32(p.x);
+    vals[2 * j + 1] = round_tf32(p.y);
+  }
+}
+// commit as is ([row][col]); works with either piece mapping
+template <typename T, bool COLS>
+__device__ __forceinline__ void commit16(float *t, const uint4 &u, int tid) {
+  const int r = COLS ? (tid & 63) : (tid >> 3), c8 = (COLS ? (tid >> 6) : (tid & 7)) * 8;
+  float vals[8];
+  unpack8<T>(u, vals);
+  *reinterpret_cast<float4 *>(t + r * kLdV + c8) = make_float4(vals[0], vals[1], vals[2], vals[3]);
+  *reinterpret_cast<float4 *>(t + r * kLdV + c8 + 4) = make_float4(vals[4], vals[5], vals[6], vals[7]);
+}
+// commit transposed ([col][row]); piece mapping COLS
+template <typename T>
+__device__ __forceinline__ void commit16_t(float *t, const uint4 &u, int tid) {
+  const int r = tid & 63, c8 = (tid >> 6) * 8;
+  float vals[8];
+  unpack8<T>(u, vals);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) t[(c8 + j) * kLdV + r] = vals[j];
+}
+template <bool COLS>
+__device__ __forceinline__ void fetch32(float4 (&r)[2], const float *src, int nrows, int tid) {
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int idx = tid + kSeqThreads * j;
+    const int row = COLS ? (idx & 63) : (idx >> 4), c4 = (COLS ? (idx >> 6) : (idx & 15)) * 4;
+    r[j] = row < nrows ? *reinterpret_cast<const float4 *>(src + (size_t)row * kDim + c4)
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+__device__ __forceinline__ void commit32(float *t, const float4 (&r)[2], int tid) {    // mapping ROWS, as is
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int idx = tid + kSeqThreads * j, row = idx >> 4, c4 = (idx & 15) * 4;
+    *reinterpret_cast<float4 *>(t + row * kLdV + c4) =
+        make_float4(round_tf32(r[j].x), round_tf32(r[j].y), round_tf32(r[j].z), round_tf32(r[j].w));
+  }
+}
+__device__ __forceinline__ void commit32_t(float *t, const float4 (&r)[2], int tid) {  // mapping COLS, transposed
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int idx = tid + kSeqThreads * j, row = idx & 63, c4 = (idx >> 6) * 4;
+    t[c4 * kLdV + row] = round_tf32(r[j].x);
+    t[(c4 + 1) * kLdV + row] = round_tf32(r[j].y);
+    t[(c4 + 2) * kLdV + row] = round_tf32(r[j].z);
+    t[(c4 + 3) * kLdV + row] = round_tf32(r[j].w);
   }
 }
 
@@ -242,13 +320,15 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
                      const float *__restrict__ W, const float *__restrict__ U, T *__restrict__ out,
                      T *__restrict__ final_state, float *__restrict__ delta, int64_t T_, int64_t nc) {
   extern __shared__ __align__(16) float sm[];
-  float *Qs = sm, *Ks = Qs + kC * kLd, *Ws = Ks + kC * kLd, *Ds = Ws + kC * kLd, *Ss = Ds + kC * kLd,
-        *As = Ss + kC * kLd;
+  constexpr int kTileF = kC * kLdV;
+  // Q [t][m], K [t][m], K^T [m][t], W [t][m], S [d][m], A = strict_lower(Q K^T) [t][i], Dl^T [d][t]
+  float *Qs = sm, *Ks = Qs + kTileF, *KsT = Ks + kTileF, *Ws = KsT + kTileF, *Ss = Ws + kTileF,
+        *As = Ss + kTileF, *DsT = As + kTileF;
   const int64_t b = blockIdx.x;
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
   const int m0 = 16 * (w & 3), n0 = 8 * kNT * (w >> 2);
 
-  // the state: this warp's 16 x 32 tile in accumulator-fragment layout, fp32
+  // the state: this warp's 16 x 16 tile in accumulator-fragment layout, fp32
   float S[kNT][4];
   {
     const T *sp = state + (size_t)b * kDim * kDim;
@@ -267,9 +347,9 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
     const int64_t t0 = c * kC;
     const int nv = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
     const size_t base = ((size_t)b * T_ + t0) * kDim, tile = ((size_t)b * nc + c) * kC * kDim;
-    rq = fetch16<T>(q + base, nv, tid);
-    rk = fetch16<T>(k + base, nv, tid);
-    fetch32(rw, W + tile, kC, tid);
+    rq = fetch16<T, false>(q + base, nv, tid);
+    rk = fetch16<T, true>(k + base, nv, tid);
+    fetch32<false>(rw, W + tile, kC, tid);
     fetch_frag(ru, U + tile, m0, n0, g, tq);
   };
   fetch(0);
@@ -277,8 +357,9 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
     const int64_t t0 = c * kC;
     const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
     const size_t base = ((size_t)b * T_ + t0) * kDim;
-    commit16<T>(Qs, rq, tid);
-    commit16<T>(Ks, rk, tid);
+    commit16<T, false>(Qs, rq, tid);
+    commit16<T, true>(Ks, rk, tid);
+    commit16_t<T>(KsT, rk, tid);
     commit32(Ws, rw, tid);
     float2 uf[kNT][2];
 #pragma unroll
@@ -287,10 +368,10 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
     __syncthreads();
     if (c + 1 < nc) fetch(c + 1);
 
-    float acc[kNT][4], accO[kNT][4];
+    float acc[kNT][4], accO[kNT][4], sc[kNT][4];
     // Dl = U - W S^T   (rows t, columns d)
     zero(acc);
-    gemm64<false, true>(acc, Ws, Ss, m0, n0, g, tq);
+    gemm64(acc, Ws, Ss, m0, n0, g, tq);
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
@@ -302,26 +383,18 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
       if (m0 + g + 8 < nvalid)
         *reinterpret_cast<float2 *>(delta + base + (size_t)(m0 + g + 8) * kDim + cc) = make_float2(acc[nt][2], acc[nt][3]);
     }
+    store_acc_t(DsT, acc, m0, n0, g, tq);
     // scores A = strict_lower(Q K^T)   (rows t, columns i)
-    float sc[kNT][4];
     zero(sc);
-    gemm64<false, true>(sc, Qs, Ks, m0, n0, g, tq);
-#pragma unroll
-    for (int nt = 0; nt < kNT; ++nt) {
-      const int cc = n0 + 8 * nt + 2 * tq;
-      sc[nt][0] = (cc < m0 + g) ? sc[nt][0] : 0.f;
-      sc[nt][1] = (cc + 1 < m0 + g) ? sc[nt][1] : 0.f;
-      sc[nt][2] = (cc < m0 + g + 8) ? sc[nt][2] : 0.f;
-      sc[nt][3] = (cc + 1 < m0 + g + 8) ? sc[nt][3] : 0.f;
-    }
+    gemm64(sc, Qs, Ks, m0, n0, g, tq);
+    mask_tri<true>(sc, m0, n0, g, tq);
+    store_acc(As, sc, m0, n0, g, tq);
     // O = Q S^T ...
     zero(accO);
-    gemm64<false, true>(accO, Qs, Ss, m0, n0, g, tq);
-    store_acc(Ds, acc, m0, n0, g, tq);
-    store_acc(As, sc, m0, n0, g, tq);
+    gemm64(accO, Qs, Ss, m0, n0, g, tq);
     __syncthreads();
     // ... + A Dl
-    gemm64<false, false>(accO, As, Ds, m0, n0, g, tq);
+    gemm64(accO, As, DsT, m0, n0, g, tq);
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
@@ -329,7 +402,7 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
       if (m0 + g + 8 < nvalid) Pair<T>::st(out + base + (size_t)(m0 + g + 8) * kDim + cc, accO[nt][2], accO[nt][3]);
     }
     // S += Dl^T K   (rows d, columns m)
-    gemm64<true, false>(S, Ds, Ks, m0, n0, g, tq);
+    gemm64(S, DsT, KsT, m0, n0, g, tq);
     __syncthreads();               // tiles are rewritten by the next chunk
   }
   T *fp = final_state + (size_t)b * kDim * kDim;
@@ -341,30 +414,22 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
   }
 }
 
-// this thread's accumulator-fragment positions -> fp32 [64][64] block in global memory
-__device__ __forceinline__ void store_frag(float *dst, const float (&acc)[kNT][4], int m0, int n0, int g, int tq) {
-#pragma unroll
-  for (int nt = 0; nt < kNT; ++nt) {
-    const int cc = n0 + 8 * nt + 2 * tq;
-    *reinterpret_cast<float2 *>(dst + (size_t)(m0 + g) * kDim + cc) = make_float2(acc[nt][0], acc[nt][1]);
-    *reinterpret_cast<float2 *>(dst + (size_t)(m0 + g + 8) * kDim + cc) = make_float2(acc[nt][2], acc[nt][3]);
-  }
-}
-
 // ---- backward, sequential part: one CTA per batch row, chunks in reverse ------------------------
 // Only what depends on the chunk after it: the walked-back state S0, E = d_value and the state
-// gradient R.  S0, R_end and E of every chunk go to scratch for the chunk-parallel kernel below.
+// gradient R.  S0^T, R_end^T and E of every chunk go to scratch for the chunk-parallel kernel below.
 template <typename T>
 __global__ void __launch_bounds__(kSeqThreads, 1)
 dfw_chunk_bwd_seq_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T *__restrict__ q,
                          const T *__restrict__ k, const float *__restrict__ delta,
                          const T *__restrict__ final_state, const float *__restrict__ Wb,
-                         const float *__restrict__ Ub, float *__restrict__ Sc, float *__restrict__ Rc,
+                         const float *__restrict__ Ub, float *__restrict__ ScT, float *__restrict__ RcT,
                          float *__restrict__ Ec, T *__restrict__ dv, T *__restrict__ ds, int64_t T_,
                          int64_t nc) {
   extern __shared__ __align__(16) float sm[];
-  float *Qs = sm, *Ks = Qs + kC * kLd, *Gs = Ks + kC * kLd, *Ds = Gs + kC * kLd, *Ws = Ds + kC * kLd,
-        *Es = Ws + kC * kLd, *Rs = Es + kC * kLd;
+  constexpr int kTileF = kC * kLdV;
+  // K^T [m][t], Q^T [m][t], dO^T [d][t], Dl^T [d][t], Wb [t][m], E^T [d][t], R [d][m]
+  float *KsT = sm, *QsT = KsT + kTileF, *GsT = QsT + kTileF, *DsT = GsT + kTileF, *Ws = DsT + kTileF,
+        *EsT = Ws + kTileF, *Rs = EsT + kTileF;
   const int64_t b = blockIdx.x;
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
   const int m0 = 16 * (w & 3), n0 = 8 * kNT * (w >> 2);
@@ -381,7 +446,6 @@ dfw_chunk_bwd_seq_kernel(const T *__restrict__ go, const T *__restrict__ gs, con
       S[nt][0] = lo.x; S[nt][1] = lo.y; S[nt][2] = hi.x; S[nt][3] = hi.y;
     }
   }
-  // global loads of a chunk, into registers: issued one chunk ahead
   uint4 rq, rk, rg;
   float4 rd[2], rw[2];
   float2 ru[kNT][2];
@@ -389,11 +453,11 @@ dfw_chunk_bwd_seq_kernel(const T *__restrict__ go, const T *__restrict__ gs, con
     const int64_t t0 = c * kC;
     const int nv = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
     const size_t base = ((size_t)b * T_ + t0) * kDim, tile = ((size_t)b * nc + c) * kC * kDim;
-    rq = fetch16<T>(q + base, nv, tid);
-    rk = fetch16<T>(k + base, nv, tid);
-    rg = fetch16<T>(go + base, nv, tid);
-    fetch32(rd, delta + base, nv, tid);
-    fetch32(rw, Wb + tile, kC, tid);
+    rq = fetch16<T, true>(q + base, nv, tid);
+    rk = fetch16<T, true>(k + base, nv, tid);
+    rg = fetch16<T, true>(go + base, nv, tid);
+    fetch32<true>(rd, delta + base, nv, tid);
+    fetch32<false>(rw, Wb + tile, kC, tid);
     fetch_frag(ru, Ub + tile, m0, n0, g, tq);
   };
   fetch(nc - 1);
@@ -401,31 +465,31 @@ dfw_chunk_bwd_seq_kernel(const T *__restrict__ go, const T *__restrict__ gs, con
     const int64_t t0 = c * kC;
     const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
     const size_t base = ((size_t)b * T_ + t0) * kDim, tile = ((size_t)b * nc + c) * kC * kDim;
-    commit16<T>(Qs, rq, tid);
-    commit16<T>(Ks, rk, tid);
-    commit16<T>(Gs, rg, tid);
-    commit32(Ds, rd, tid);
+    commit16_t<T>(QsT, rq, tid);
+    commit16_t<T>(KsT, rk, tid);
+    commit16_t<T>(GsT, rg, tid);
+    commit32_t(DsT, rd, tid);
     commit32(Ws, rw, tid);
     float2 uf[kNT][2];
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt) { uf[nt][0] = ru[nt][0]; uf[nt][1] = ru[nt][1]; }
     store_acc(Rs, R, m0, n0, g, tq);
-    store_frag(Rc + tile, R, m0, n0, g, tq);
+    store_frag_t(RcT + tile, R, m0, n0, g, tq);
     __syncthreads();
     if (c > 0) fetch(c - 1);
 
     float acc[kNT][4];
     // S0 = S_end - Dl^T K
     zero(acc);
-    gemm64<true, false>(acc, Ds, Ks, m0, n0, g, tq);
+    gemm64(acc, DsT, KsT, m0, n0, g, tq);
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) S[nt][e] -= acc[nt][e];
-    store_frag(Sc + tile, S, m0, n0, g, tq);
+    store_frag_t(ScT + tile, S, m0, n0, g, tq);
     // E = Ub + Wb R_end^T = d_value
     zero(acc);
-    gemm64<false, true>(acc, Ws, Rs, m0, n0, g, tq);
+    gemm64(acc, Ws, Rs, m0, n0, g, tq);
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt) {
       const int cc = n0 + 8 * nt + 2 * tq;
@@ -434,13 +498,13 @@ dfw_chunk_bwd_seq_kernel(const T *__restrict__ go, const T *__restrict__ gs, con
       if (m0 + g < nvalid) Pair<T>::st(dv + base + (size_t)(m0 + g) * kDim + cc, acc[nt][0], acc[nt][1]);
       if (m0 + g + 8 < nvalid) Pair<T>::st(dv + base + (size_t)(m0 + g + 8) * kDim + cc, acc[nt][2], acc[nt][3]);
     }
-    store_acc(Es, acc, m0, n0, g, tq);
+    store_acc_t(EsT, acc, m0, n0, g, tq);
     store_frag(Ec + tile, acc, m0, n0, g, tq);
-    __syncthreads();               // E tile complete
+    __syncthreads();               // E^T tile complete
     // R_start = R_end + dO^T Q - E^T K
-    gemm64<true, false>(R, Gs, Qs, m0, n0, g, tq);
+    gemm64(R, GsT, QsT, m0, n0, g, tq);
     zero(acc);
-    gemm64<true, false>(acc, Es, Ks, m0, n0, g, tq);
+    gemm64(acc, EsT, KsT, m0, n0, g, tq);
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt)
 #pragma unroll
@@ -460,72 +524,73 @@ dfw_chunk_bwd_seq_kernel(const T *__restrict__ go, const T *__restrict__ gs, con
 template <typename T>
 __global__ void __launch_bounds__(kSeqThreads, 1)
 dfw_chunk_bwd_par_kernel(const T *__restrict__ go, const T *__restrict__ q, const T *__restrict__ k,
-                         const float *__restrict__ delta, const float *__restrict__ Sc,
-                         const float *__restrict__ Rc, const float *__restrict__ Ec, T *__restrict__ dq,
+                         const float *__restrict__ delta, const float *__restrict__ ScT,
+                         const float *__restrict__ RcT, const float *__restrict__ Ec, T *__restrict__ dq,
                          T *__restrict__ dk, int64_t T_, int64_t nc) {
   extern __shared__ __align__(16) float sm[];
-  float *Qs = sm, *Ks = Qs + kC * kLd, *Gs = Ks + kC * kLd, *Ds = Gs + kC * kLd, *Es = Ds + kC * kLd,
-        *Rs = Es + kC * kLd, *Ss = Rs + kC * kLd, *X1s = Ss + kC * kLd, *X2s = X1s + kC * kLd;
+  constexpr int kTileF = kC * kLdV;
+  // dO [t][d], Dl [t][d], E [t][d], S0^T [m][d], R_end^T [m][d], K^T [m][t], Q^T [m][t],
+  // X1 = strict_lower(dO Dl^T) [t][i] and its transpose, Y = strict_upper(X2) + its mirror image, X2 = Dl E^T
+  float *Gs = sm, *Ds = Gs + kTileF, *Es = Ds + kTileF, *SsT = Es + kTileF, *RsT = SsT + kTileF,
+        *KsT = RsT + kTileF, *QsT = KsT + kTileF, *X1s = QsT + kTileF, *X1sT = X1s + kTileF, *Ys = X1sT + kTileF;
   const int64_t b = blockIdx.x / nc, c = blockIdx.x % nc, t0 = c * kC;
   const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
   const size_t base = ((size_t)b * T_ + t0) * kDim, tile = (size_t)blockIdx.x * kC * kDim;
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
   const int m0 = 16 * (w & 3), n0 = 8 * kNT * (w >> 2);
   {
-    const uint4 rq = fetch16<T>(q + base, nvalid, tid), rk = fetch16<T>(k + base, nvalid, tid),
-                rg = fetch16<T>(go + base, nvalid, tid);
+    const uint4 rq = fetch16<T, true>(q + base, nvalid, tid), rk = fetch16<T, true>(k + base, nvalid, tid),
+                rg = fetch16<T, false>(go + base, nvalid, tid);
     float4 rd[2], re[2], rs[2], rr[2];
-    fetch32(rd, delta + base, nvalid, tid);
-    fetch32(re, Ec + tile, kC, tid);
-    fetch32(rs, Sc + tile, kC, tid);
-    fetch32(rr, Rc + tile, kC, tid);
-    commit16<T>(Qs, rq, tid);
-    commit16<T>(Ks, rk, tid);
-    commit16<T>(Gs, rg, tid);
+    fetch32<false>(rd, delta + base, nvalid, tid);
+    fetch32<false>(re, Ec + tile, kC, tid);
+    fetch32<false>(rs, ScT + tile, kC, tid);
+    fetch32<false>(rr, RcT + tile, kC, tid);
+    commit16_t<T>(QsT, rq, tid);
+    commit16_t<T>(KsT, rk, tid);
+    commit16<T, false>(Gs, rg, tid);
     commit32(Ds, rd, tid);
     commit32(Es, re, tid);
-    commit32(Ss, rs, tid);
-    commit32(Rs, rr, tid);
+    commit32(SsT, rs, tid);
+    commit32(RsT, rr, tid);
   }
   __syncthreads();
-  float acc[kNT][4], acc2[kNT][4];
-  // X1 = strict_lower(dO Dl^T)
+  float acc[kNT][4], acc2[kNT][4], acck[kNT][4];
+  // X1 = strict_lower(dO Dl^T), kept in both orientations
   zero(acc);
-  gemm64<false, true>(acc, Gs, Ds, m0, n0, g, tq);
-#pragma unroll
-  for (int nt = 0; nt < kNT; ++nt) {
-    const int cc = n0 + 8 * nt + 2 * tq;
-    acc[nt][0] = (cc < m0 + g) ? acc[nt][0] : 0.f;
-    acc[nt][1] = (cc + 1 < m0 + g) ? acc[nt][1] : 0.f;
-    acc[nt][2] = (cc < m0 + g + 8) ? acc[nt][2] : 0.f;
-    acc[nt][3] = (cc + 1 < m0 + g + 8) ? acc[nt][3] : 0.f;
-  }
+  gemm64(acc, Gs, Ds, m0, n0, g, tq);
+  mask_tri<true>(acc, m0, n0, g, tq);
   store_acc(X1s, acc, m0, n0, g, tq);
-  // X2 = strict_upper(Dl E^T)
+  store_acc_t(X1sT, acc, m0, n0, g, tq);
+  // Y = strict_upper(X2) + strict_lower(X2^T), X2 = Dl E^T: every thread writes its elements above
+  // the diagonal to both mirror positions and zeroes the diagonal
   zero(acc);
-  gemm64<false, true>(acc, Ds, Es, m0, n0, g, tq);
+  gemm64(acc, Ds, Es, m0, n0, g, tq);
 #pragma unroll
   for (int nt = 0; nt < kNT; ++nt) {
-    const int cc = n0 + 8 * nt + 2 * tq;
-    acc[nt][0] = (cc > m0 + g) ? acc[nt][0] : 0.f;
-    acc[nt][1] = (cc + 1 > m0 + g) ? acc[nt][1] : 0.f;
-    acc[nt][2] = (cc > m0 + g + 8) ? acc[nt][2] : 0.f;
-    acc[nt][3] = (cc + 1 > m0 + g + 8) ? acc[nt][3] : 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int r = m0 + g + 8 * (e >> 1), cc = n0 + 8 * nt + 2 * tq + (e & 1);
+      const float v = round_tf32(acc[nt][e]);
+      if (cc > r) {
+        Ys[r * kLdV + cc] = v;
+        Ys[cc * kLdV + r] = v;
+      } else if (cc == r) {
+        Ys[r * kLdV + cc] = 0.f;
+      }
+    }
   }
-  store_acc(X2s, acc, m0, n0, g, tq);
-  // d_query = dO S0 + X1 K ;  d_key = Dl R_end + X1^T Q - (X2 + X2^T) K - E S0
+  // d_query = dO S0 + X1 K ;  d_key = Dl R_end + X1^T Q - Y K - E S0
   zero(acc);
-  gemm64<false, false>(acc, Gs, Ss, m0, n0, g, tq);
+  gemm64(acc, Gs, SsT, m0, n0, g, tq);
   zero(acc2);
-  gemm64<false, false>(acc2, Es, Ss, m0, n0, g, tq);
-  float acck[kNT][4];
+  gemm64(acc2, Es, SsT, m0, n0, g, tq);
   zero(acck);
-  gemm64<false, false>(acck, Ds, Rs, m0, n0, g, tq);
-  __syncthreads();                 // X1, X2 tiles complete
-  gemm64<false, false>(acc, X1s, Ks, m0, n0, g, tq);
-  gemm64<true, false>(acck, X1s, Qs, m0, n0, g, tq);
-  gemm64<false, false>(acc2, X2s, Ks, m0, n0, g, tq);
-  gemm64<true, false>(acc2, X2s, Ks, m0, n0, g, tq);
+  gemm64(acck, Ds, RsT, m0, n0, g, tq);
+  __syncthreads();                 // X1, X1^T, Y tiles complete
+  gemm64(acc, X1s, KsT, m0, n0, g, tq);
+  gemm64(acck, X1sT, QsT, m0, n0, g, tq);
+  gemm64(acc2, Ys, KsT, m0, n0, g, tq);
 #pragma unroll
   for (int nt = 0; nt < kNT; ++nt) {
     const int cc = n0 + 8 * nt + 2 * tq;
@@ -540,7 +605,8 @@ dfw_chunk_bwd_par_kernel(const T *__restrict__ go, const T *__restrict__ q, cons
   }
 }
 
-constexpr size_t kTileBytes = (size_t)kC * kLd * sizeof(float);
+constexpr size_t kTileBytes = (size_t)kC * kLd * sizeof(float);     // prep kernel tiles
+constexpr size_t kTileVBytes = (size_t)kC * kLdV * sizeof(float);   // tiles of the chunk kernels
 constexpr size_t kPrepTile = kTileBytes;
 
 inline size_t wu_floats(int64_t B, int64_t nc) { return (size_t)B * nc * kC * kDim; }
@@ -567,8 +633,8 @@ static int dfw_chunk_forward_typed(const void *q, const void *k, const void *v, 
   dfw_chunk_prep_kernel<T, false><<<(unsigned)(B * nc), 128, 3 * kPrepTile, st>>>(
       (const T *)q, (const T *)k, (const T *)v, W, U, T_, nc);
   T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_fwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)(6 * kTileBytes)));
-  dfw_chunk_fwd_kernel<T><<<(unsigned)B, kSeqThreads, 6 * kTileBytes, st>>>(
+                                       (int)(7 * kTileVBytes)));
+  dfw_chunk_fwd_kernel<T><<<(unsigned)B, kSeqThreads, 7 * kTileVBytes, st>>>(
       (const T *)q, (const T *)k, (const T *)state, W, U, (T *)out, (T *)final_state, (float *)delta, T_, nc);
   T2FW_CHECK_LAUNCH(2);
   return T2FW_OK;
@@ -594,13 +660,13 @@ static int dfw_chunk_backward_typed(const void *go, const void *gs, const void *
       (const T *)q, (const T *)k, (const T *)go, Wb, Ub, T_, nc);
   float *Sc = Ub + wu_floats(B, nc), *Rc = Sc + wu_floats(B, nc), *Ec = Rc + wu_floats(B, nc);
   T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_seq_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)(7 * kTileBytes)));
-  dfw_chunk_bwd_seq_kernel<T><<<(unsigned)B, kSeqThreads, 7 * kTileBytes, st>>>(
+                                       (int)(7 * kTileVBytes)));
+  dfw_chunk_bwd_seq_kernel<T><<<(unsigned)B, kSeqThreads, 7 * kTileVBytes, st>>>(
       (const T *)go, (const T *)gs, (const T *)q, (const T *)k, (const float *)delta, (const T *)final_state, Wb,
       Ub, Sc, Rc, Ec, (T *)dv, (T *)ds, T_, nc);
   T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_par_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)(9 * kTileBytes)));
-  dfw_chunk_bwd_par_kernel<T><<<(unsigned)(B * nc), kSeqThreads, 9 * kTileBytes, st>>>(
+                                       (int)(10 * kTileVBytes)));
+  dfw_chunk_bwd_par_kernel<T><<<(unsigned)(B * nc), kSeqThreads, 10 * kTileVBytes, st>>>(
       (const T *)go, (const T *)q, (const T *)k, (const float *)delta, Sc, Rc, Ec, (T *)dq, (T *)dk, T_, nc);
   T2FW_CHECK_LAUNCH(3);
   return T2FW_OK;
