@@ -543,18 +543,22 @@ def run_ours(args):
         # that step i's device->host copy overlaps step i+1's host->device copy and compute
         s_cmp = torch.cuda.current_stream(dev)
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-        res_host, out_done = [None, None], [None, None]
+        res_host, out_done, keep = [None, None], [None, None], [None, None]
 
         def e2e_step(i):
             nonlocal d2h
             slot = i & 1
+            # Tensors are shared between the three streams without record_stream: every tensor of a
+            # step stays referenced in keep[slot] until the step two before this one has finished
+            # its device->host copies, so the allocator never reuses memory that is still in use.
+            if out_done[slot] is not None:
+                out_done[slot].synchronize()      # the host is done with this set's previous results
+            keep[slot] = None
             with torch.cuda.stream(s_in):
                 devs = [t.to(dev, non_blocking=True) for t in srcs]
                 ev_in = torch.cuda.Event()
                 ev_in.record(s_in)
             s_cmp.wait_event(ev_in)
-            for t in devs:
-                t.record_stream(s_cmp)
             if dfw:
                 leaves = [t.requires_grad_(True) for t in devs[:4]]
                 out, nxt = DFWFunction.apply(*leaves)
@@ -574,16 +578,14 @@ def run_ours(args):
             if res_host[slot] is None:
                 res_host[slot] = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in results]
                 d2h = sum(r.numel() * r.element_size() for r in results)
-            if out_done[slot] is not None:
-                out_done[slot].synchronize()      # the host is done with this set's previous results
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_c)
                 for h, r in zip(res_host[slot], results):
-                    r.record_stream(s_out)
                     h.copy_(r, non_blocking=True)
                 done = torch.cuda.Event()
                 done.record(s_out)
             out_done[slot] = done
+            keep[slot] = (devs, results)
 
         def e2e_drain():
             s_cmp.wait_stream(s_in)
