@@ -86,17 +86,38 @@ dfw_chunk_prep_kernel(const T *__restrict__ q, const T *__restrict__ k, const T 
   const size_t base = ((size_t)b * T_ + t0) * kDim;
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
 
-  for (int idx = tid; idx < kC * (kDim / 2); idx += 128) {
-    const int r = idx / (kDim / 2), c2 = (idx % (kDim / 2)) * 2;
-    float2 kk = make_float2(0.f, 0.f), vv = kk, qq = kk;
-    if (r < nvalid) {
-      kk = Pair<T>::ld(k + base + (size_t)r * kDim + c2);
-      vv = Pair<T>::ld(v_or_go + base + (size_t)r * kDim + c2);
-      if (kBwd) qq = Pair<T>::ld(q + base + (size_t)r * kDim + c2);
+  // 512 16-byte pieces per [64][64] block, 4 per thread and tensor; all loads are issued before
+  // the first conversion so that their latencies overlap
+  {
+    uint4 rk[4], rv[4], rq[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int idx = tid + 128 * j, r = idx >> 3, c8 = (idx & 7) * 8;
+      const bool in = r < nvalid;
+      const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+      rk[j] = in ? *reinterpret_cast<const uint4 *>(k + base + (size_t)r * kDim + c8) : z;
+      rv[j] = in ? *reinterpret_cast<const uint4 *>(v_or_go + base + (size_t)r * kDim + c8) : z;
+      if (kBwd) rq[j] = in ? *reinterpret_cast<const uint4 *>(q + base + (size_t)r * kDim + c8) : z;
     }
-    *reinterpret_cast<float2 *>(Ks + r * kLd + c2) = kk;
-    *reinterpret_cast<float2 *>(Vs + r * kLd + c2) = vv;
-    if (kBwd) *reinterpret_cast<float2 *>(Qs + r * kLd + c2) = qq;
+    auto put = [&](float *t, const uint4 &u, int idx) {
+      const int r = idx >> 3, c8 = (idx & 7) * 8;
+      const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+      float vals[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 p2 = Pair<T>::ld(reinterpret_cast<const T *>(&w4[e]));
+        vals[2 * e] = p2.x;
+        vals[2 * e + 1] = p2.y;
+      }
+      *reinterpret_cast<float4 *>(t + r * kLd + c8) = make_float4(vals[0], vals[1], vals[2], vals[3]);
+      *reinterpret_cast<float4 *>(t + r * kLd + c8 + 4) = make_float4(vals[4], vals[5], vals[6], vals[7]);
+    };
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      put(Ks, rk[j], tid + 128 * j);
+      put(Vs, rv[j], tid + 128 * j);
+      if (kBwd) put(Qs, rq[j], tid + 128 * j);
+    }
   }
   __syncthreads();
 
