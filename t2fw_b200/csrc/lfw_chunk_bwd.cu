@@ -116,7 +116,7 @@ lfw_chunk_bwd_local_kernel(const T *__restrict__ go, const T *__restrict__ f, co
 // R_end(c-1) = (Ac Gc^T) R_end(c) + G_c, from the last chunk (R_end = grad_state) down; G_c is
 // overwritten with R_end(c).  The value left after chunk 0 is d_state.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 6)
 lfw_chunk_bwd_carry_kernel(const T *__restrict__ grad_state, float *__restrict__ G,
                            const float *__restrict__ Ac, const float *__restrict__ Gc,
                            const int *__restrict__ flags, int *__restrict__ rowflag,

@@ -123,7 +123,7 @@ lfw_chunk_local_kernel(const T *__restrict__ x, const T *__restrict__ f, const T
 // One thread per (b, d, 4 consecutive k): S_{c+1} = (Ac Gc^T) S_c + L_c.  L_c is overwritten with
 // the state at the START of chunk c; ckpt slot c receives the state after chunk c.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 6)
 lfw_chunk_carry_kernel(const T *__restrict__ state, float *__restrict__ L, const float *__restrict__ Ac,
                        const float *__restrict__ Gc, const int *__restrict__ flags,
                        int *__restrict__ rowflag, T *__restrict__ ckpt, int64_t B, int64_t nc) {
