@@ -17,7 +17,7 @@ namespace t2fw {
 namespace {
 
 constexpr int kThreads = 128;
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr uint32_t kSpinLimit = 1u << 19;   // polls (each may suspend up to ~2 us) before giving up
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
