@@ -99,6 +99,10 @@ constexpr int oRaw = oStg + 2 * kStgBytes;        // x, f, q, k, fk, dO raw bloc
 constexpr int kSmem = oRaw + 6 * kRawBytes;
 static_assert(kSmem + 256 <= 227 * 1024, "shared memory budget");
 static_assert(oRaw % 128 == 0 && oStg % 16 == 0, "alignment of the bulk-copy and staging areas");
+// The S0 / R~ tiles are double-buffered by sub-block parity; the second buffer lives in the raw
+// input area, which is dead between the operand preparation and the prefetch of the next chunk.
+constexpr int oS1 = oRaw, oR1 = oRaw + 2 * kTile;
+static_assert(4 * kTile <= 6 * kRawBytes, "second tile buffer fits the raw input area");
 
 // tensor-memory columns.  Lanes A = lanes 0-15 of every quarter, lanes B = lanes 16-31.
 constexpr int cS = 0;        // A: S[0..3] at 64*I (1..3 first hold Xt Kt^T of the block before);
@@ -111,7 +115,7 @@ constexpr int cPZ = 384;     // A: P, B: Z (whole chunk)
 constexpr int kBarH = 5;     // the helper warps among themselves
 constexpr int kBarA = 6;     // workers -> helpers: tiles of a block published
 constexpr int kBarB = 7;     // (7, 8) workers -> helpers: staging of a block complete
-constexpr int kBarY = 9;     // helpers -> workers: exact path done, earlier staging written out
+constexpr int kBarY = 9;     // (9, 10) helpers -> workers: exact path done, earlier staging written out
 
 __device__ __forceinline__ void sync_all() {
   umma::fence_before_sync();
@@ -248,7 +252,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
                           int *__restrict__ rowflag, int *__restrict__ status, int64_t T_, int64_t nc,
                           int64_t total) {
   extern __shared__ __align__(128) unsigned char sm[];
-  __shared__ __align__(8) uint64_t barM, barRaw;
+  __shared__ __align__(8) uint64_t barM[2], barR, barRaw;   // barM: by sub-block parity (pre-phase rounds use [0])
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int s_fail;
   __shared__ int fix_n[kNSub];
@@ -292,7 +296,9 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
 
   bool raw_pending = false;   // thread 0: a prefetch has been issued and not yet awaited
   if (threadIdx.x == 0) {
-    umma::mbar_init(&barM, kHelpers);
+    umma::mbar_init(&barM[0], kHelpers);
+    umma::mbar_init(&barM[1], kHelpers);
+    umma::mbar_init(&barR, 1);
     umma::mbar_init(&barRaw, 1);
     umma::mbar_fence_init();
     s_fail = 0;
@@ -308,15 +314,24 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
   }
 
   const uint32_t aQ = umma::smem_u32(sm + oQ), aK = umma::smem_u32(sm + oK), aX = umma::smem_u32(sm + oX);
-  const uint32_t aO = umma::smem_u32(sm + oO), aS = umma::smem_u32(sm + oS), aR = umma::smem_u32(sm + oR);
+  const uint32_t aO = umma::smem_u32(sm + oO), aS0 = umma::smem_u32(sm + oS), aR0 = umma::smem_u32(sm + oR);
+  const uint32_t aS1 = umma::smem_u32(sm + oS1), aR1 = umma::smem_u32(sm + oR1);
   const uint32_t aP = umma::smem_u32(sm + oP), aZ = umma::smem_u32(sm + oZ);
   const uint32_t dA = tb, dB = umma::tmem_addr(tb, 16, 0);   // lane sets
 
-  uint32_t pm = 0, praw = 0;     // mbarrier phase parities
+  uint32_t pm[2] = {0u, 0u}, pr_ = 0, praw = 0;     // mbarrier phase parities
   // the workers wait for the MMAs of the current round; every helper arrives once per round
-  auto wait_mma = [&]() {
-    if (!s_fail && !umma::mbar_wait(&barM, pm)) s_fail = 1;   // after a failure: no more waiting
-    pm ^= 1u;
+  // dOt Qt^T of a block (the first MMAs issued for it): all the next tile publish waits for
+  auto wait_rupd = [&]() {
+    if (!s_fail && !umma::mbar_wait(&barR, pr_)) s_fail = 1;
+    pr_ ^= 1u;
+    umma::fence_after_sync();
+  };
+  // Two barriers, used alternately: the MMAs of a block are committed while the workers may not
+  // yet have looked at the barrier of the block before it.
+  auto wait_mma = [&](int which) {
+    if (!s_fail && !umma::mbar_wait(&barM[which], which ? pm[1] : pm[0])) s_fail = 1;   // after a failure: no more waiting
+    if (which) pm[1] ^= 1u; else pm[0] ^= 1u;
     umma::fence_after_sync();
   };
 
@@ -444,10 +459,6 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
     }
     umma::fence_async_smem();
     sync_all();                       // tiles complete; raw blocks, S0 and R_end buffers consumed
-    if (threadIdx.x == 0 && ci + gridDim.x < total) {
-      issue_raw(ci + gridDim.x);
-      raw_pending = true;
-    }
     if (threadIdx.x == 0 && !(__uint_as_float(div_max[0]) * __uint_as_float(div_max[1]) <= kDivProdHi))
       atomicExch(rowflag + b, 1);
     PROF(2);
@@ -465,9 +476,9 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
       } else {
         gemm3<false, false, kDim, kDim, 1, kDim, false>(dA + cS + 192, dlo<false, kDim>(aX, 0, 2), dlo<false, kDim>(aK, 0, 2));
       }
-      umma::mma_commit(&barM);
+      umma::mma_commit(&barM[0]);
     }
-    if (worker) wait_mma();
+    if (worker) wait_mma(0);
     sync_all();
     if (s_fail) break;
     PROF(3);
@@ -517,11 +528,8 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
       const int J = I + 1;      // the block whose results are finished in this iteration
       T *stg = reinterpret_cast<T *>(sm + oStg + (J & 1) * kStgBytes);
       if (worker) {
-        if (I < kNSub - 1) {
-          umma::named_barrier(kBarY, kTAll);
-          umma::fence_after_sync();
-        }
         if (I < 0 && ci + gridDim.x < total) prefetch_rows(ci + gridDim.x);   // R is no longer live
+        if (I >= 0 && I < kNSub - 1) wait_rupd();     // dOt Qt^T of block I+1
         if (I >= 0) {
           // lanes A: S[I];  lanes B: dOt Qt^T of block I+1 (the part of R that block added)
           float v[16];
@@ -542,7 +550,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
               }
             }
           }
-          unsigned char *th = sm + (side ? oR : oS);
+          unsigned char *th = sm + ((I & 1) ? (side ? oR1 : oS1) : (side ? oR : oS));
           write8<kTile>(th, umma::tile16_off(feat, 16 * part, kDim), v);
           write8<kTile>(th, umma::tile16_off(feat, 16 * part + 8, kDim), v + 8);
           // boundary terms sum_d R~ .* S0 (k side) and sum_k R~ .* S0 (d side): the two half warps
@@ -564,6 +572,13 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
         }
         PROF(5);
         if (I < kNSub - 1) {
+          wait_mma(J & 1);                                       // every MMA of block J
+          umma::named_barrier(kBarY + (J & 1), kTAll);           // the helpers are done with block J's tiles
+          umma::fence_after_sync();
+          if (I == 0 && threadIdx.x == 0 && ci + gridDim.x < total) {
+            issue_raw(ci + gridDim.x);     // block 1 was the last user of the tile buffer in the raw area
+            raw_pending = true;
+          }
           // ---- feature-major epilogue of block J: this thread = one feature, 4 steps -------------
           const int cres = (J & 1) ? cTs : cRes0;
           float r0v[4], r1v[4], r2v[4];
@@ -622,8 +637,6 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
           bar_arrive(kBarB + (I & 1), kTAll);
         }
         PROF(6);
-        if (I >= 0) wait_mma();     // the MMAs of block I
-        PROF(7);
       } else {
         if (I >= 0) {
           PROFH(5);
@@ -633,11 +646,15 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
           if (lane == 0) {
             const int cres = (I & 1) ? cTs : cRes0;
             const uint32_t zI = aZ + I * 2 * kTileS, pI = aP + I * 2 * kTileS;
+            const uint32_t aS = (I & 1) ? aS1 : aS0, aR = (I & 1) ? aR1 : aR0;
             if (hw == 0) {
-              // dOt Qt^T of this block first: the next (earlier) sub-block needs it soonest
-              if (I > 0)
+              // dOt Qt^T of this block first, with its own barrier: the tile publish of the next
+              // (earlier) sub-block waits for nothing else
+              if (I > 0) {
                 gemm3<false, false, kDim, kDim, 1, kDim, false>(dB + cS + 64 * (I - 1), dlo<false, kDim>(aO, 0, I),
                                                                 dlo<false, kDim>(aQ, 0, I));
+                umma::mma_commit(&barR);
+              }
               // TQ = S0^T dOt + Kt Z^T
               gemm3<true, true, kDim, kDim, 4, kSub, false>(dA + cres, dlo<true, kDim>(aS, 0, 0), dlo<true, kDim>(aO, r0, 0));
               gemm3<false, false, kDim, kSub, 1, kSub, true>(dA + cres, dlo<false, kDim>(aK, 0, I), dlo<false, kSub>(zI, 0, 0));
@@ -654,7 +671,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
               gemm3<false, true, kDim, kDim, 4, kSub, false>(dB + cres + 32, dlo<false, kDim>(aR, 0, 0), dlo<true, kDim>(aK, r0, 0));
               gemm3<false, true, kDim, kSub, 1, kSub, false>(dB + cres + 16, dlo<false, kDim>(aO, 0, I), dlo<true, kSub>(pI, 0, 0));
             }
-            umma::mma_commit(&barM);
+            umma::mma_commit(&barM[I & 1]);
           }
           __syncwarp();
           PROFH(1);
@@ -674,7 +691,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
             // the lane, the K / Q row of the fixed feature is shared; d side: roles exchanged
             const unsigned char *var = sm + (wh ? (ds ? oQ : oO) : (ds ? oK : oX));
             const unsigned char *fix = sm + (wh ? (ds ? oO : oQ) : (ds ? oX : oK));
-            const unsigned char *st0 = sm + (wh ? oR : oS);
+            const unsigned char *st0 = sm + ((I & 1) ? (wh ? oR1 : oS1) : (wh ? oR : oS));
             float val = ds ? rd1(st0, col, o) : rd1(st0, o, col);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -694,7 +711,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
           }
           if (ht == 0) acp::bulk_wait_read<0>();   // the earlier write-outs have left shared memory
           __threadfence_block();
-          bar_arrive(kBarY, kTAll);
+          bar_arrive(kBarY + (I & 1), kTAll);
           PROFH(2);
         }
         if (I < kNSub - 1) {
