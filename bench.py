@@ -219,7 +219,7 @@ def cpu_reference_run(workload, gates, steps, warmup, seed):
 
 
 def run_gpt2(args):
-    """BASELINE config 5: GPT-2-small (12 layers, d_model 768, 12 heads, 124 M parameters, random
+    """The end-to-end configuration: GPT-2-small (12 layers, d_model 768, 12 heads, 124 M parameters, random
     init), every attention replaced by a fast-weight layer, fp16, sequence 1024, batch 8 per GPU,
     random token ids; one step = forward + backward + DDP gradient all-reduce + AdamW update."""
     import torch
@@ -339,8 +339,8 @@ def run_reference(args):
     if rank != 0:
         return
     if args.workload == "gpt2":
-        print(json.dumps({"impl": "reference", "unavailable": "the reference ships no model: BASELINE "
-                          "config 5 has no reference implementation and no CPU baseline"}))
+        print(json.dumps({"impl": "reference", "unavailable": "the reference ships no model: the end-to-end "
+                          "GPT-2 configuration has no reference implementation and no CPU baseline"}))
         return
     steps = max(1, min(args.steps, 5))
     warmup = max(2, min(args.warmup, 3))

@@ -9,7 +9,7 @@
 // while checkpoints, next state and d_state are block-local.  The blocks are laid out as a
 // virtual batch of B * (D/64) * (K/64) rows with 64-wide contiguous vectors, run through the
 // chunked 64 x 64 kernels (and, for rows they flag, the scan kernels), and the per-block
-// results are summed in fp32.  This is what makes BASELINE config 4 (D = K = 128, T = 16384)
+// results are summed in fp32.  This is what makes the long-sequence configuration (D = K = 128, T = 16384)
 // run on the tensor-core path.
 #include <type_traits>
 

@@ -97,7 +97,7 @@ constexpr int oFixVal = oFixRg + kNSub * kFixCap * 4;    // [2][kFixCap] float: 
 constexpr int oStg = oFixVal + 2 * kFixCap * 4;   // [2 buffers] 5 tiles [16][kStgLd] 16-bit
 constexpr int oRaw = oStg + 2 * kStgBytes;        // x, f, q, k, fk, dO raw blocks
 constexpr int kSmem = oRaw + 6 * kRawBytes;
-static_assert(kSmem + 256 <= 227 * 1024, "shared memory budget");
+static_assert(kSmem + 256 <= 227 * 1024, "shared memory limit");
 static_assert(oRaw % 128 == 0 && oStg % 16 == 0, "alignment of the bulk-copy and staging areas");
 // The S0 / R~ tiles are double-buffered by sub-block parity; the second buffer lives in the raw
 // input area, which is dead between the operand preparation and the prefetch of the next chunk.
@@ -463,7 +463,7 @@ lfw_chunk_bwd_umma_kernel(const T *__restrict__ go, const T *__restrict__ x, con
       atomicExch(rowflag + b, 1);
     PROF(2);
 
-    // ---- round 1: P = Qt^T Kt (lanes A), Z = dOt^T Xt (lanes B) for the whole chunk, and the
+    // ---- first MMA round: P = Qt^T Kt (lanes A), Z = dOt^T Xt (lanes B) for the whole chunk, and the
     //      local state increments U_J = Xt_J Kt_J^T of blocks 0..2 into the slots of S[1..3] --------
     if (issuer) {
       if (hw == 0) {
