@@ -23,6 +23,7 @@
 //   dfw_chunk_fwd_kernel<T>          one CTA per batch row, sequential over chunks
 //   dfw_chunk_bwd_seq_kernel<T>      one CTA per batch row, chunks in reverse: state walk-back, E, R
 //   dfw_chunk_bwd_par_kernel<T>      (batch row, chunk): d_query and d_key from the stored S0, R_end, E
+#include <cstdlib>
 #include <type_traits>
 
 #include "lfw_chunk.cuh"
@@ -634,6 +635,18 @@ inline size_t wu_floats(int64_t B, int64_t nc) { return (size_t)B * nc * kC * kD
 
 }  // namespace
 
+// dfw_chunk_umma.cu: the forward chunk walk on the tcgen05 tensor core
+int dfw_chunk_forward_umma(const void *q, const void *k, const void *state, const float *W, const float *U,
+                           void *out, void *final_state, void *delta, int64_t B, int64_t T_, int dtype,
+                           cudaStream_t st);
+static bool dfw_umma_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("T2FW_DFW_UMMA");
+    return e && e[0] == '1';
+  }();
+  return on;
+}
+
 bool dfw_chunk_supported(int64_t D, int64_t M, int dtype) {
   return D == kDim && M == kDim && (dtype == T2FW_F16 || dtype == T2FW_BF16);
 }
@@ -653,6 +666,11 @@ static int dfw_chunk_forward_typed(const void *q, const void *k, const void *v, 
                                        (int)(3 * kPrepTile)));
   dfw_chunk_prep_kernel<T, false><<<(unsigned)(B * nc), 128, 3 * kPrepTile, st>>>(
       (const T *)q, (const T *)k, (const T *)v, W, U, T_, nc);
+  if (dfw_umma_enabled()) {
+    const int rc = dfw_chunk_forward_umma(q, k, state, W, U, out, final_state, delta, B, T_,
+                                          std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16, st);
+    if (rc != T2FW_ERR_UNSUPPORTED) return rc;
+  }
   T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_fwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)(7 * kTileVBytes)));
   dfw_chunk_fwd_kernel<T><<<(unsigned)B, kSeqThreads, 7 * kTileVBytes, st>>>(
