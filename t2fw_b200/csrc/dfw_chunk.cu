@@ -36,6 +36,10 @@ namespace {
 
 constexpr int kSeqThreads = 512;  // 16 warps: warp w owns rows 16*(w&3), columns 16*(w>>2) of a product
 constexpr int kNT = 2;            // 8-column accumulator tiles per warp
+// U and Ub tiles (the right-hand sides after substitution) are stored with rows of kLdU = 68 floats:
+// a tile then lands in shared memory by one bulk copy with its rows 17 x 16 bytes apart, which
+// lets threads that own consecutive rows read 16-byte pieces without bank conflicts
+constexpr int kLdU = kDim + 4;
 
 // ---- prep: W, U (forward) or Wb, Ub (backward) --------------------------------------------------
 // grid = B * nc, 128 threads (4 warps).  Output tiles are fp32 [64][64] row-major, rows beyond the
@@ -172,9 +176,11 @@ dfw_chunk_prep_kernel(const T *__restrict__ q, const T *__restrict__ k, const T 
       x[t] = a0 + a1;
     }
   }
-  float *dst = (second ? Uout : Wout) + (size_t)blockIdx.x * kC * kDim + col;
+  // the second tile has its rows padded to kLdU floats (see kLdU)
+  const int ld = second ? kLdU : kDim;
+  float *dst = (second ? Uout : Wout) + (size_t)blockIdx.x * kC * ld + col;
 #pragma unroll
-  for (int t = 0; t < kC; ++t) dst[t * kDim] = x[t];
+  for (int t = 0; t < kC; ++t) dst[t * ld] = x[t];
 }
 
 // ---- helpers of the chunk kernels ----------------------------------------------------------------
@@ -257,12 +263,13 @@ __device__ __forceinline__ void store_frag_t(float *dst, const float (&acc)[kNT]
     dst[(size_t)(cc + 1) * kDim + m0 + g + 8] = acc[nt][3];
   }
 }
+// accumulator-fragment-shaped read of a U / Ub tile (rows padded to kLdU floats)
 __device__ __forceinline__ void fetch_frag(float2 (&r)[kNT][2], const float *src, int m0, int n0, int g, int tq) {
 #pragma unroll
   for (int nt = 0; nt < kNT; ++nt) {
     const int cc = n0 + 8 * nt + 2 * tq;
-    r[nt][0] = *reinterpret_cast<const float2 *>(src + (size_t)(m0 + g) * kDim + cc);
-    r[nt][1] = *reinterpret_cast<const float2 *>(src + (size_t)(m0 + g + 8) * kDim + cc);
+    r[nt][0] = *reinterpret_cast<const float2 *>(src + (size_t)(m0 + g) * kLdU + cc);
+    r[nt][1] = *reinterpret_cast<const float2 *>(src + (size_t)(m0 + g + 8) * kLdU + cc);
   }
 }
 
@@ -372,7 +379,7 @@ dfw_chunk_fwd_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
     rq = fetch16<T, false>(q + base, nv, tid);
     rk = fetch16<T, true>(k + base, nv, tid);
     fetch32<false>(rw, W + tile, kC, tid);
-    fetch_frag(ru, U + tile, m0, n0, g, tq);
+    fetch_frag(ru, U + ((size_t)b * nc + c) * kC * kLdU, m0, n0, g, tq);
   };
   fetch(0);
   for (int64_t c = 0; c < nc; ++c) {
@@ -480,7 +487,7 @@ dfw_chunk_bwd_seq_kernel(const T *__restrict__ go, const T *__restrict__ gs, con
     rg = fetch16<T, true>(go + base, nv, tid);
     fetch32<true>(rd, delta + base, nv, tid);
     fetch32<false>(rw, Wb + tile, kC, tid);
-    fetch_frag(ru, Ub + tile, m0, n0, g, tq);
+    fetch_frag(ru, Ub + ((size_t)b * nc + c) * kC * kLdU, m0, n0, g, tq);
   };
   fetch(nc - 1);
   for (int64_t c = nc - 1; c >= 0; --c) {
@@ -632,6 +639,7 @@ constexpr size_t kTileVBytes = (size_t)kC * kLdV * sizeof(float);   // tiles of 
 constexpr size_t kPrepTile = kTileBytes;
 
 inline size_t wu_floats(int64_t B, int64_t nc) { return (size_t)B * nc * kC * kDim; }
+inline size_t u_floats(int64_t B, int64_t nc) { return (size_t)B * nc * kC * kLdU; }   // U, Ub: padded rows
 
 }  // namespace
 
@@ -651,9 +659,11 @@ bool dfw_chunk_supported(int64_t D, int64_t M, int dtype) {
   return D == kDim && M == kDim && (dtype == T2FW_F16 || dtype == T2FW_BF16);
 }
 
-// fp32 [B][n_chunks][64][64] arrays: W and U (forward); Wb, Ub and the per-chunk S0, R_end, E (backward)
+// fp32 [B][n_chunks][64][64] arrays: W and U (forward); Wb, Ub and the per-chunk S0, R_end, E (backward);
+// U and Ub with rows of kLdU floats
 size_t dfw_chunk_scratch_bytes(int64_t B, int64_t T_, bool backward) {
-  return align_up((backward ? 5 : 2) * wu_floats(B, ceil_div64(T_, kC)) * sizeof(float), 256);
+  const int64_t nc = ceil_div64(T_, kC);
+  return align_up(((backward ? 4 : 1) * wu_floats(B, nc) + u_floats(B, nc)) * sizeof(float), 256);
 }
 
 template <typename T>
@@ -697,7 +707,7 @@ static int dfw_chunk_backward_typed(const void *go, const void *gs, const void *
                                        (int)(4 * kPrepTile)));
   dfw_chunk_prep_kernel<T, true><<<(unsigned)(B * nc), 128, 4 * kPrepTile, st>>>(
       (const T *)q, (const T *)k, (const T *)go, Wb, Ub, T_, nc);
-  float *Sc = Ub + wu_floats(B, nc), *Rc = Sc + wu_floats(B, nc), *Ec = Rc + wu_floats(B, nc);
+  float *Sc = Ub + u_floats(B, nc), *Rc = Sc + wu_floats(B, nc), *Ec = Rc + wu_floats(B, nc);
   T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_seq_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)(7 * kTileVBytes)));
   dfw_chunk_bwd_seq_kernel<T><<<(unsigned)B, kSeqThreads, 7 * kTileVBytes, st>>>(

@@ -13,7 +13,8 @@
 // so the state never leaves tensor memory between chunks; after each chunk it is read once to
 // refresh its TF32 copy in shared memory.  The two halves of every warp work on the two lane sets.
 // The raw inputs of the next chunk arrive by bulk asynchronous copies while the current chunk is
-// processed; every wait is bounded.
+// processed; Dl and the outputs leave through padded staging rows, copied out with coalesced
+// stores while the next products run.  Every wait is bounded.
 #include <type_traits>
 
 #include "async_copy.cuh"
@@ -44,20 +45,41 @@ namespace {
 
 constexpr int kTh = 256;                                  // 4 lane quarters x 2 column halves
 constexpr int kTileU = umma::tile_bytes(kDim, kC);        // 18432: [64][64] TF32, core-matrix layout
-constexpr int oQ = 0, oK = kTileU, oKT = 2 * kTileU, oW = 3 * kTileU, oSt = 4 * kTileU, oAs = 5 * kTileU,
-              oDT = 6 * kTileU;
-constexpr int oRawQ = 7 * kTileU;                         // 16-bit [64][64]
+// K and S are adjacent: together they are the 128-row operand of Q [K; S]^T
+constexpr int oQ = 0, oW = kTileU, oK = 2 * kTileU, oSt = 3 * kTileU, oAs = 4 * kTileU, oDT = 5 * kTileU,
+              oKT = 6 * kTileU;
+// K^T is written by transposing scalar stores; with its row groups 16 bytes further apart than
+// the dense layout a warp that covers 8 column pieces x 4 steps hits 32 different banks
+constexpr int kKTGroup = umma::tile_row_group_bytes(kC) + 16, kKTBytes = (kDim / 8) * kKTGroup;
+constexpr int kLdU = kDim + 4;                            // row stride of U tiles in global memory, floats
+constexpr int kRow16 = kDim * 2 + 16, kRow32 = kLdU * 4;  // padded staging rows
+constexpr int oRawQ = 6 * kTileU + kKTBytes;              // 16-bit [64][64], dense
 constexpr int oRawK = oRawQ + kC * kDim * 2;
-constexpr int oRawW = oRawK + kC * kDim * 2;              // fp32 [64][64]
-constexpr int oRawU = oRawW + kC * kDim * 4;
-constexpr int kSmemU = oRawU + kC * kDim * 4;
+constexpr int oRawW = oRawK + kC * kDim * 2;              // fp32 [64][64], dense
+constexpr int oRawU = oRawW + kC * kDim * 4;              // fp32 [64][kLdU]
+constexpr int oStgD = oRawU + kC * kRow32;                // Dl, fp32, row stride kRow32
+constexpr int oStgO = oStgD + kC * kRow32;                // outputs, 16-bit, row stride kRow16
+constexpr int kSmemU = oStgO + kC * kRow16;
 static_assert(kSmemU <= 227 * 1024 && oRawQ % 128 == 0, "shared memory layout");
 constexpr int cWS = 0, cSt = 64;                          // tensor-memory columns (both lane sets)
+constexpr int kCopyWarp = 7;                              // issues the bulk copies of the next chunk
 
 __device__ __forceinline__ void sync_all() {
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
+}
+__device__ __forceinline__ int kt_off(int m, int t) {
+  return (m & 7) * 16 + (m >> 3) * kKTGroup + (t & 3) * 4 + (t >> 2) * umma::kColGroupBytes;
+}
+__device__ __forceinline__ uint64_t kt_desc(uint32_t tile_addr, int ks) {
+  return umma::make_desc(tile_addr + ks * 2 * umma::kColGroupBytes, umma::kColGroupBytes, kKTGroup);
+}
+// round to TF32 (nearest, ties away from zero) with one integer addition: the tensor core ignores
+// the 13 low mantissa bits.  Infinities and NaNs pass unchanged.
+__device__ __forceinline__ float rt(float v) {
+  const uint32_t u = __float_as_uint(v);
+  return __uint_as_float((u & 0x7f800000u) == 0x7f800000u ? u : u + 0x1000u);
 }
 
 template <typename T>
@@ -67,7 +89,7 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
                           T *__restrict__ final_state, float *__restrict__ delta, int *__restrict__ status,
                           int64_t T_, int64_t nc) {
   extern __shared__ __align__(128) unsigned char sm[];
-  __shared__ __align__(8) uint64_t bar_mma, bar_raw;
+  __shared__ __align__(8) uint64_t bar_m1, bar_m2, bar_raw;
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int s_fail;
 
@@ -75,23 +97,36 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qd = warp & 3, half = warp >> 2, side = lane >> 4, fl = lane & 15;
   const int row = 16 * qd + fl, c0 = 32 * half;
-  float *tQ = reinterpret_cast<float *>(sm + oQ);
   unsigned char *tS = sm + oSt;
 
-  auto issue_raw = [&](int64_t c) {     // thread 0 only
+  // one thread: the four raw blocks of a chunk
+  auto issue_raw = [&](int64_t c) {
     const int64_t t0 = c * kC;
     const int nv = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
     const uint32_t vb = (uint32_t)nv * kDim * sizeof(T);
-    const size_t base = ((size_t)b * T_ + t0) * kDim, tile = ((size_t)b * nc + c) * kC * kDim;
-    acp::mbar_expect_tx(&bar_raw, 2 * vb + 2 * kC * kDim * 4);
+    const size_t base = ((size_t)b * T_ + t0) * kDim, tile = (size_t)b * nc + c;
+    acp::mbar_expect_tx(&bar_raw, 2 * vb + kC * kDim * 4 + kC * kRow32);
+    acp::bulk_g2s(sm + oRawW, W + tile * kC * kDim, kC * kDim * 4, &bar_raw);
+    acp::bulk_g2s(sm + oRawU, U + tile * kC * kLdU, kC * kRow32, &bar_raw);
     acp::bulk_g2s(sm + oRawQ, q + base, vb, &bar_raw);
     acp::bulk_g2s(sm + oRawK, k + base, vb, &bar_raw);
-    acp::bulk_g2s(sm + oRawW, W + tile, kC * kDim * 4, &bar_raw);
-    acp::bulk_g2s(sm + oRawU, U + tile, kC * kDim * 4, &bar_raw);
+  };
+  // staged outputs of one chunk -> global, 16 bytes per thread and step, consecutive threads
+  // consecutive addresses
+  auto copy_out_o = [&](int64_t c) {
+    const int64_t t0 = c * kC;
+    const int nv = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
+    T *op = out + ((size_t)b * T_ + t0) * kDim;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int p = tid + kTh * j, r = p >> 3, c8 = (p & 7) * 8;
+      if (r < nv) *reinterpret_cast<uint4 *>(op + r * kDim + c8) = *reinterpret_cast<const uint4 *>(sm + oStgO + r * kRow16 + c8 * 2);
+    }
   };
 
   if (tid == 0) {
-    umma::mbar_init(&bar_mma, 1);
+    umma::mbar_init(&bar_m1, 2);
+    umma::mbar_init(&bar_m2, 2);
     umma::mbar_init(&bar_raw, 1);
     umma::mbar_fence_init();
     s_fail = 0;
@@ -100,7 +135,7 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
   sync_all();
   const uint32_t tb = tmem_slot;
   const uint32_t tl = umma::tmem_addr(tb, 32 * qd, 0);
-  if (tid == 0) issue_raw(0);
+  if (warp == kCopyWarp && lane == 0) issue_raw(0);
 
   // initial state: row `row`, columns c0 .. c0+31 -> tensor memory (lane set A) and the TF32 tile
   {
@@ -117,19 +152,16 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
       }
 #pragma unroll
       for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<float4 *>(tS + umma::tile_off(row, c0 + j, kDim)) =
-            make_float4(round_tf32(v[j]), round_tf32(v[j + 1]), round_tf32(v[j + 2]), round_tf32(v[j + 3]));
+        *reinterpret_cast<float4 *>(tS + umma::tile_off(row, c0 + j, kDim)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
     }
     umma::tmem_st16(tl + cSt + c0, v);            // lanes B receive zeros (overwritten by Q S^T)
     umma::tmem_st16(tl + cSt + c0 + 16, v + 16);
     umma::tmem_st_wait();
   }
 
-  uint32_t p_mma = 0, p_raw = 0;
-  auto wait_mma = [&]() {
-    if (!s_fail && !umma::mbar_wait(&bar_mma, p_mma)) s_fail = 1;
-    p_mma ^= 1u;
-    umma::fence_after_sync();
+  uint32_t par = 0;     // all three barriers complete one phase per chunk
+  auto wait_bar = [&](uint64_t *bar) {
+    if (!s_fail && !umma::mbar_wait(bar, par)) s_fail = 1;
   };
 
 #ifdef T2FW_DFW_PROFILE
@@ -140,64 +172,63 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
     const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
     const size_t base = ((size_t)b * T_ + t0) * kDim;
     PROF(0);
-    if (!s_fail && !acp::mbar_wait(&bar_raw, p_raw)) s_fail = 1;
-    p_raw ^= 1u;
+    if (!umma::mbar_wait(&bar_raw, par)) s_fail = 1;    // also after a failure: no copy stays in flight
     __syncthreads();
     if (s_fail) break;
     PROF(1);
 
-    // ---- raw blocks -> TF32 tiles: pieces of 4 consecutive columns, 1024 per block ----------------
+    // ---- raw blocks -> TF32 tiles, in pieces of 4 consecutive columns (1024 per block) -------------
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int p = tid + kTh * j, r = p >> 4, c4 = (p & 15) * 4;
-      const bool in = r < nvalid;
-      const uint2 uq = in ? *reinterpret_cast<const uint2 *>(sm + oRawQ + (r * kDim + c4) * 2) : make_uint2(0u, 0u);
-      const uint2 uk = in ? *reinterpret_cast<const uint2 *>(sm + oRawK + (r * kDim + c4) * 2) : make_uint2(0u, 0u);
-      const float2 q0 = Pair<T>::ld(reinterpret_cast<const T *>(&uq.x)), q1 = Pair<T>::ld(reinterpret_cast<const T *>(&uq.y));
-      const float2 k0 = Pair<T>::ld(reinterpret_cast<const T *>(&uk.x)), k1 = Pair<T>::ld(reinterpret_cast<const T *>(&uk.y));
-      *reinterpret_cast<float4 *>(sm + oQ + umma::tile_off(r, c4, kDim)) = make_float4(q0.x, q0.y, q1.x, q1.y);
-      *reinterpret_cast<float4 *>(sm + oK + umma::tile_off(r, c4, kDim)) = make_float4(k0.x, k0.y, k1.x, k1.y);
-      // K^T[m][t] = K[t][m]
-      *reinterpret_cast<float *>(sm + oKT + umma::tile_off(c4, r, kC)) = k0.x;
-      *reinterpret_cast<float *>(sm + oKT + umma::tile_off(c4 + 1, r, kC)) = k0.y;
-      *reinterpret_cast<float *>(sm + oKT + umma::tile_off(c4 + 2, r, kC)) = k1.x;
-      *reinterpret_cast<float *>(sm + oKT + umma::tile_off(c4 + 3, r, kC)) = k1.y;
-      const float4 w4 = *reinterpret_cast<const float4 *>(sm + oRawW + (r * kDim + c4) * 4);
-      *reinterpret_cast<float4 *>(sm + oW + umma::tile_off(r, c4, kDim)) =
-          make_float4(round_tf32(w4.x), round_tf32(w4.y), round_tf32(w4.z), round_tf32(w4.w));
+      {  // Q and W: 16 consecutive lanes cover one row
+        const int p = tid + kTh * j, r = p >> 4, c4 = (p & 15) * 4;
+        const uint2 uq = (r < nvalid) ? *reinterpret_cast<const uint2 *>(sm + oRawQ + (r * kDim + c4) * 2) : make_uint2(0u, 0u);
+        const float2 q0 = Pair<T>::ld(reinterpret_cast<const T *>(&uq.x)), q1 = Pair<T>::ld(reinterpret_cast<const T *>(&uq.y));
+        *reinterpret_cast<float4 *>(sm + oQ + umma::tile_off(r, c4, kDim)) = make_float4(q0.x, q0.y, q1.x, q1.y);
+        const float4 w4 = *reinterpret_cast<const float4 *>(sm + oRawW + (r * kDim + c4) * 4);
+        *reinterpret_cast<float4 *>(sm + oW + umma::tile_off(r, c4, kDim)) = make_float4(rt(w4.x), rt(w4.y), rt(w4.z), rt(w4.w));
+      }
+      {  // K and K^T: a warp covers 8 column pieces x 4 steps (see kKTGroup)
+        const int combo = warp * 4 + j, r = 4 * (combo >> 1) + (lane >> 3), c4 = 4 * (8 * (combo & 1) + (lane & 7));
+        const uint2 uk = (r < nvalid) ? *reinterpret_cast<const uint2 *>(sm + oRawK + (r * kDim + c4) * 2) : make_uint2(0u, 0u);
+        const float2 k0 = Pair<T>::ld(reinterpret_cast<const T *>(&uk.x)), k1 = Pair<T>::ld(reinterpret_cast<const T *>(&uk.y));
+        *reinterpret_cast<float4 *>(sm + oK + umma::tile_off(r, c4, kDim)) = make_float4(k0.x, k0.y, k1.x, k1.y);
+        *reinterpret_cast<float *>(sm + oKT + kt_off(c4, r)) = k0.x;
+        *reinterpret_cast<float *>(sm + oKT + kt_off(c4 + 1, r)) = k0.y;
+        *reinterpret_cast<float *>(sm + oKT + kt_off(c4 + 2, r)) = k1.x;
+        *reinterpret_cast<float *>(sm + oKT + kt_off(c4 + 3, r)) = k1.y;
+      }
     }
     // this thread's part of U (lane set A threads): row `row`, columns c0 .. c0+31
     float uv[32];
     if (side == 0) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
-        const float4 u4 = *reinterpret_cast<const float4 *>(sm + oRawU + (row * kDim + c0 + j) * 4);
+        const float4 u4 = *reinterpret_cast<const float4 *>(sm + oRawU + row * kRow32 + (c0 + j) * 4);
         uv[j] = u4.x; uv[j + 1] = u4.y; uv[j + 2] = u4.z; uv[j + 3] = u4.w;
       }
     }
+    if (c > 0) copy_out_o(c - 1);     // staged by the previous chunk, ordered by the barrier above
     PROF(2);
     umma::fence_async_smem();
     sync_all();                       // tiles complete (the S tile since the end of the last chunk)
     PROF(3);
 
-    if (tid == 0) {
-      if (c + 1 < nc) issue_raw(c + 1);
-      const uint32_t idesc = umma::make_idesc_tf32(kDim, kDim, false, false);
-      const uint32_t aQ = umma::smem_u32(sm + oQ), aK = umma::smem_u32(sm + oK), aW = umma::smem_u32(sm + oW),
-                     aS = umma::smem_u32(sm + oSt);
+    // ---- first round: W S^T (lane set A, columns 0-63) and Q [K; S]^T (lane set B, all columns),
+    //      one issuing thread each ---------------------------------------------------------------------
+    if (lane == 0 && warp < 2) {
+      const uint32_t idesc = umma::make_idesc_tf32(kDim, warp == 0 ? kDim : 2 * kDim, false, false);
+      const uint32_t aA = umma::smem_u32(sm + (warp == 0 ? oW : oQ)), aB = umma::smem_u32(sm + (warp == 0 ? oSt : oK));
+      const uint32_t d = umma::tmem_addr(tb, warp == 0 ? 0 : 16, cWS);
 #pragma unroll
-      for (int ks = 0; ks < kC / 8; ++ks) {
-        umma::mma_tf32(umma::tmem_addr(tb, 0, cWS), umma::desc_kmajor(aW, kDim, 0, ks),
-                       umma::desc_kmajor(aS, kDim, 0, ks), idesc, ks > 0);     // W S^T
-        umma::mma_tf32(umma::tmem_addr(tb, 16, cSt), umma::desc_kmajor(aQ, kDim, 0, ks),
-                       umma::desc_kmajor(aS, kDim, 0, ks), idesc, ks > 0);     // Q S^T
-        umma::mma_tf32(umma::tmem_addr(tb, 16, cWS), umma::desc_kmajor(aQ, kDim, 0, ks),
-                       umma::desc_kmajor(aK, kDim, 0, ks), idesc, ks > 0);     // Q K^T
-      }
-      umma::mma_commit(&bar_mma);
+      for (int ks = 0; ks < kC / 8; ++ks)
+        umma::mma_tf32(d, umma::desc_kmajor(aA, kDim, 0, ks), umma::desc_kmajor(aB, kDim, 0, ks), idesc, ks > 0);
+      umma::mma_commit(&bar_m1);
     }
+    if (warp == kCopyWarp && lane == 0 && c + 1 < nc) issue_raw(c + 1);
     PROF(4);
-    wait_mma();
+    wait_bar(&bar_m1);
+    umma::fence_after_sync();
     PROF(5);
     {
       // lane set A: Dl = U - W S^T (row t = `row`, columns d);  lane set B: scores (row t, columns i)
@@ -208,17 +239,15 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
       if (side == 0) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = uv[j] - v[j];
-        if (row < nvalid) {
-          float *dp = delta + base + (size_t)row * kDim + c0;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(dp + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        }
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4 *>(sm + oStgD + row * kRow32 + (c0 + j) * 4) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
 #pragma unroll
         for (int j = 0; j < 32; ++j)      // Dl^T[d][t]
-          *reinterpret_cast<float *>(sm + oDT + umma::tile_off(c0 + j, row, kC)) = round_tf32(v[j]);
+          *reinterpret_cast<float *>(sm + oDT + umma::tile_off(c0 + j, row, kC)) = rt(v[j]);
       } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = (c0 + j < row) ? round_tf32(v[j]) : 0.f;
+        for (int j = 0; j < 32; ++j) v[j] = (c0 + j < row) ? rt(v[j]) : 0.f;
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
           *reinterpret_cast<float4 *>(sm + oAs + umma::tile_off(row, c0 + j, kC)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -228,48 +257,58 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
     umma::fence_async_smem();
     sync_all();
     PROF(7);
-    if (tid == 0) {
+    // ---- second round: O += A Dl, S += Dl^T K ---------------------------------------------------------
+    if (lane == 0 && warp < 2) {
       const uint32_t idesc = umma::make_idesc_tf32(kDim, kDim, false, false);
-      const uint32_t aA = umma::smem_u32(sm + oAs), aD = umma::smem_u32(sm + oDT), aKT = umma::smem_u32(sm + oKT);
+      const uint32_t aA = umma::smem_u32(sm + (warp == 0 ? oAs : oDT)), aD = umma::smem_u32(sm + oDT),
+                     aKT = umma::smem_u32(sm + oKT);
+      const uint32_t d = umma::tmem_addr(tb, warp == 0 ? 16 : 0, cSt);
 #pragma unroll
-      for (int ks = 0; ks < kC / 8; ++ks) {
-        umma::mma_tf32(umma::tmem_addr(tb, 16, cSt), umma::desc_kmajor(aA, kC, 0, ks),
-                       umma::desc_kmajor(aD, kC, 0, ks), idesc, true);        // O += A Dl
-        umma::mma_tf32(umma::tmem_addr(tb, 0, cSt), umma::desc_kmajor(aD, kC, 0, ks),
-                       umma::desc_kmajor(aKT, kC, 0, ks), idesc, true);       // S += Dl^T K
-      }
-      umma::mma_commit(&bar_mma);
+      for (int ks = 0; ks < kC / 8; ++ks)
+        umma::mma_tf32(d, umma::desc_kmajor(aA, kC, 0, ks), warp == 0 ? umma::desc_kmajor(aD, kC, 0, ks) : kt_desc(aKT, ks),
+                       idesc, true);
+      umma::mma_commit(&bar_m2);
+    }
+    // Dl of this chunk -> global while the products run
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int p = tid + kTh * j, r = p >> 4, c4 = (p & 15) * 4;
+      if (r < nvalid)
+        *reinterpret_cast<float4 *>(delta + base + (size_t)r * kDim + c4) = *reinterpret_cast<const float4 *>(sm + oStgD + r * kRow32 + c4 * 4);
     }
     PROF(8);
-    wait_mma();
+    wait_bar(&bar_m2);
+    umma::fence_after_sync();
     PROF(9);
     {
-      // lane set B: O (row t, columns d) -> global;  lane set A: S (row d, columns m) -> TF32 tile
+      // lane set B: O (row t, columns d) -> staging;  lane set A: S (row d, columns m) -> TF32 tile
       float v[32];
       umma::tmem_ld16(tl + cSt + c0, *reinterpret_cast<float(*)[16]>(v));
       umma::tmem_ld16(tl + cSt + c0 + 16, *reinterpret_cast<float(*)[16]>(v + 16));
       umma::tmem_ld_wait();
       if (side) {
-        if (row < nvalid) {
-          T *op = out + base + (size_t)row * kDim + c0;
+        uint32_t pk[16];
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) Pair<T>::st(op + j, v[j], v[j + 1]);
-        }
+        for (int j = 0; j < 16; ++j) Pair<T>::st(reinterpret_cast<T *>(&pk[j]), v[2 * j], v[2 * j + 1]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4 *>(sm + oStgO + row * kRow16 + c0 * 2 + 16 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
       } else if (c + 1 < nc) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4 *>(tS + umma::tile_off(row, c0 + j, kDim)) =
-              make_float4(round_tf32(v[j]), round_tf32(v[j + 1]), round_tf32(v[j + 2]), round_tf32(v[j + 3]));
+          *reinterpret_cast<float4 *>(tS + umma::tile_off(row, c0 + j, kDim)) = make_float4(rt(v[j]), rt(v[j + 1]), rt(v[j + 2]), rt(v[j + 3]));
       } else {
         T *fp = final_state + (size_t)b * kDim * kDim + row * kDim + c0;
 #pragma unroll
         for (int j = 0; j < 32; j += 2) Pair<T>::st(fp + j, v[j], v[j + 1]);
       }
     }
+    par ^= 1u;
     umma::fence_before_sync();   // accumulator reads are ordered before the next chunk's MMAs
     PROF(10);
   }
-  (void)tQ;
+  __syncthreads();
+  if (!s_fail && nc > 0) copy_out_o(nc - 1);
   if (s_fail && tid == 0) atomicExch(status, 1);
   sync_all();
   if (warp == 0) umma::tmem_dealloc(tb, 128);
