@@ -649,8 +649,8 @@ int dfw_chunk_forward_umma(const void *q, const void *k, const void *state, cons
                            cudaStream_t st);
 static bool dfw_umma_enabled() {
   static const bool on = [] {
-    const char *e = std::getenv("T2FW_DFW_UMMA");
-    return e && e[0] == '1';
+    const char *e = std::getenv("T2FW_DISABLE_DFW_UMMA");
+    return !(e && e[0] == '1');
   }();
   return on;
 }
