@@ -647,10 +647,22 @@ inline size_t u_floats(int64_t B, int64_t nc) { return (size_t)B * nc * kC * kLd
 int dfw_chunk_forward_umma(const void *q, const void *k, const void *state, const float *W, const float *U,
                            void *out, void *final_state, void *delta, int64_t B, int64_t T_, int dtype,
                            cudaStream_t st);
+int dfw_chunk_bwd_seq_umma(const void *go, const void *gs, const void *q, const void *k, const void *delta,
+                           const void *final_state, const float *Wb, const float *Ub, float *ScT, float *RcT,
+                           float *Ec, void *dv, void *ds, int64_t B, int64_t T_, int dtype, cudaStream_t st);
 static bool dfw_umma_enabled() {
   static const bool on = [] {
     const char *e = std::getenv("T2FW_DISABLE_DFW_UMMA");
     return !(e && e[0] == '1');
+  }();
+  return on;
+}
+
+// experiment switch: tcgen05 forward with the mma.sync sequential backward
+static bool dfw_bwd_mma_sync_forced() {
+  static const bool on = [] {
+    const char *e = std::getenv("T2FW_DFW_BWD_MMA_SYNC");
+    return e && e[0] == '1';
   }();
   return on;
 }
@@ -708,11 +720,18 @@ static int dfw_chunk_backward_typed(const void *go, const void *gs, const void *
   dfw_chunk_prep_kernel<T, true><<<(unsigned)(B * nc), 128, 4 * kPrepTile, st>>>(
       (const T *)q, (const T *)k, (const T *)go, Wb, Ub, T_, nc);
   float *Sc = Ub + u_floats(B, nc), *Rc = Sc + wu_floats(B, nc), *Ec = Rc + wu_floats(B, nc);
-  T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_seq_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)(7 * kTileVBytes)));
-  dfw_chunk_bwd_seq_kernel<T><<<(unsigned)B, kSeqThreads, 7 * kTileVBytes, st>>>(
-      (const T *)go, (const T *)gs, (const T *)q, (const T *)k, (const float *)delta, (const T *)final_state, Wb,
-      Ub, Sc, Rc, Ec, (T *)dv, (T *)ds, T_, nc);
+  int seq_rc = T2FW_ERR_UNSUPPORTED;
+  if (dfw_umma_enabled() && !dfw_bwd_mma_sync_forced())
+    seq_rc = dfw_chunk_bwd_seq_umma(go, gs, q, k, delta, final_state, Wb, Ub, Sc, Rc, Ec, dv, ds, B, T_,
+                                    std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16, st);
+  if (seq_rc != T2FW_OK && seq_rc != T2FW_ERR_UNSUPPORTED) return seq_rc;
+  if (seq_rc == T2FW_ERR_UNSUPPORTED) {
+    T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_seq_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(7 * kTileVBytes)));
+    dfw_chunk_bwd_seq_kernel<T><<<(unsigned)B, kSeqThreads, 7 * kTileVBytes, st>>>(
+        (const T *)go, (const T *)gs, (const T *)q, (const T *)k, (const float *)delta, (const T *)final_state,
+        Wb, Ub, Sc, Rc, Ec, (T *)dv, (T *)ds, T_, nc);
+  }
   T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_par_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)(10 * kTileVBytes)));
   dfw_chunk_bwd_par_kernel<T><<<(unsigned)(B * nc), kSeqThreads, 10 * kTileVBytes, st>>>(

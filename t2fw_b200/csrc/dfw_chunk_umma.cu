@@ -28,7 +28,7 @@ using namespace chunk;
 int lfw_chunk_status_ptr(int **out);   // lfw_chunk_local_umma.cu
 
 #ifdef T2FW_DFW_PROFILE
-__device__ long long g_dfw_prof[16];
+__device__ long long g_dfw_prof[32];
 #define PROF(i)                                                    \
   do {                                                             \
     if (threadIdx.x == 0 && blockIdx.x == 0) {                     \
@@ -37,8 +37,17 @@ __device__ long long g_dfw_prof[16];
       tprev = now_;                                                \
     }                                                              \
   } while (0)
+#define PROFB(i)                                                   \
+  do {                                                             \
+    if (threadIdx.x == 0 && blockIdx.x == 0) {                     \
+      const long long now_ = clock64();                            \
+      g_dfw_prof[16 + i] += now_ - tprev;                          \
+      tprev = now_;                                                \
+    }                                                              \
+  } while (0)
 #else
 #define PROF(i)
+#define PROFB(i)
 #endif
 
 namespace {
@@ -314,6 +323,260 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
   if (warp == 0) umma::tmem_dealloc(tb, 128);
 }
 
+// ---- backward, sequential part ----------------------------------------------------------------------
+// Chunks in reverse order; per chunk (S: state walked back, R: state gradient)
+//   S0 = S_end - Dl^T K ,  E = Ub + Wb R_end^T (= d_value) ,  R_start = R_end + dO^T Q - E^T K
+// and S0^T, R_end^T, E of every chunk go to scratch for the chunk-parallel kernel.  Tensor memory:
+//   columns  0-63 :  lane set A: Wb R_end^T        lane set B: S (persistent)
+//   columns 64-127:  lane set A: R (persistent)    lane set B: unused
+// Tiles with the step index as contraction ([.][t]: -Dl^T, K^T, dO^T, Q^T, -E^T) use the shifted
+// row-group stride kKTGroup; Wb and the TF32 copy of R the dense one.
+constexpr int oBD = 0, oBK = kKTBytes, oBG = 2 * kKTBytes, oBQ = 3 * kKTBytes, oBE = 4 * kKTBytes,
+              oBW = 5 * kKTBytes, oBR = oBW + kTileU;
+constexpr int oBRawQ = oBR + kTileU;                      // 16-bit [64][64], dense
+constexpr int oBRawK = oBRawQ + kC * kDim * 2;
+constexpr int oBRawG = oBRawK + kC * kDim * 2;
+constexpr int oBRawD = oBRawG + kC * kDim * 2;            // fp32 [64][64], dense
+constexpr int oBRawW = oBRawD + kC * kDim * 4;
+constexpr int oBRawU = oBRawW + kC * kDim * 4;            // fp32 [64][kLdU]
+constexpr int oBStgE = oBRawU + kC * kRow32;              // E, fp32, row stride kRow32
+constexpr int kSmemB = oBStgE + kC * kRow32;
+static_assert(kSmemB <= 227 * 1024 && oBRawQ % 128 == 0, "shared memory layout");
+constexpr int cE = 0, cR = 64;                            // tensor-memory columns
+
+template <typename T>
+__global__ void __launch_bounds__(kTh, 1)
+dfw_chunk_bwd_seq_umma_kernel(const T *__restrict__ go, const T *__restrict__ gs, const T *__restrict__ q,
+                              const T *__restrict__ k, const float *__restrict__ delta,
+                              const T *__restrict__ final_state, const float *__restrict__ Wb,
+                              const float *__restrict__ Ub, float *__restrict__ ScT, float *__restrict__ RcT,
+                              float *__restrict__ Ec, T *__restrict__ dv, T *__restrict__ ds,
+                              int *__restrict__ status, int64_t T_, int64_t nc) {
+  extern __shared__ __align__(128) unsigned char sm[];
+  __shared__ __align__(8) uint64_t bar_m1, bar_m2, bar_raw;
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int s_fail;
+
+  const int64_t b = blockIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qd = warp & 3, half = warp >> 2, side = lane >> 4, fl = lane & 15;
+  const int row = 16 * qd + fl, c0 = 32 * half;
+
+  auto issue_raw = [&](int64_t c) {     // one thread
+    const int64_t t0 = c * kC;
+    const int nv = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
+    const uint32_t vb = (uint32_t)nv * kDim * sizeof(T), vd = (uint32_t)nv * kDim * 4u;
+    const size_t base = ((size_t)b * T_ + t0) * kDim, tile = (size_t)b * nc + c;
+    acp::mbar_expect_tx(&bar_raw, 3 * vb + vd + kC * kDim * 4 + kC * kRow32);
+    acp::bulk_g2s(sm + oBRawW, Wb + tile * kC * kDim, kC * kDim * 4, &bar_raw);
+    acp::bulk_g2s(sm + oBRawU, Ub + tile * kC * kLdU, kC * kRow32, &bar_raw);
+    acp::bulk_g2s(sm + oBRawQ, q + base, vb, &bar_raw);
+    acp::bulk_g2s(sm + oBRawK, k + base, vb, &bar_raw);
+    acp::bulk_g2s(sm + oBRawG, go + base, vb, &bar_raw);
+    acp::bulk_g2s(sm + oBRawD, delta + base, vd, &bar_raw);
+  };
+  // row `row`, columns c0 .. c0+31 of a [d][m] matrix, transposed into a [m][d] scratch tile
+  auto store_t = [&](float *dst, const float (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) dst[(size_t)(c0 + j) * kDim + row] = v[j];
+  };
+  auto store_r_tile = [&](const float (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+      *reinterpret_cast<float4 *>(sm + oBR + umma::tile_off(row, c0 + j, kDim)) =
+          make_float4(rt(v[j]), rt(v[j + 1]), rt(v[j + 2]), rt(v[j + 3]));
+  };
+
+  if (tid == 0) {
+    umma::mbar_init(&bar_m1, 3);
+    umma::mbar_init(&bar_m2, 1);
+    umma::mbar_init(&bar_raw, 1);
+    umma::mbar_fence_init();
+    s_fail = 0;
+  }
+  if (warp == 0) umma::tmem_alloc(&tmem_slot, 128);
+  sync_all();
+  const uint32_t tb = tmem_slot;
+  const uint32_t tl = umma::tmem_addr(tb, 32 * qd, 0);
+  if (warp == kCopyWarp && lane == 0) issue_raw(nc - 1);
+
+  // lane set A threads: the incoming state gradient (= R_end of the last chunk); lane set B threads:
+  // the final state.  One store per column range serves both lane sets.
+  {
+    const T *src = (side == 0 ? gs : final_state) + (size_t)b * kDim * kDim + row * kDim + c0;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float2 p = Pair<T>::ld(src + 2 * j);
+      v[2 * j] = p.x;
+      v[2 * j + 1] = p.y;
+    }
+    if (side == 0) {
+      store_r_tile(v);
+      store_t(RcT + ((size_t)b * nc + nc - 1) * kC * kDim, v);
+    }
+    // R into columns 64.., S into columns 0..: each lane set keeps only its own matrix, the other
+    // half of either store lands in accumulator space that the first products overwrite or never read
+    umma::tmem_st16(tl + cR + c0, v);
+    umma::tmem_st16(tl + cR + c0 + 16, v + 16);
+    umma::tmem_st16(tl + cE + c0, v);
+    umma::tmem_st16(tl + cE + c0 + 16, v + 16);
+    umma::tmem_st_wait();
+  }
+
+  uint32_t par = 0;
+  auto wait_bar = [&](uint64_t *bar) {
+    if (!s_fail && !umma::mbar_wait(bar, par)) s_fail = 1;
+  };
+#ifdef T2FW_DFW_PROFILE
+  long long tprev = clock64();
+#endif
+  for (int64_t c = nc - 1; c >= 0; --c) {
+    const int64_t t0 = c * kC;
+    const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
+    const size_t base = ((size_t)b * T_ + t0) * kDim, tile = ((size_t)b * nc + c) * kC * kDim;
+    PROFB(0);
+    if (!umma::mbar_wait(&bar_raw, par)) s_fail = 1;    // also after a failure: no copy stays in flight
+    __syncthreads();
+    if (s_fail) break;
+    PROFB(1);
+
+    // ---- raw blocks -> TF32 tiles.  A warp covers 8 column pieces x 4 steps per instruction. ---------
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int combo = warp * 4 + j, r = 4 * (combo >> 1) + (lane >> 3), c4 = 4 * (8 * (combo & 1) + (lane & 7));
+      const bool in = r < nvalid;
+      const uint2 z2 = make_uint2(0u, 0u);
+      const uint2 uq = in ? *reinterpret_cast<const uint2 *>(sm + oBRawQ + (r * kDim + c4) * 2) : z2;
+      const uint2 uk = in ? *reinterpret_cast<const uint2 *>(sm + oBRawK + (r * kDim + c4) * 2) : z2;
+      const uint2 ug = in ? *reinterpret_cast<const uint2 *>(sm + oBRawG + (r * kDim + c4) * 2) : z2;
+      const float4 d4 = in ? *reinterpret_cast<const float4 *>(sm + oBRawD + (r * kDim + c4) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 w4 = *reinterpret_cast<const float4 *>(sm + oBRawW + (r * kDim + c4) * 4);
+      const float2 q0 = Pair<T>::ld(reinterpret_cast<const T *>(&uq.x)), q1 = Pair<T>::ld(reinterpret_cast<const T *>(&uq.y));
+      const float2 k0 = Pair<T>::ld(reinterpret_cast<const T *>(&uk.x)), k1 = Pair<T>::ld(reinterpret_cast<const T *>(&uk.y));
+      const float2 g0 = Pair<T>::ld(reinterpret_cast<const T *>(&ug.x)), g1 = Pair<T>::ld(reinterpret_cast<const T *>(&ug.y));
+      const int o0 = kt_off(c4, r), o1 = kt_off(c4 + 1, r), o2 = kt_off(c4 + 2, r), o3 = kt_off(c4 + 3, r);
+      *reinterpret_cast<float *>(sm + oBQ + o0) = q0.x; *reinterpret_cast<float *>(sm + oBQ + o1) = q0.y;
+      *reinterpret_cast<float *>(sm + oBQ + o2) = q1.x; *reinterpret_cast<float *>(sm + oBQ + o3) = q1.y;
+      *reinterpret_cast<float *>(sm + oBK + o0) = k0.x; *reinterpret_cast<float *>(sm + oBK + o1) = k0.y;
+      *reinterpret_cast<float *>(sm + oBK + o2) = k1.x; *reinterpret_cast<float *>(sm + oBK + o3) = k1.y;
+      *reinterpret_cast<float *>(sm + oBG + o0) = g0.x; *reinterpret_cast<float *>(sm + oBG + o1) = g0.y;
+      *reinterpret_cast<float *>(sm + oBG + o2) = g1.x; *reinterpret_cast<float *>(sm + oBG + o3) = g1.y;
+      *reinterpret_cast<float *>(sm + oBD + o0) = -rt(d4.x); *reinterpret_cast<float *>(sm + oBD + o1) = -rt(d4.y);
+      *reinterpret_cast<float *>(sm + oBD + o2) = -rt(d4.z); *reinterpret_cast<float *>(sm + oBD + o3) = -rt(d4.w);
+      *reinterpret_cast<float4 *>(sm + oBW + umma::tile_off(r, c4, kDim)) = make_float4(rt(w4.x), rt(w4.y), rt(w4.z), rt(w4.w));
+    }
+    // this thread's part of Ub (lane set A threads): row `row`, columns c0 .. c0+31
+    float uv[32];
+    if (side == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 u4 = *reinterpret_cast<const float4 *>(sm + oBRawU + row * kRow32 + (c0 + j) * 4);
+        uv[j] = u4.x; uv[j + 1] = u4.y; uv[j + 2] = u4.z; uv[j + 3] = u4.w;
+      }
+    }
+    PROFB(2);
+    umma::fence_async_smem();
+    sync_all();                       // tiles complete (the R tile since the end of the chunk before)
+    PROFB(3);
+
+    // ---- first round, one issuing thread per product -------------------------------------------------
+    if (lane == 0 && warp < 3) {
+      const uint32_t idesc = umma::make_idesc_tf32(kDim, kDim, false, false);
+      if (warp == 0) {          // Wb R_end^T  (rows t, columns d)
+        const uint32_t aA = umma::smem_u32(sm + oBW), aB = umma::smem_u32(sm + oBR);
+#pragma unroll
+        for (int ks = 0; ks < kC / 8; ++ks)
+          umma::mma_tf32(umma::tmem_addr(tb, 0, cE), umma::desc_kmajor(aA, kDim, 0, ks),
+                         umma::desc_kmajor(aB, kDim, 0, ks), idesc, ks > 0);
+      } else {                  // S -= Dl^T K   and   R += dO^T Q
+        const uint32_t aA = umma::smem_u32(sm + (warp == 1 ? oBD : oBG)), aB = umma::smem_u32(sm + (warp == 1 ? oBK : oBQ));
+        const uint32_t d = warp == 1 ? umma::tmem_addr(tb, 16, cE) : umma::tmem_addr(tb, 0, cR);
+#pragma unroll
+        for (int ks = 0; ks < kC / 8; ++ks) umma::mma_tf32(d, kt_desc(aA, ks), kt_desc(aB, ks), idesc, true);
+      }
+      umma::mma_commit(&bar_m1);
+    }
+    if (warp == kCopyWarp && lane == 0 && c > 0) issue_raw(c - 1);
+    PROFB(4);
+    wait_bar(&bar_m1);
+    umma::fence_after_sync();
+    PROFB(5);
+    {
+      // lane set A: E = Ub + Wb R_end^T (row t = `row`, columns d);  lane set B: S0 (row d, columns m)
+      float v[32];
+      umma::tmem_ld16(tl + cE + c0, *reinterpret_cast<float(*)[16]>(v));
+      umma::tmem_ld16(tl + cE + c0 + 16, *reinterpret_cast<float(*)[16]>(v + 16));
+      umma::tmem_ld_wait();
+      if (side == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += uv[j];
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4 *>(sm + oBStgE + row * kRow32 + (c0 + j) * 4) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j)      // -E^T[d][t]
+          *reinterpret_cast<float *>(sm + oBE + kt_off(c0 + j, row)) = -rt(v[j]);
+      } else {
+        store_t(ScT + tile, v);
+      }
+    }
+    PROFB(6);
+    umma::fence_async_smem();
+    sync_all();
+    PROFB(7);
+    // ---- second round: R -= E^T K ----------------------------------------------------------------------
+    if (tid == 0) {
+      const uint32_t idesc = umma::make_idesc_tf32(kDim, kDim, false, false);
+      const uint32_t aA = umma::smem_u32(sm + oBE), aB = umma::smem_u32(sm + oBK);
+#pragma unroll
+      for (int ks = 0; ks < kC / 8; ++ks)
+        umma::mma_tf32(umma::tmem_addr(tb, 0, cR), kt_desc(aA, ks), kt_desc(aB, ks), idesc, true);
+      umma::mma_commit(&bar_m2);
+    }
+    // E of this chunk -> scratch (all rows) and d_value (valid rows) while the product runs
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int p = tid + kTh * j, r = p >> 4, c4 = (p & 15) * 4;
+      const float4 e4 = *reinterpret_cast<const float4 *>(sm + oBStgE + r * kRow32 + c4 * 4);
+      *reinterpret_cast<float4 *>(Ec + tile + r * kDim + c4) = e4;
+      if (r < nvalid) {
+        uint2 pk;
+        Pair<T>::st(reinterpret_cast<T *>(&pk.x), e4.x, e4.y);
+        Pair<T>::st(reinterpret_cast<T *>(&pk.y), e4.z, e4.w);
+        *reinterpret_cast<uint2 *>(dv + base + (size_t)r * kDim + c4) = pk;
+      }
+    }
+    PROFB(8);
+    wait_bar(&bar_m2);
+    umma::fence_after_sync();
+    PROFB(9);
+    {
+      // R_start (row d, columns m) = R_end of the chunk before, or the state gradient at the start
+      float v[32];
+      umma::tmem_ld16(tl + cR + c0, *reinterpret_cast<float(*)[16]>(v));
+      umma::tmem_ld16(tl + cR + c0 + 16, *reinterpret_cast<float(*)[16]>(v + 16));
+      umma::tmem_ld_wait();
+      if (side == 0) {
+        if (c > 0) {
+          store_r_tile(v);
+          store_t(RcT + tile - (size_t)kC * kDim, v);
+        } else {
+          T *dp = ds + (size_t)b * kDim * kDim + row * kDim + c0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) Pair<T>::st(dp + j, v[j], v[j + 1]);
+        }
+      }
+    }
+    par ^= 1u;
+    umma::fence_before_sync();   // accumulator reads are ordered before the next chunk's MMAs
+    PROFB(10);
+  }
+  if (s_fail && tid == 0) atomicExch(status, 1);
+  sync_all();
+  if (warp == 0) umma::tmem_dealloc(tb, 128);
+}
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
@@ -343,10 +606,36 @@ int dfw_chunk_forward_umma(const void *q, const void *k, const void *state, cons
   return T2FW_OK;
 }
 
+// sequential part of the backward; same contract as above
+int dfw_chunk_bwd_seq_umma(const void *go, const void *gs, const void *q, const void *k, const void *delta,
+                           const void *final_state, const float *Wb, const float *Ub, float *ScT, float *RcT,
+                           float *Ec, void *dv, void *ds, int64_t B, int64_t T_, int dtype, cudaStream_t st) {
+  if (!(aligned16(go) && aligned16(gs) && aligned16(q) && aligned16(k) && aligned16(delta) &&
+        aligned16(final_state) && aligned16(Wb) && aligned16(Ub) && aligned16(ScT) && aligned16(RcT) &&
+        aligned16(Ec) && aligned16(dv) && aligned16(ds)))
+    return T2FW_ERR_UNSUPPORTED;
+  int *status = nullptr;
+  int rc = lfw_chunk_status_ptr(&status);
+  if (rc != T2FW_OK) return rc;
+  const int64_t nc = ceil_div64(T_, kC);
+#define T2FW_LAUNCH(TT)                                                                                  \
+  do {                                                                                                   \
+    T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_seq_umma_kernel<TT>,                              \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemB));          \
+    dfw_chunk_bwd_seq_umma_kernel<TT><<<(unsigned)B, kTh, kSmemB, st>>>(                                 \
+        (const TT *)go, (const TT *)gs, (const TT *)q, (const TT *)k, (const float *)delta,              \
+        (const TT *)final_state, Wb, Ub, ScT, RcT, Ec, (TT *)dv, (TT *)ds, status, T_, nc);              \
+  } while (0)
+  if (dtype == T2FW_F16) T2FW_LAUNCH(__half); else T2FW_LAUNCH(__nv_bfloat16);
+#undef T2FW_LAUNCH
+  T2FW_CHECK_LAUNCH(1);
+  return T2FW_OK;
+}
+
 }  // namespace t2fw
 
 #ifdef T2FW_DFW_PROFILE
 extern "C" int t2fw_debug_dfw_prof(long long *out) {
-  return (int)cudaMemcpyFromSymbol(out, t2fw::g_dfw_prof, sizeof(long long) * 16);
+  return (int)cudaMemcpyFromSymbol(out, t2fw::g_dfw_prof, sizeof(long long) * 32);
 }
 #endif
