@@ -650,6 +650,9 @@ int dfw_chunk_forward_umma(const void *q, const void *k, const void *state, cons
 int dfw_chunk_bwd_seq_umma(const void *go, const void *gs, const void *q, const void *k, const void *delta,
                            const void *final_state, const float *Wb, const float *Ub, float *ScT, float *RcT,
                            float *Ec, void *dv, void *ds, int64_t B, int64_t T_, int dtype, cudaStream_t st);
+int dfw_chunk_bwd_par_umma(const void *go, const void *q, const void *k, const void *delta, const float *ScT,
+                           const float *RcT, const float *Ec, void *dq, void *dk, int64_t B, int64_t T_, int dtype,
+                           cudaStream_t st);
 static bool dfw_umma_enabled() {
   static const bool on = [] {
     const char *e = std::getenv("T2FW_DISABLE_DFW_UMMA");
@@ -732,10 +735,17 @@ static int dfw_chunk_backward_typed(const void *go, const void *gs, const void *
         (const T *)go, (const T *)gs, (const T *)q, (const T *)k, (const float *)delta, (const T *)final_state,
         Wb, Ub, Sc, Rc, Ec, (T *)dv, (T *)ds, T_, nc);
   }
-  T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_par_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)(10 * kTileVBytes)));
-  dfw_chunk_bwd_par_kernel<T><<<(unsigned)(B * nc), kSeqThreads, 10 * kTileVBytes, st>>>(
-      (const T *)go, (const T *)q, (const T *)k, (const float *)delta, Sc, Rc, Ec, (T *)dq, (T *)dk, T_, nc);
+  int par_rc = T2FW_ERR_UNSUPPORTED;
+  if (dfw_umma_enabled() && !dfw_bwd_mma_sync_forced())
+    par_rc = dfw_chunk_bwd_par_umma(go, q, k, delta, Sc, Rc, Ec, dq, dk, B, T_,
+                                    std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16, st);
+  if (par_rc != T2FW_OK && par_rc != T2FW_ERR_UNSUPPORTED) return par_rc;
+  if (par_rc == T2FW_ERR_UNSUPPORTED) {
+    T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_par_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(10 * kTileVBytes)));
+    dfw_chunk_bwd_par_kernel<T><<<(unsigned)(B * nc), kSeqThreads, 10 * kTileVBytes, st>>>(
+        (const T *)go, (const T *)q, (const T *)k, (const float *)delta, Sc, Rc, Ec, (T *)dq, (T *)dk, T_, nc);
+  }
   T2FW_CHECK_LAUNCH(3);
   return T2FW_OK;
 }

@@ -577,6 +577,193 @@ dfw_chunk_bwd_seq_umma_kernel(const T *__restrict__ go, const T *__restrict__ gs
   if (warp == 0) umma::tmem_dealloc(tb, 128);
 }
 
+// ---- backward, chunk-parallel part -------------------------------------------------------------------
+// One CTA per (batch row, chunk):  with X1 = strict_lower(dO Dl^T), X2 = Dl E^T,
+// Y = strict_upper(X2) + its mirror image,
+//   d_query = dO S0 + X1 K ,   d_key = Dl R_end + X1^T Q - Y K - E S0 .
+// E is stored negated, which makes the third and fourth term of d_key accumulate with a plus sign.
+// Tensor memory (M = 64 accumulators, lane sets A / B as above):
+//   columns  0-63 :  A: d_key               B: d_query
+//   columns 64-127:  A: Dl (-E)^T = -X2     B: dO Dl^T
+// First round: dO [S0^T; Dl]^T -> lane set B, Dl [R_end^T; -E]^T -> lane set A (128-column products
+// over two adjacent tiles), then (-E) S0 onto d_key.  Second round after the masked tiles are
+// written: X1 K onto d_query, X1^T Q and (-Y) K onto d_key.
+constexpr int oPS = 0, oPD = kTileU, oPR = 2 * kTileU, oPE = 3 * kTileU, oPG = 4 * kTileU, oPX = 5 * kTileU,
+              oPXT = 6 * kTileU, oPY = 7 * kTileU, oPK = 8 * kTileU, oPQ = oPK + kKTBytes;
+constexpr int oPStgQ = oPQ + kKTBytes, oPStgK = oPStgQ + kC * kRow16;
+constexpr int kSmemP = oPStgK + kC * kRow16;
+static_assert(kSmemP <= 227 * 1024, "shared memory layout");
+
+template <typename T>
+__global__ void __launch_bounds__(kTh, 1)
+dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q, const T *__restrict__ k,
+                              const float *__restrict__ delta, const float *__restrict__ ScT,
+                              const float *__restrict__ RcT, const float *__restrict__ Ec, T *__restrict__ dq,
+                              T *__restrict__ dk, int *__restrict__ status, int64_t T_, int64_t nc) {
+  extern __shared__ __align__(128) unsigned char sm[];
+  __shared__ __align__(8) uint64_t bar_m1, bar_m2;
+  __shared__ uint32_t tmem_slot;
+  __shared__ volatile int s_fail;
+
+  const int64_t b = blockIdx.x / nc, c = blockIdx.x % nc, t0 = c * kC;
+  const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
+  const size_t base = ((size_t)b * T_ + t0) * kDim, tile = (size_t)blockIdx.x * kC * kDim;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qd = warp & 3, half = warp >> 2, side = lane >> 4, fl = lane & 15;
+  const int row = 16 * qd + fl, c0 = 32 * half;
+
+  if (tid == 0) {
+    umma::mbar_init(&bar_m1, 2);
+    umma::mbar_init(&bar_m2, 2);
+    umma::mbar_fence_init();
+    s_fail = 0;
+  }
+  if (warp == 0) umma::tmem_alloc(&tmem_slot, 128);
+
+  // ---- global -> TF32 tiles; every load is issued before the first store ----------------------------
+  {
+    float4 rd[4], re[4], rs[4], rr[4];
+    uint2 rg[4], rq[4], rk[4];
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const uint2 z2 = make_uint2(0u, 0u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int p = tid + kTh * j, r = p >> 4, c4 = (p & 15) * 4;       // 16 lanes per row
+      const bool in = r < nvalid;
+      rd[j] = in ? *reinterpret_cast<const float4 *>(delta + base + (size_t)r * kDim + c4) : z4;
+      rg[j] = in ? *reinterpret_cast<const uint2 *>(go + base + (size_t)r * kDim + c4) : z2;
+      re[j] = *reinterpret_cast<const float4 *>(Ec + tile + r * kDim + c4);
+      rs[j] = *reinterpret_cast<const float4 *>(ScT + tile + r * kDim + c4);
+      rr[j] = *reinterpret_cast<const float4 *>(RcT + tile + r * kDim + c4);
+      const int combo = warp * 4 + j, rt_ = 4 * (combo >> 1) + (lane >> 3), ct = 4 * (8 * (combo & 1) + (lane & 7));
+      const bool in2 = rt_ < nvalid;                                     // 8 column pieces x 4 steps per warp
+      rq[j] = in2 ? *reinterpret_cast<const uint2 *>(q + base + (size_t)rt_ * kDim + ct) : z2;
+      rk[j] = in2 ? *reinterpret_cast<const uint2 *>(k + base + (size_t)rt_ * kDim + ct) : z2;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int p = tid + kTh * j, r = p >> 4, c4 = (p & 15) * 4;
+      const int o = umma::tile_off(r, c4, kDim);
+      *reinterpret_cast<float4 *>(sm + oPD + o) = make_float4(rt(rd[j].x), rt(rd[j].y), rt(rd[j].z), rt(rd[j].w));
+      *reinterpret_cast<float4 *>(sm + oPE + o) = make_float4(-rt(re[j].x), -rt(re[j].y), -rt(re[j].z), -rt(re[j].w));
+      *reinterpret_cast<float4 *>(sm + oPS + o) = make_float4(rt(rs[j].x), rt(rs[j].y), rt(rs[j].z), rt(rs[j].w));
+      *reinterpret_cast<float4 *>(sm + oPR + o) = make_float4(rt(rr[j].x), rt(rr[j].y), rt(rr[j].z), rt(rr[j].w));
+      const float2 g0 = Pair<T>::ld(reinterpret_cast<const T *>(&rg[j].x)), g1 = Pair<T>::ld(reinterpret_cast<const T *>(&rg[j].y));
+      *reinterpret_cast<float4 *>(sm + oPG + o) = make_float4(g0.x, g0.y, g1.x, g1.y);
+      const int combo = warp * 4 + j, rt_ = 4 * (combo >> 1) + (lane >> 3), ct = 4 * (8 * (combo & 1) + (lane & 7));
+      const float2 q0 = Pair<T>::ld(reinterpret_cast<const T *>(&rq[j].x)), q1 = Pair<T>::ld(reinterpret_cast<const T *>(&rq[j].y));
+      const float2 k0 = Pair<T>::ld(reinterpret_cast<const T *>(&rk[j].x)), k1 = Pair<T>::ld(reinterpret_cast<const T *>(&rk[j].y));
+      const int o0 = kt_off(ct, rt_), o1 = kt_off(ct + 1, rt_), o2 = kt_off(ct + 2, rt_), o3 = kt_off(ct + 3, rt_);
+      *reinterpret_cast<float *>(sm + oPQ + o0) = q0.x; *reinterpret_cast<float *>(sm + oPQ + o1) = q0.y;
+      *reinterpret_cast<float *>(sm + oPQ + o2) = q1.x; *reinterpret_cast<float *>(sm + oPQ + o3) = q1.y;
+      *reinterpret_cast<float *>(sm + oPK + o0) = k0.x; *reinterpret_cast<float *>(sm + oPK + o1) = k0.y;
+      *reinterpret_cast<float *>(sm + oPK + o2) = k1.x; *reinterpret_cast<float *>(sm + oPK + o3) = k1.y;
+    }
+  }
+  umma::fence_async_smem();
+  sync_all();
+  const uint32_t tb = tmem_slot;
+  const uint32_t tl = umma::tmem_addr(tb, 32 * qd, 0);
+
+  // ---- first round -----------------------------------------------------------------------------------
+  if (lane == 0 && warp < 2) {
+    const uint32_t i128 = umma::make_idesc_tf32(kDim, 2 * kDim, false, false), i64 = umma::make_idesc_tf32(kDim, kDim, false, false);
+    const uint32_t aA = umma::smem_u32(sm + (warp == 0 ? oPG : oPD)), aB = umma::smem_u32(sm + (warp == 0 ? oPS : oPR));
+    const uint32_t d = umma::tmem_addr(tb, warp == 0 ? 16 : 0, 0);
+#pragma unroll
+    for (int ks = 0; ks < kC / 8; ++ks)
+      umma::mma_tf32(d, umma::desc_kmajor(aA, kDim, 0, ks), umma::desc_kmajor(aB, kDim, 0, ks), i128, ks > 0);
+    if (warp == 1) {
+      const uint32_t aE = umma::smem_u32(sm + oPE), aS = umma::smem_u32(sm + oPS);
+#pragma unroll
+      for (int ks = 0; ks < kC / 8; ++ks)
+        umma::mma_tf32(d, umma::desc_kmajor(aE, kDim, 0, ks), umma::desc_kmajor(aS, kDim, 0, ks), i64, true);
+    }
+    umma::mma_commit(&bar_m1);
+  }
+  if (!umma::mbar_wait(&bar_m1, 0)) s_fail = 1;
+  umma::fence_after_sync();
+  {
+    // lane set B: dO Dl^T (row t, columns i) -> X1 and X1^T;  lane set A: -X2 (row t, columns i) -> -Y
+    float v[32];
+    umma::tmem_ld16(tl + 64 + c0, *reinterpret_cast<float(*)[16]>(v));
+    umma::tmem_ld16(tl + 64 + c0 + 16, *reinterpret_cast<float(*)[16]>(v + 16));
+    umma::tmem_ld_wait();
+    if (side) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = (c0 + j < row) ? rt(v[j]) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4 *>(sm + oPX + umma::tile_off(row, c0 + j, kC)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) *reinterpret_cast<float *>(sm + oPXT + umma::tile_off(c0 + j, row, kC)) = v[j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int i = c0 + j;
+        const float y = rt(v[j]);
+        if (i > row) {
+          *reinterpret_cast<float *>(sm + oPY + umma::tile_off(row, i, kC)) = y;
+          *reinterpret_cast<float *>(sm + oPY + umma::tile_off(i, row, kC)) = y;
+        } else if (i == row) {
+          *reinterpret_cast<float *>(sm + oPY + umma::tile_off(row, i, kC)) = 0.f;
+        }
+      }
+    }
+  }
+  umma::fence_async_smem();
+  sync_all();
+  // ---- second round ----------------------------------------------------------------------------------
+  if (lane == 0 && warp < 2) {
+    const uint32_t idesc = umma::make_idesc_tf32(kDim, kDim, false, false);
+    const uint32_t aK = umma::smem_u32(sm + oPK), aQ = umma::smem_u32(sm + oPQ);
+    if (warp == 0) {
+      const uint32_t aX = umma::smem_u32(sm + oPX);
+#pragma unroll
+      for (int ks = 0; ks < kC / 8; ++ks)
+        umma::mma_tf32(umma::tmem_addr(tb, 16, 0), umma::desc_kmajor(aX, kC, 0, ks), kt_desc(aK, ks), idesc, true);
+    } else {
+      const uint32_t aXT = umma::smem_u32(sm + oPXT), aY = umma::smem_u32(sm + oPY);
+#pragma unroll
+      for (int ks = 0; ks < kC / 8; ++ks)
+        umma::mma_tf32(umma::tmem_addr(tb, 0, 0), umma::desc_kmajor(aXT, kC, 0, ks), kt_desc(aQ, ks), idesc, true);
+#pragma unroll
+      for (int ks = 0; ks < kC / 8; ++ks)
+        umma::mma_tf32(umma::tmem_addr(tb, 0, 0), umma::desc_kmajor(aY, kC, 0, ks), kt_desc(aK, ks), idesc, true);
+    }
+    umma::mma_commit(&bar_m2);
+  }
+  if (!s_fail && !umma::mbar_wait(&bar_m2, 0)) s_fail = 1;
+  umma::fence_after_sync();
+  {
+    // lane set A: d_key, lane set B: d_query (row t, columns m) -> padded 16-bit staging rows
+    float v[32];
+    umma::tmem_ld16(tl + c0, *reinterpret_cast<float(*)[16]>(v));
+    umma::tmem_ld16(tl + c0 + 16, *reinterpret_cast<float(*)[16]>(v + 16));
+    umma::tmem_ld_wait();
+    uint32_t pk[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) Pair<T>::st(reinterpret_cast<T *>(&pk[j]), v[2 * j], v[2 * j + 1]);
+    unsigned char *stg = sm + (side ? oPStgQ : oPStgK) + row * kRow16 + c0 * 2;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      *reinterpret_cast<uint4 *>(stg + 16 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+  }
+  sync_all();
+  if (!s_fail) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int p = tid + kTh * j, r = p >> 3, c8 = (p & 7) * 8;
+      if (r < nvalid) {
+        *reinterpret_cast<uint4 *>(dq + base + (size_t)r * kDim + c8) = *reinterpret_cast<const uint4 *>(sm + oPStgQ + r * kRow16 + c8 * 2);
+        *reinterpret_cast<uint4 *>(dk + base + (size_t)r * kDim + c8) = *reinterpret_cast<const uint4 *>(sm + oPStgK + r * kRow16 + c8 * 2);
+      }
+    }
+  }
+  if (s_fail && tid == 0) atomicExch(status, 1);
+  if (warp == 0) umma::tmem_dealloc(tb, 128);
+}
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
@@ -625,6 +812,31 @@ int dfw_chunk_bwd_seq_umma(const void *go, const void *gs, const void *q, const 
     dfw_chunk_bwd_seq_umma_kernel<TT><<<(unsigned)B, kTh, kSmemB, st>>>(                                 \
         (const TT *)go, (const TT *)gs, (const TT *)q, (const TT *)k, (const float *)delta,              \
         (const TT *)final_state, Wb, Ub, ScT, RcT, Ec, (TT *)dv, (TT *)ds, status, T_, nc);              \
+  } while (0)
+  if (dtype == T2FW_F16) T2FW_LAUNCH(__half); else T2FW_LAUNCH(__nv_bfloat16);
+#undef T2FW_LAUNCH
+  T2FW_CHECK_LAUNCH(1);
+  return T2FW_OK;
+}
+
+// chunk-parallel part of the backward; same contract as above
+int dfw_chunk_bwd_par_umma(const void *go, const void *q, const void *k, const void *delta, const float *ScT,
+                           const float *RcT, const float *Ec, void *dq, void *dk, int64_t B, int64_t T_, int dtype,
+                           cudaStream_t st) {
+  if (!(aligned16(go) && aligned16(q) && aligned16(k) && aligned16(delta) && aligned16(ScT) && aligned16(RcT) &&
+        aligned16(Ec) && aligned16(dq) && aligned16(dk)))
+    return T2FW_ERR_UNSUPPORTED;
+  int *status = nullptr;
+  int rc = lfw_chunk_status_ptr(&status);
+  if (rc != T2FW_OK) return rc;
+  const int64_t nc = ceil_div64(T_, kC);
+#define T2FW_LAUNCH(TT)                                                                                  \
+  do {                                                                                                   \
+    T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_par_umma_kernel<TT>,                              \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemP));          \
+    dfw_chunk_bwd_par_umma_kernel<TT><<<(unsigned)(B * nc), kTh, kSmemP, st>>>(                          \
+        (const TT *)go, (const TT *)q, (const TT *)k, (const float *)delta, ScT, RcT, Ec, (TT *)dq,      \
+        (TT *)dk, status, T_, nc);                                                                       \
   } while (0)
   if (dtype == T2FW_F16) T2FW_LAUNCH(__half); else T2FW_LAUNCH(__nv_bfloat16);
 #undef T2FW_LAUNCH
