@@ -578,7 +578,7 @@ dfw_chunk_bwd_seq_umma_kernel(const T *__restrict__ go, const T *__restrict__ gs
 }
 
 // ---- backward, chunk-parallel part -------------------------------------------------------------------
-// One CTA per (batch row, chunk):  with X1 = strict_lower(dO Dl^T), X2 = Dl E^T,
+// Persistent CTAs, one per SM, each taking every gridDim-th (batch row, chunk):  with X1 = strict_lower(dO Dl^T), X2 = Dl E^T,
 // Y = strict_upper(X2) + its mirror image,
 //   d_query = dO S0 + X1 K ,   d_key = Dl R_end + X1^T Q - Y K - E S0 .
 // E is stored negated, which makes the third and fourth term of d_key accumulate with a plus sign.
@@ -599,15 +599,13 @@ __global__ void __launch_bounds__(kTh, 1)
 dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q, const T *__restrict__ k,
                               const float *__restrict__ delta, const float *__restrict__ ScT,
                               const float *__restrict__ RcT, const float *__restrict__ Ec, T *__restrict__ dq,
-                              T *__restrict__ dk, int *__restrict__ status, int64_t T_, int64_t nc) {
+                              T *__restrict__ dk, int *__restrict__ status, int64_t T_, int64_t nc,
+                              int64_t total) {
   extern __shared__ __align__(128) unsigned char sm[];
   __shared__ __align__(8) uint64_t bar_m1, bar_m2;
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int s_fail;
 
-  const int64_t b = blockIdx.x / nc, c = blockIdx.x % nc, t0 = c * kC;
-  const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
-  const size_t base = ((size_t)b * T_ + t0) * kDim, tile = (size_t)blockIdx.x * kC * kDim;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qd = warp & 3, half = warp >> 2, side = lane >> 4, fl = lane & 15;
   const int row = 16 * qd + fl, c0 = 32 * half;
@@ -620,26 +618,37 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
   }
   if (warp == 0) umma::tmem_alloc(&tmem_slot, 128);
 
-  // ---- global -> TF32 tiles; every load is issued before the first store ----------------------------
-  {
-    float4 rd[4], re[4], rs[4], rr[4];
-    uint2 rg[4], rq[4], rk[4];
+  // The inputs of a chunk travel global -> registers -> TF32 tiles in two steps, so that the loads of
+  // the next chunk are in flight during the first round of products and land in the tiles as soon as
+  // the products that read them have finished.
+  float4 rd[4], re[4], rs[4], rr[4];
+  uint2 rg[4], rq[4], rk[4];
+  auto chunk_base = [&](int64_t ci) { return ((size_t)(ci / nc) * T_ + (ci % nc) * kC) * kDim; };
+  auto chunk_valid = [&](int64_t ci) {
+    const int64_t t0 = (ci % nc) * kC;
+    return (int)((T_ - t0 < kC) ? T_ - t0 : kC);
+  };
+  auto load = [&](int64_t ci) {
+    const size_t base = chunk_base(ci), tile = (size_t)ci * kC * kDim;
+    const int nv = chunk_valid(ci);
     const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
     const uint2 z2 = make_uint2(0u, 0u);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int p = tid + kTh * j, r = p >> 4, c4 = (p & 15) * 4;       // 16 lanes per row
-      const bool in = r < nvalid;
+      const bool in = r < nv;
       rd[j] = in ? *reinterpret_cast<const float4 *>(delta + base + (size_t)r * kDim + c4) : z4;
       rg[j] = in ? *reinterpret_cast<const uint2 *>(go + base + (size_t)r * kDim + c4) : z2;
       re[j] = *reinterpret_cast<const float4 *>(Ec + tile + r * kDim + c4);
       rs[j] = *reinterpret_cast<const float4 *>(ScT + tile + r * kDim + c4);
       rr[j] = *reinterpret_cast<const float4 *>(RcT + tile + r * kDim + c4);
       const int combo = warp * 4 + j, rt_ = 4 * (combo >> 1) + (lane >> 3), ct = 4 * (8 * (combo & 1) + (lane & 7));
-      const bool in2 = rt_ < nvalid;                                     // 8 column pieces x 4 steps per warp
+      const bool in2 = rt_ < nv;                                         // 8 column pieces x 4 steps per warp
       rq[j] = in2 ? *reinterpret_cast<const uint2 *>(q + base + (size_t)rt_ * kDim + ct) : z2;
       rk[j] = in2 ? *reinterpret_cast<const uint2 *>(k + base + (size_t)rt_ * kDim + ct) : z2;
     }
+  };
+  auto store_direct = [&]() {     // Dl, -E, S0^T, R_end^T, dO: read by the first round only
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int p = tid + kTh * j, r = p >> 4, c4 = (p & 15) * 4;
@@ -650,6 +659,11 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
       *reinterpret_cast<float4 *>(sm + oPR + o) = make_float4(rt(rr[j].x), rt(rr[j].y), rt(rr[j].z), rt(rr[j].w));
       const float2 g0 = Pair<T>::ld(reinterpret_cast<const T *>(&rg[j].x)), g1 = Pair<T>::ld(reinterpret_cast<const T *>(&rg[j].y));
       *reinterpret_cast<float4 *>(sm + oPG + o) = make_float4(g0.x, g0.y, g1.x, g1.y);
+    }
+  };
+  auto store_trans = [&]() {      // Q^T, K^T: read by the second round only
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
       const int combo = warp * 4 + j, rt_ = 4 * (combo >> 1) + (lane >> 3), ct = 4 * (8 * (combo & 1) + (lane & 7));
       const float2 q0 = Pair<T>::ld(reinterpret_cast<const T *>(&rq[j].x)), q1 = Pair<T>::ld(reinterpret_cast<const T *>(&rq[j].y));
       const float2 k0 = Pair<T>::ld(reinterpret_cast<const T *>(&rk[j].x)), k1 = Pair<T>::ld(reinterpret_cast<const T *>(&rk[j].y));
@@ -659,109 +673,133 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
       *reinterpret_cast<float *>(sm + oPK + o0) = k0.x; *reinterpret_cast<float *>(sm + oPK + o1) = k0.y;
       *reinterpret_cast<float *>(sm + oPK + o2) = k1.x; *reinterpret_cast<float *>(sm + oPK + o3) = k1.y;
     }
-  }
-  umma::fence_async_smem();
-  sync_all();
-  const uint32_t tb = tmem_slot;
-  const uint32_t tl = umma::tmem_addr(tb, 32 * qd, 0);
-
-  // ---- first round -----------------------------------------------------------------------------------
-  if (lane == 0 && warp < 2) {
-    const uint32_t i128 = umma::make_idesc_tf32(kDim, 2 * kDim, false, false), i64 = umma::make_idesc_tf32(kDim, kDim, false, false);
-    const uint32_t aA = umma::smem_u32(sm + (warp == 0 ? oPG : oPD)), aB = umma::smem_u32(sm + (warp == 0 ? oPS : oPR));
-    const uint32_t d = umma::tmem_addr(tb, warp == 0 ? 16 : 0, 0);
-#pragma unroll
-    for (int ks = 0; ks < kC / 8; ++ks)
-      umma::mma_tf32(d, umma::desc_kmajor(aA, kDim, 0, ks), umma::desc_kmajor(aB, kDim, 0, ks), i128, ks > 0);
-    if (warp == 1) {
-      const uint32_t aE = umma::smem_u32(sm + oPE), aS = umma::smem_u32(sm + oPS);
-#pragma unroll
-      for (int ks = 0; ks < kC / 8; ++ks)
-        umma::mma_tf32(d, umma::desc_kmajor(aE, kDim, 0, ks), umma::desc_kmajor(aS, kDim, 0, ks), i64, true);
-    }
-    umma::mma_commit(&bar_m1);
-  }
-  if (!umma::mbar_wait(&bar_m1, 0)) s_fail = 1;
-  umma::fence_after_sync();
-  {
-    // lane set B: dO Dl^T (row t, columns i) -> X1 and X1^T;  lane set A: -X2 (row t, columns i) -> -Y
-    float v[32];
-    umma::tmem_ld16(tl + 64 + c0, *reinterpret_cast<float(*)[16]>(v));
-    umma::tmem_ld16(tl + 64 + c0 + 16, *reinterpret_cast<float(*)[16]>(v + 16));
-    umma::tmem_ld_wait();
-    if (side) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = (c0 + j < row) ? rt(v[j]) : 0.f;
-#pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<float4 *>(sm + oPX + umma::tile_off(row, c0 + j, kC)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) *reinterpret_cast<float *>(sm + oPXT + umma::tile_off(c0 + j, row, kC)) = v[j];
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int i = c0 + j;
-        const float y = rt(v[j]);
-        if (i > row) {
-          *reinterpret_cast<float *>(sm + oPY + umma::tile_off(row, i, kC)) = y;
-          *reinterpret_cast<float *>(sm + oPY + umma::tile_off(i, row, kC)) = y;
-        } else if (i == row) {
-          *reinterpret_cast<float *>(sm + oPY + umma::tile_off(row, i, kC)) = 0.f;
-        }
-      }
-    }
-  }
-  umma::fence_async_smem();
-  sync_all();
-  // ---- second round ----------------------------------------------------------------------------------
-  if (lane == 0 && warp < 2) {
-    const uint32_t idesc = umma::make_idesc_tf32(kDim, kDim, false, false);
-    const uint32_t aK = umma::smem_u32(sm + oPK), aQ = umma::smem_u32(sm + oPQ);
-    if (warp == 0) {
-      const uint32_t aX = umma::smem_u32(sm + oPX);
-#pragma unroll
-      for (int ks = 0; ks < kC / 8; ++ks)
-        umma::mma_tf32(umma::tmem_addr(tb, 16, 0), umma::desc_kmajor(aX, kC, 0, ks), kt_desc(aK, ks), idesc, true);
-    } else {
-      const uint32_t aXT = umma::smem_u32(sm + oPXT), aY = umma::smem_u32(sm + oPY);
-#pragma unroll
-      for (int ks = 0; ks < kC / 8; ++ks)
-        umma::mma_tf32(umma::tmem_addr(tb, 0, 0), umma::desc_kmajor(aXT, kC, 0, ks), kt_desc(aQ, ks), idesc, true);
-#pragma unroll
-      for (int ks = 0; ks < kC / 8; ++ks)
-        umma::mma_tf32(umma::tmem_addr(tb, 0, 0), umma::desc_kmajor(aY, kC, 0, ks), kt_desc(aK, ks), idesc, true);
-    }
-    umma::mma_commit(&bar_m2);
-  }
-  if (!s_fail && !umma::mbar_wait(&bar_m2, 0)) s_fail = 1;
-  umma::fence_after_sync();
-  {
-    // lane set A: d_key, lane set B: d_query (row t, columns m) -> padded 16-bit staging rows
-    float v[32];
-    umma::tmem_ld16(tl + c0, *reinterpret_cast<float(*)[16]>(v));
-    umma::tmem_ld16(tl + c0 + 16, *reinterpret_cast<float(*)[16]>(v + 16));
-    umma::tmem_ld_wait();
-    uint32_t pk[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) Pair<T>::st(reinterpret_cast<T *>(&pk[j]), v[2 * j], v[2 * j + 1]);
-    unsigned char *stg = sm + (side ? oPStgQ : oPStgK) + row * kRow16 + c0 * 2;
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      *reinterpret_cast<uint4 *>(stg + 16 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-  }
-  sync_all();
-  if (!s_fail) {
+  };
+  // staged d_query / d_key rows of a chunk -> global, consecutive threads consecutive addresses
+  auto copy_out = [&](int64_t ci) {
+    const size_t base = chunk_base(ci);
+    const int nv = chunk_valid(ci);
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int p = tid + kTh * j, r = p >> 3, c8 = (p & 7) * 8;
-      if (r < nvalid) {
+      if (r < nv) {
         *reinterpret_cast<uint4 *>(dq + base + (size_t)r * kDim + c8) = *reinterpret_cast<const uint4 *>(sm + oPStgQ + r * kRow16 + c8 * 2);
         *reinterpret_cast<uint4 *>(dk + base + (size_t)r * kDim + c8) = *reinterpret_cast<const uint4 *>(sm + oPStgK + r * kRow16 + c8 * 2);
       }
     }
+  };
+
+  int64_t ci = blockIdx.x, prev = -1;
+  if (ci < total) {
+    load(ci);
+    store_direct();
+    store_trans();
   }
+  uint32_t par = 0;
+  uint32_t tb = 0, tl = 0;
+  for (; ci < total; ci += gridDim.x) {
+    umma::fence_async_smem();
+    sync_all();                   // tiles complete; staging rows of the chunk before complete
+    tb = tmem_slot;
+    tl = umma::tmem_addr(tb, 32 * qd, 0);
+    if (s_fail) break;
+    // ---- first round ---------------------------------------------------------------------------------
+    if (lane == 0 && warp < 2) {
+      const uint32_t i128 = umma::make_idesc_tf32(kDim, 2 * kDim, false, false), i64 = umma::make_idesc_tf32(kDim, kDim, false, false);
+      const uint32_t aA = umma::smem_u32(sm + (warp == 0 ? oPG : oPD)), aB = umma::smem_u32(sm + (warp == 0 ? oPS : oPR));
+      const uint32_t d = umma::tmem_addr(tb, warp == 0 ? 16 : 0, 0);
+#pragma unroll
+      for (int ks = 0; ks < kC / 8; ++ks)
+        umma::mma_tf32(d, umma::desc_kmajor(aA, kDim, 0, ks), umma::desc_kmajor(aB, kDim, 0, ks), i128, ks > 0);
+      if (warp == 1) {
+        const uint32_t aE = umma::smem_u32(sm + oPE), aS = umma::smem_u32(sm + oPS);
+#pragma unroll
+        for (int ks = 0; ks < kC / 8; ++ks)
+          umma::mma_tf32(d, umma::desc_kmajor(aE, kDim, 0, ks), umma::desc_kmajor(aS, kDim, 0, ks), i64, true);
+      }
+      umma::mma_commit(&bar_m1);
+    }
+    const int64_t next = ci + gridDim.x;
+    const bool has_next = next < total;
+    if (has_next) load(next);
+    if (prev >= 0) copy_out(prev);
+    if (!umma::mbar_wait(&bar_m1, par)) s_fail = 1;
+    umma::fence_after_sync();
+    {
+      // lane set B: dO Dl^T (row t, columns i) -> X1 and X1^T;  lane set A: -X2 (row t, columns i) -> -Y
+      float v[32];
+      umma::tmem_ld16(tl + 64 + c0, *reinterpret_cast<float(*)[16]>(v));
+      umma::tmem_ld16(tl + 64 + c0 + 16, *reinterpret_cast<float(*)[16]>(v + 16));
+      umma::tmem_ld_wait();
+      if (side) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (c0 + j < row) ? rt(v[j]) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4 *>(sm + oPX + umma::tile_off(row, c0 + j, kC)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) *reinterpret_cast<float *>(sm + oPXT + umma::tile_off(c0 + j, row, kC)) = v[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int i = c0 + j;
+          const float y = rt(v[j]);
+          if (i > row) {
+            *reinterpret_cast<float *>(sm + oPY + umma::tile_off(row, i, kC)) = y;
+            *reinterpret_cast<float *>(sm + oPY + umma::tile_off(i, row, kC)) = y;
+          } else if (i == row) {
+            *reinterpret_cast<float *>(sm + oPY + umma::tile_off(row, i, kC)) = 0.f;
+          }
+        }
+      }
+    }
+    umma::fence_async_smem();
+    sync_all();
+    // ---- second round --------------------------------------------------------------------------------
+    if (lane == 0 && warp < 2) {
+      const uint32_t idesc = umma::make_idesc_tf32(kDim, kDim, false, false);
+      const uint32_t aK = umma::smem_u32(sm + oPK), aQ = umma::smem_u32(sm + oPQ);
+      if (warp == 0) {
+        const uint32_t aX = umma::smem_u32(sm + oPX);
+#pragma unroll
+        for (int ks = 0; ks < kC / 8; ++ks)
+          umma::mma_tf32(umma::tmem_addr(tb, 16, 0), umma::desc_kmajor(aX, kC, 0, ks), kt_desc(aK, ks), idesc, true);
+      } else {
+        const uint32_t aXT = umma::smem_u32(sm + oPXT), aY = umma::smem_u32(sm + oPY);
+#pragma unroll
+        for (int ks = 0; ks < kC / 8; ++ks)
+          umma::mma_tf32(umma::tmem_addr(tb, 0, 0), umma::desc_kmajor(aXT, kC, 0, ks), kt_desc(aQ, ks), idesc, true);
+#pragma unroll
+        for (int ks = 0; ks < kC / 8; ++ks)
+          umma::mma_tf32(umma::tmem_addr(tb, 0, 0), umma::desc_kmajor(aY, kC, 0, ks), kt_desc(aK, ks), idesc, true);
+      }
+      umma::mma_commit(&bar_m2);
+    }
+    if (has_next) store_direct();     // the first round has finished with these tiles
+    if (!s_fail && !umma::mbar_wait(&bar_m2, par)) s_fail = 1;
+    umma::fence_after_sync();
+    {
+      // lane set A: d_key, lane set B: d_query (row t, columns m) -> padded 16-bit staging rows
+      float v[32];
+      umma::tmem_ld16(tl + c0, *reinterpret_cast<float(*)[16]>(v));
+      umma::tmem_ld16(tl + c0 + 16, *reinterpret_cast<float(*)[16]>(v + 16));
+      umma::tmem_ld_wait();
+      uint32_t pk[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) Pair<T>::st(reinterpret_cast<T *>(&pk[j]), v[2 * j], v[2 * j + 1]);
+      unsigned char *stg = sm + (side ? oPStgQ : oPStgK) + row * kRow16 + c0 * 2;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4 *>(stg + 16 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+    }
+    if (has_next) store_trans();      // the second round has finished with these tiles
+    prev = ci;
+    par ^= 1u;
+    umma::fence_before_sync();
+  }
+  sync_all();
+  if (!s_fail && prev >= 0) copy_out(prev);
   if (s_fail && tid == 0) atomicExch(status, 1);
-  if (warp == 0) umma::tmem_dealloc(tb, 128);
+  if (warp == 0) umma::tmem_dealloc(tmem_slot, 128);
 }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -826,17 +864,23 @@ int dfw_chunk_bwd_par_umma(const void *go, const void *q, const void *k, const v
   if (!(aligned16(go) && aligned16(q) && aligned16(k) && aligned16(delta) && aligned16(ScT) && aligned16(RcT) &&
         aligned16(Ec) && aligned16(dq) && aligned16(dk)))
     return T2FW_ERR_UNSUPPORTED;
+  int dev = 0;
+  T2FW_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return T2FW_ERR_UNSUPPORTED;
+  static int sms[64] = {};
+  if (sms[dev] == 0) T2FW_CHECK_CUDA(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
   int *status = nullptr;
   int rc = lfw_chunk_status_ptr(&status);
   if (rc != T2FW_OK) return rc;
-  const int64_t nc = ceil_div64(T_, kC);
+  const int64_t nc = ceil_div64(T_, kC), total = B * nc;
+  const unsigned grid = (unsigned)(total < sms[dev] ? total : sms[dev]);     // one persistent CTA per SM
 #define T2FW_LAUNCH(TT)                                                                                  \
   do {                                                                                                   \
     T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_par_umma_kernel<TT>,                              \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemP));          \
-    dfw_chunk_bwd_par_umma_kernel<TT><<<(unsigned)(B * nc), kTh, kSmemP, st>>>(                          \
+    dfw_chunk_bwd_par_umma_kernel<TT><<<grid, kTh, kSmemP, st>>>(                                        \
         (const TT *)go, (const TT *)q, (const TT *)k, (const float *)delta, ScT, RcT, Ec, (TT *)dq,      \
-        (TT *)dk, status, T_, nc);                                                                       \
+        (TT *)dk, status, T_, nc, total);                                                                \
   } while (0)
   if (dtype == T2FW_F16) T2FW_LAUNCH(__half); else T2FW_LAUNCH(__nv_bfloat16);
 #undef T2FW_LAUNCH
