@@ -23,6 +23,8 @@
 //   dfw_chunk_fwd_kernel<T>          one CTA per batch row, sequential over chunks
 //   dfw_chunk_bwd_seq_kernel<T>      one CTA per batch row, chunks in reverse: state walk-back, E, R
 //   dfw_chunk_bwd_par_kernel<T>      (batch row, chunk): d_query and d_key from the stored S0, R_end, E
+// The last three have tcgen05 versions in dfw_chunk_umma.cu, which the launchers below prefer; the
+// versions here run when a pointer is not 16-byte aligned or T2FW_DISABLE_DFW_UMMA=1 is set.
 #include <cstdlib>
 #include <type_traits>
 
@@ -661,15 +663,6 @@ static bool dfw_umma_enabled() {
   return on;
 }
 
-// experiment switch: tcgen05 forward with the mma.sync sequential backward
-static bool dfw_bwd_mma_sync_forced() {
-  static const bool on = [] {
-    const char *e = std::getenv("T2FW_DFW_BWD_MMA_SYNC");
-    return e && e[0] == '1';
-  }();
-  return on;
-}
-
 bool dfw_chunk_supported(int64_t D, int64_t M, int dtype) {
   return D == kDim && M == kDim && (dtype == T2FW_F16 || dtype == T2FW_BF16);
 }
@@ -724,7 +717,7 @@ static int dfw_chunk_backward_typed(const void *go, const void *gs, const void *
       (const T *)q, (const T *)k, (const T *)go, Wb, Ub, T_, nc);
   float *Sc = Ub + u_floats(B, nc), *Rc = Sc + wu_floats(B, nc), *Ec = Rc + wu_floats(B, nc);
   int seq_rc = T2FW_ERR_UNSUPPORTED;
-  if (dfw_umma_enabled() && !dfw_bwd_mma_sync_forced())
+  if (dfw_umma_enabled())
     seq_rc = dfw_chunk_bwd_seq_umma(go, gs, q, k, delta, final_state, Wb, Ub, Sc, Rc, Ec, dv, ds, B, T_,
                                     std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16, st);
   if (seq_rc != T2FW_OK && seq_rc != T2FW_ERR_UNSUPPORTED) return seq_rc;
@@ -736,7 +729,7 @@ static int dfw_chunk_backward_typed(const void *go, const void *gs, const void *
         Wb, Ub, Sc, Rc, Ec, (T *)dv, (T *)ds, T_, nc);
   }
   int par_rc = T2FW_ERR_UNSUPPORTED;
-  if (dfw_umma_enabled() && !dfw_bwd_mma_sync_forced())
+  if (dfw_umma_enabled())
     par_rc = dfw_chunk_bwd_par_umma(go, q, k, delta, Sc, Rc, Ec, dq, dk, B, T_,
                                     std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16, st);
   if (par_rc != T2FW_OK && par_rc != T2FW_ERR_UNSUPPORTED) return par_rc;
