@@ -28,7 +28,7 @@ using namespace chunk;
 int lfw_chunk_status_ptr(int **out);   // lfw_chunk_local_umma.cu
 
 #ifdef T2FW_DFW_PROFILE
-__device__ long long g_dfw_prof[32];
+__device__ long long g_dfw_prof[48];
 #define PROF(i)                                                    \
   do {                                                             \
     if (threadIdx.x == 0 && blockIdx.x == 0) {                     \
@@ -45,9 +45,18 @@ __device__ long long g_dfw_prof[32];
       tprev = now_;                                                \
     }                                                              \
   } while (0)
+#define PROFP(i)                                                   \
+  do {                                                             \
+    if (threadIdx.x == 0 && blockIdx.x == 0) {                     \
+      const long long now_ = clock64();                            \
+      g_dfw_prof[32 + i] += now_ - tprev;                          \
+      tprev = now_;                                                \
+    }                                                              \
+  } while (0)
 #else
 #define PROF(i)
 #define PROFB(i)
+#define PROFP(i)
 #endif
 
 namespace {
@@ -619,8 +628,8 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
   if (warp == 0) umma::tmem_alloc(&tmem_slot, 128);
 
   // The inputs of a chunk travel global -> registers -> TF32 tiles in two steps, so that the loads of
-  // the next chunk are in flight during the first round of products and land in the tiles as soon as
-  // the products that read them have finished.
+  // the next chunk are in flight during the products and land in the tiles as soon as the products
+  // that read them have finished.
   float4 rd[4], re[4], rs[4], rr[4];
   uint2 rg[4], rq[4], rk[4];
   auto chunk_base = [&](int64_t ci) { return ((size_t)(ci / nc) * T_ + (ci % nc) * kC) * kDim; };
@@ -628,37 +637,52 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
     const int64_t t0 = (ci % nc) * kC;
     return (int)((T_ - t0 < kC) ? T_ - t0 : kC);
   };
-  auto load = [&](int64_t ci) {
+  // group A (issued under the first round of products): Dl, E, dO;  group B (under the second): S0^T,
+  // R_end^T, q, k.  Two bursts of ~44 KB per SM keep the memory system busy more evenly than one.
+  auto load_a = [&](int64_t ci) {
     const size_t base = chunk_base(ci), tile = (size_t)ci * kC * kDim;
     const int nv = chunk_valid(ci);
-    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    const uint2 z2 = make_uint2(0u, 0u);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int p = tid + kTh * j, r = p >> 4, c4 = (p & 15) * 4;       // 16 lanes per row
       const bool in = r < nv;
-      rd[j] = in ? *reinterpret_cast<const float4 *>(delta + base + (size_t)r * kDim + c4) : z4;
-      rg[j] = in ? *reinterpret_cast<const uint2 *>(go + base + (size_t)r * kDim + c4) : z2;
+      rd[j] = in ? *reinterpret_cast<const float4 *>(delta + base + (size_t)r * kDim + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      rg[j] = in ? *reinterpret_cast<const uint2 *>(go + base + (size_t)r * kDim + c4) : make_uint2(0u, 0u);
       re[j] = *reinterpret_cast<const float4 *>(Ec + tile + r * kDim + c4);
+    }
+  };
+  auto load_b = [&](int64_t ci) {
+    const size_t base = chunk_base(ci), tile = (size_t)ci * kC * kDim;
+    const int nv = chunk_valid(ci);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int p = tid + kTh * j, r = p >> 4, c4 = (p & 15) * 4;
       rs[j] = *reinterpret_cast<const float4 *>(ScT + tile + r * kDim + c4);
       rr[j] = *reinterpret_cast<const float4 *>(RcT + tile + r * kDim + c4);
       const int combo = warp * 4 + j, rt_ = 4 * (combo >> 1) + (lane >> 3), ct = 4 * (8 * (combo & 1) + (lane & 7));
       const bool in2 = rt_ < nv;                                         // 8 column pieces x 4 steps per warp
-      rq[j] = in2 ? *reinterpret_cast<const uint2 *>(q + base + (size_t)rt_ * kDim + ct) : z2;
-      rk[j] = in2 ? *reinterpret_cast<const uint2 *>(k + base + (size_t)rt_ * kDim + ct) : z2;
+      rq[j] = in2 ? *reinterpret_cast<const uint2 *>(q + base + (size_t)rt_ * kDim + ct) : make_uint2(0u, 0u);
+      rk[j] = in2 ? *reinterpret_cast<const uint2 *>(k + base + (size_t)rt_ * kDim + ct) : make_uint2(0u, 0u);
     }
   };
-  auto store_direct = [&]() {     // Dl, -E, S0^T, R_end^T, dO: read by the first round only
+  auto store_a = [&]() {          // Dl, -E, dO: read by the first round only
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int p = tid + kTh * j, r = p >> 4, c4 = (p & 15) * 4;
       const int o = umma::tile_off(r, c4, kDim);
       *reinterpret_cast<float4 *>(sm + oPD + o) = make_float4(rt(rd[j].x), rt(rd[j].y), rt(rd[j].z), rt(rd[j].w));
       *reinterpret_cast<float4 *>(sm + oPE + o) = make_float4(-rt(re[j].x), -rt(re[j].y), -rt(re[j].z), -rt(re[j].w));
-      *reinterpret_cast<float4 *>(sm + oPS + o) = make_float4(rt(rs[j].x), rt(rs[j].y), rt(rs[j].z), rt(rs[j].w));
-      *reinterpret_cast<float4 *>(sm + oPR + o) = make_float4(rt(rr[j].x), rt(rr[j].y), rt(rr[j].z), rt(rr[j].w));
       const float2 g0 = Pair<T>::ld(reinterpret_cast<const T *>(&rg[j].x)), g1 = Pair<T>::ld(reinterpret_cast<const T *>(&rg[j].y));
       *reinterpret_cast<float4 *>(sm + oPG + o) = make_float4(g0.x, g0.y, g1.x, g1.y);
+    }
+  };
+  auto store_sr = [&]() {         // S0^T, R_end^T: read by the first round only
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int p = tid + kTh * j, r = p >> 4, c4 = (p & 15) * 4;
+      const int o = umma::tile_off(r, c4, kDim);
+      *reinterpret_cast<float4 *>(sm + oPS + o) = make_float4(rt(rs[j].x), rt(rs[j].y), rt(rs[j].z), rt(rs[j].w));
+      *reinterpret_cast<float4 *>(sm + oPR + o) = make_float4(rt(rr[j].x), rt(rr[j].y), rt(rr[j].z), rt(rr[j].w));
     }
   };
   auto store_trans = [&]() {      // Q^T, K^T: read by the second round only
@@ -690,15 +714,22 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
 
   int64_t ci = blockIdx.x, prev = -1;
   if (ci < total) {
-    load(ci);
-    store_direct();
+    load_a(ci);
+    load_b(ci);
+    store_a();
+    store_sr();
     store_trans();
   }
   uint32_t par = 0;
   uint32_t tb = 0, tl = 0;
+#ifdef T2FW_DFW_PROFILE
+  long long tprev = clock64();
+#endif
   for (; ci < total; ci += gridDim.x) {
+    PROFP(0);
     umma::fence_async_smem();
     sync_all();                   // tiles complete; staging rows of the chunk before complete
+    PROFP(1);
     tb = tmem_slot;
     tl = umma::tmem_addr(tb, 32 * qd, 0);
     if (s_fail) break;
@@ -720,10 +751,13 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
     }
     const int64_t next = ci + gridDim.x;
     const bool has_next = next < total;
-    if (has_next) load(next);
+    PROFP(2);
+    if (has_next) load_a(next);
     if (prev >= 0) copy_out(prev);
+    PROFP(3);
     if (!umma::mbar_wait(&bar_m1, par)) s_fail = 1;
     umma::fence_after_sync();
+    PROFP(4);
     {
       // lane set B: dO Dl^T (row t, columns i) -> X1 and X1^T;  lane set A: -X2 (row t, columns i) -> -Y
       float v[32];
@@ -741,19 +775,18 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
+          // two independent predicated stores (an if / else-if chain compiles to divergent branches)
           const int i = c0 + j;
-          const float y = rt(v[j]);
-          if (i > row) {
-            *reinterpret_cast<float *>(sm + oPY + umma::tile_off(row, i, kC)) = y;
-            *reinterpret_cast<float *>(sm + oPY + umma::tile_off(i, row, kC)) = y;
-          } else if (i == row) {
-            *reinterpret_cast<float *>(sm + oPY + umma::tile_off(row, i, kC)) = 0.f;
-          }
+          const float y = (i == row) ? 0.f : rt(v[j]);
+          if (i >= row) *reinterpret_cast<float *>(sm + oPY + umma::tile_off(row, i, kC)) = y;
+          if (i > row) *reinterpret_cast<float *>(sm + oPY + umma::tile_off(i, row, kC)) = y;
         }
       }
     }
+    PROFP(5);
     umma::fence_async_smem();
     sync_all();
+    PROFP(6);
     // ---- second round --------------------------------------------------------------------------------
     if (lane == 0 && warp < 2) {
       const uint32_t idesc = umma::make_idesc_tf32(kDim, kDim, false, false);
@@ -774,9 +807,15 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
       }
       umma::mma_commit(&bar_m2);
     }
-    if (has_next) store_direct();     // the first round has finished with these tiles
+    PROFP(7);
+    if (has_next) {                   // the first round has finished with these tiles
+      store_a();
+      load_b(next);
+    }
+    PROFP(8);
     if (!s_fail && !umma::mbar_wait(&bar_m2, par)) s_fail = 1;
     umma::fence_after_sync();
+    PROFP(9);
     {
       // lane set A: d_key, lane set B: d_query (row t, columns m) -> padded 16-bit staging rows
       float v[32];
@@ -791,7 +830,12 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
       for (int j = 0; j < 4; ++j)
         *reinterpret_cast<uint4 *>(stg + 16 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
     }
-    if (has_next) store_trans();      // the second round has finished with these tiles
+    PROFP(10);
+    if (has_next) {                   // both rounds have finished with the tiles
+      store_sr();
+      store_trans();
+    }
+    PROFP(11);
     prev = ci;
     par ^= 1u;
     umma::fence_before_sync();
@@ -892,6 +936,6 @@ int dfw_chunk_bwd_par_umma(const void *go, const void *q, const void *k, const v
 
 #ifdef T2FW_DFW_PROFILE
 extern "C" int t2fw_debug_dfw_prof(long long *out) {
-  return (int)cudaMemcpyFromSymbol(out, t2fw::g_dfw_prof, sizeof(long long) * 32);
+  return (int)cudaMemcpyFromSymbol(out, t2fw::g_dfw_prof, sizeof(long long) * 48);
 }
 #endif
