@@ -35,6 +35,16 @@ def test_library_exports_every_declared_symbol():
     assert set(declared_functions()) >= set(_lib.EXPORTS)
 
 
+def test_library_is_not_an_instrumented_build():
+    """The clock-counter instrumentation of the kernels (compile-time macros) exports debug entry
+    points; a library built that way is slower and must not be the one that ships."""
+    from t2fw_b200 import _lib
+
+    lib = ctypes.CDLL(_lib.CORE_PATH)
+    for name in ("t2fw_debug_prof", "t2fw_debug_dfw_prof"):
+        assert not hasattr(lib, name), name + ": rebuild without the profiling macro"
+
+
 def test_cheap_entry_points_run_without_gpu():
     from t2fw_b200 import _lib
 
