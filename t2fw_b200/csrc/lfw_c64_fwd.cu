@@ -1,0 +1,274 @@
+// Outputs of the chunked decay-rule forward on the tcgen05 tensor core (D = K = 64, 16-bit
+// storage, chunks of 64 steps): the third phase after the chunk-local states and the carry over
+// chunks.  Replaces the reference's materialised states and output einsum
+// (t2fw/csrc/lfw_kernel.cu:43-57, t2fw/csrc/lfw.cpp:45).
+//
+// Per chunk, with S0 the state at the chunk start (notation of lfw_c64.cuh):
+//     P   = tril( (q pm_g) (k / pm_g)^T )                       in-chunk decays, k side
+//     O^  = (q G_t) (A_REF .* S0)^T  +  P (x / pm_a)            [t][d]
+//     o_t = pm_a[t] .* O^_t
+// i.e. three 64 x 64 x 64 contractions, all on TF32 operand tiles in shared memory with fp32
+// accumulators in tensor memory.
+//
+// One persistent CTA of 16 warps per SM.  The five raw 8 KB input blocks of a chunk arrive by bulk
+// asynchronous copies into one of two buffers (the next chunk is fetched while this one is
+// computed); thread (gate side, 16-step quarter, feature) walks its steps with a running gate
+// product and writes the operand tiles; two elected threads issue the MMAs; the accumulators come
+// back time-major (a thread owns one step and eight features), so the 16-bit outputs leave as
+// 16-byte stores.
+#include <type_traits>
+
+#include "lfw_c64.cuh"
+
+namespace t2fw {
+
+using namespace c64;
+
+int lfw_chunk_status_ptr(int **out);   // lfw_chunk_local_umma.cu
+
+namespace {
+
+constexpr int kThreadsF = 512;
+constexpr int kPmLd = 68;                          // row stride (floats) of the pm_a table
+// shared-memory map
+constexpr int oT = 0;                              // tiles: 0 Qmid -> P, 1 Kmid, 2 Qstart, 3 Xmid (feature-major), 4 S0'
+constexpr int oPm = oT + 5 * kTile;                // pm_a[t][d]
+constexpr int oQt = oPm + kC * kPmLd * 4;          // quarter products [2 sides][4][64]
+constexpr int oRaw = oQt + 2 * 4 * kDim * 4;       // [2 buffers] x, f, q, k, fk
+constexpr int kSmemF = oRaw + 2 * 5 * kRawBytes + 1024;   // + slack for the 1024-byte alignment
+static_assert(oRaw % 128 == 0, "bulk-copy destination alignment");
+static_assert(kSmemF + 256 <= 227 * 1024, "shared memory limit");
+
+constexpr int cP = 0, cO = 32;                     // tensor-memory columns
+
+template <typename T>
+__global__ void __launch_bounds__(kThreadsF, 1)
+lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__restrict__ q,
+                   const T *__restrict__ k, const T *__restrict__ fk, const float *__restrict__ Sstart,
+                   T *__restrict__ out, int *__restrict__ rowflag, int *__restrict__ status, int64_t T_,
+                   int64_t nc, int64_t total) {
+  extern __shared__ __align__(1024) unsigned char sm_raw[];
+  unsigned char *sm = sm_raw + ((1024u - (umma::smem_u32(sm_raw) & 1023u)) & 1023u);   // swizzle atoms are 1024-byte aligned
+  __shared__ __align__(8) uint64_t barRaw[2], barP, barO;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_fail, s_bad;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // operand preparation: gate side (0: k side, 1: d side), quarter of the chunk, feature
+  const int gs = warp >> 3, tq = (warp >> 1) & 3, feat = (warp & 1) * 32 + lane;
+  // accumulator read-out: lane quarter, column part, column half (lane set), row in the quarter
+  const int q4 = warp & 3, part = warp >> 2, h = lane >> 4, fl = lane & 15;
+  // state tile: row d, eight columns
+  const int sr = tid & 63, sc0 = (tid >> 6) * 8;
+
+  float *pmT = reinterpret_cast<float *>(sm + oPm);
+  float *qtot = reinterpret_cast<float *>(sm + oQt);
+
+  auto issue_raw = [&](int64_t ci, int buf) {     // thread 0 only
+    const int64_t b = ci / nc, c = ci % nc, t0 = c * kC;
+    const int nv = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
+    const uint32_t vb = (uint32_t)nv * kDim * sizeof(T);
+    const size_t base = ((size_t)b * T_ + t0) * kDim;
+    unsigned char *r = sm + oRaw + buf * 5 * kRawBytes;
+    acp::mbar_expect_tx(&barRaw[buf], 5 * vb);
+    acp::bulk_g2s(r, x + base, vb, &barRaw[buf]);
+    acp::bulk_g2s(r + kRawBytes, f + base, vb, &barRaw[buf]);
+    acp::bulk_g2s(r + 2 * kRawBytes, q + base, vb, &barRaw[buf]);
+    acp::bulk_g2s(r + 3 * kRawBytes, k + base, vb, &barRaw[buf]);
+    acp::bulk_g2s(r + 4 * kRawBytes, fk + base, vb, &barRaw[buf]);
+  };
+
+  if (tid == 0) {
+    umma::mbar_init(&barRaw[0], 1);
+    umma::mbar_init(&barRaw[1], 1);
+    umma::mbar_init(&barP, 1);
+    umma::mbar_init(&barO, 1);
+    umma::mbar_fence_init();
+    s_fail = 0;
+  }
+  if (warp == 0) umma::tmem_alloc(&tmem_slot, 64);
+  sync_all();
+  const uint32_t tb = tmem_slot;
+  const uint32_t tl = umma::tmem_addr(tb, 32 * q4, 0);
+  uint32_t n_issued[2] = {0u, 0u}, n_landed[2] = {0u, 0u};      // thread 0: bulk-copy rounds per buffer
+  if (tid == 0 && (int64_t)blockIdx.x < total) {
+    issue_raw(blockIdx.x, 0);
+    ++n_issued[0];
+  }
+  const uint32_t aT = umma::smem_u32(sm + oT);
+
+  uint32_t it = 0;
+  for (int64_t ci = blockIdx.x; ci < total; ci += gridDim.x, ++it) {
+    const int buf = it & 1;
+    const int64_t b = ci / nc, c = ci % nc, t0c = c * kC;
+    const int nvalid = (int)((T_ - t0c < kC) ? T_ - t0c : kC);
+    const T *raw = reinterpret_cast<const T *>(sm + oRaw + buf * 5 * kRawBytes);
+
+    // start-of-chunk state: requested now, used after the operand tiles
+    const float4 *sp = reinterpret_cast<const float4 *>(Sstart + (size_t)ci * kDim * kDim + sr * kDim + sc0);
+    const float4 s_lo = sp[0], s_hi = sp[1];
+
+    if (tid == 0) {
+      s_bad = 0;
+      if (ci + gridDim.x < total) {      // the other buffer was released at the end of the previous chunk
+        issue_raw(ci + gridDim.x, buf ^ 1);
+        ++n_issued[buf ^ 1];
+      }
+    }
+    if (acp::mbar_wait(&barRaw[buf], (it >> 1) & 1u)) {
+      if (tid == 0) ++n_landed[buf];
+    } else {
+      s_fail = 1;
+    }
+    __syncthreads();
+    if (s_fail) break;
+
+    // ---- gate products of the four quarters ----
+    const T *r_gate = raw + (gs ? 1 : 4) * kC * kDim + feat;
+    float g[16];
+    qtot[(gs * 4 + tq) * kDim + feat] = load_gates16<T>(r_gate, tq, nvalid, g);
+    __syncthreads();
+
+    // ---- operand tiles ----
+    {
+      const float *qt = qtot + gs * 4 * kDim + feat;
+      const float carry = tq == 0 ? qt[kDim] : tq == 3 ? qt[2 * kDim] : 1.f;
+      bool ok;
+      if (gs == 0) {
+        const float g_ref = qt[0] * qt[kDim];
+        const T *r_q = raw + 2 * kC * kDim + feat, *r_k = raw + 3 * kC * kDim + feat;
+        unsigned char *tQ = sm + oT, *tK = sm + oT + kTile, *tQs = sm + oT + 2 * kTile;
+        ok = walk_quarter(tq, g, carry, [&](int, int t, float mf, float df) {
+          const bool in = t < nvalid;
+          const float qv = in ? Elem<T>::ld(r_q + t * kDim) : 0.f;
+          const float kv = in ? Elem<T>::ld(r_k + t * kDim) : 0.f;
+          const int o = toff(t, feat);
+          const float qm = qv * mf;
+          *reinterpret_cast<float *>(tQ + o) = rna_tf32(qm);
+          *reinterpret_cast<float *>(tK + o) = rna_tf32(kv * df);
+          *reinterpret_cast<float *>(tQs + o) = rna_tf32(qm * g_ref);
+        });
+      } else {
+        const T *r_x = raw + feat;
+        unsigned char *tX = sm + oT + 3 * kTile;
+        float xb[4];
+        ok = walk_quarter(tq, g, carry, [&](int j, int t, float mf, float df) {
+          const float xv = t < nvalid ? Elem<T>::ld(r_x + t * kDim) : 0.f;
+          pmT[t * kPmLd + feat] = mf;
+          xb[j & 3] = rna_tf32(xv * df);
+          if ((tq < 2 && (j & 3) == 0) || (tq >= 2 && (j & 3) == 3))
+            *reinterpret_cast<float4 *>(tX + toff(feat, t & ~3)) = make_float4(xb[0], xb[1], xb[2], xb[3]);
+        });
+      }
+      if (!ok) s_bad = 1;
+    }
+    // ---- state tile S0' = A_REF .* S0 ----
+    {
+      const float a_ref = qtot[4 * kDim + sr] * qtot[5 * kDim + sr];
+      unsigned char *tS = sm + oT + 4 * kTile;
+      *reinterpret_cast<float4 *>(tS + toff(sr, sc0)) =
+          make_float4(rna_tf32(s_lo.x * a_ref), rna_tf32(s_lo.y * a_ref), rna_tf32(s_lo.z * a_ref),
+                      rna_tf32(s_lo.w * a_ref));
+      *reinterpret_cast<float4 *>(tS + toff(sr, sc0 + 4)) =
+          make_float4(rna_tf32(s_hi.x * a_ref), rna_tf32(s_hi.y * a_ref), rna_tf32(s_hi.z * a_ref),
+                      rna_tf32(s_hi.w * a_ref));
+    }
+    umma::fence_async_smem();
+    sync_all();       // tiles complete, raw buffer consumed
+
+    if (tid == 0) {
+      if (s_bad) atomicExch(rowflag + b, 1);      // the scan kernel redoes this batch row
+      mma_64x64x64(tb, cP, aT, aT + kTile, false);                    // P = Qmid Kmid^T
+      umma::mma_commit(&barP);
+      mma_64x64x64(tb, cO, aT + 2 * kTile, aT + 4 * kTile, false);    // O^ = Qstart S0'^T
+    }
+    // ---- P: mask, round, store as the [t][s] operand (over Qmid, which only the P product reads) ----
+    if (!umma::mbar_wait(&barP, it & 1u)) s_fail = 1;
+    umma::fence_after_sync();
+    {
+      const int t = 16 * q4 + fl, s0 = 32 * h + 8 * part;
+      float v[8];
+      umma::tmem_ld8(tl + cP + 8 * part, v);
+      umma::tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (s0 + j <= t) ? rna_tf32(v[j]) : 0.f;
+      unsigned char *tP = sm + oT;
+      *reinterpret_cast<float4 *>(tP + toff(t, s0)) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4 *>(tP + toff(t, s0 + 4)) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    umma::fence_async_smem();
+    sync_all();
+    if (s_fail) break;
+    if (tid == 0) {
+      mma_64x64x64(tb, cO, aT, aT + 3 * kTile, true);                 // O^ += P Xmid
+      umma::mma_commit(&barO);
+    }
+    if (!umma::mbar_wait(&barO, it & 1u)) s_fail = 1;
+    umma::fence_after_sync();
+    {
+      const int t = 16 * q4 + fl, d0 = 32 * h + 8 * part;
+      float v[8];
+      umma::tmem_ld8(tl + cO + 8 * part, v);
+      const float4 p0 = *reinterpret_cast<const float4 *>(pmT + t * kPmLd + d0);
+      const float4 p1 = *reinterpret_cast<const float4 *>(pmT + t * kPmLd + d0 + 4);
+      umma::tmem_ld_wait();
+      if (t < nvalid) {
+        __align__(16) T o[8];
+        o[0] = (T)(v[0] * p0.x); o[1] = (T)(v[1] * p0.y); o[2] = (T)(v[2] * p0.z); o[3] = (T)(v[3] * p0.w);
+        o[4] = (T)(v[4] * p1.x); o[5] = (T)(v[5] * p1.y); o[6] = (T)(v[6] * p1.z); o[7] = (T)(v[7] * p1.w);
+        *reinterpret_cast<uint4 *>(out + ((size_t)b * T_ + t0c + t) * kDim + d0) = *reinterpret_cast<const uint4 *>(o);
+      }
+    }
+    sync_all();       // accumulators and tiles free for the next chunk
+    if (s_fail) break;
+  }
+  if (tid == 0) {
+    if (s_fail) atomicExch(status, 1);
+    // bounded: let copies that are still in flight land before the CTA leaves
+    for (int bb = 0; bb < 2; ++bb)
+      if (n_issued[bb] > n_landed[bb]) acp::mbar_wait(&barRaw[bb], n_landed[bb] & 1u);
+  }
+  sync_all();
+  if (warp == 0) umma::tmem_dealloc(tb, 64);
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+int g_sms_f[64] = {};
+
+}  // namespace
+
+// Returns T2FW_ERR_UNSUPPORTED (without launching) if a pointer is not 16-byte aligned.
+int lfw_c64_forward_out(const void *x, const void *f, const void *q, const void *k, const void *fk,
+                        const float *Sstart, void *out, int *rowflag, int64_t B, int64_t T_, int dtype,
+                        cudaStream_t st) {
+  if (!(aligned16(x) && aligned16(f) && aligned16(q) && aligned16(k) && aligned16(fk) && aligned16(Sstart) &&
+        aligned16(out)))
+    return T2FW_ERR_UNSUPPORTED;
+  int dev = 0;
+  T2FW_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return T2FW_ERR_UNSUPPORTED;
+  if (g_sms_f[dev] == 0) {
+    int n = 0;
+    T2FW_CHECK_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    g_sms_f[dev] = n;
+  }
+  int *status = nullptr;
+  int rc = lfw_chunk_status_ptr(&status);
+  if (rc != T2FW_OK) return rc;
+  const int64_t nc = ceil_div64(T_, kC), total = B * nc;
+  const unsigned grid = (unsigned)(total < g_sms_f[dev] ? total : g_sms_f[dev]);
+#define T2FW_LAUNCH(TT)                                                                              \
+  do {                                                                                               \
+    T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_c64_fwd_kernel<TT>,                                     \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemF));      \
+    lfw_c64_fwd_kernel<TT><<<grid, kThreadsF, kSmemF, st>>>(                                         \
+        (const TT *)x, (const TT *)f, (const TT *)q, (const TT *)k, (const TT *)fk, Sstart, (TT *)out, \
+        rowflag, status, T_, nc, total);                                                             \
+  } while (0)
+  if (dtype == T2FW_F16) T2FW_LAUNCH(__half); else T2FW_LAUNCH(__nv_bfloat16);
+#undef T2FW_LAUNCH
+  T2FW_CHECK_LAUNCH(1);
+  return T2FW_OK;
+}
+
+}  // namespace t2fw

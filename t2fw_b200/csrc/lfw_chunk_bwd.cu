@@ -42,7 +42,21 @@ int lfw_chunk_bwd_main_umma(const void *go, const void *x, const void *f, const 
                             void *dx, void *df, void *dq, void *dk, void *dfk, int *rowflag, int64_t B,
                             int64_t T_, int dtype, cudaStream_t st);
 
+// tcgen05 main kernel on 64-step chunks (lfw_c64_bwd.cu)
+int lfw_c64_backward_main(const void *go, const void *x, const void *f, const void *q, const void *k,
+                          const void *fk, const void *state, const void *ckpt, const float *Rend, void *dx,
+                          void *df, void *dq, void *dk, void *dfk, int *rowflag, int64_t B, int64_t T_,
+                          int dtype, cudaStream_t st);
+
 namespace {
+
+bool c64_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("T2FW_DISABLE_C64");
+    return !(e && e[0] == '1');
+  }();
+  return on && umma_enabled();
+}
 
 bool bwd_umma_enabled() {
   static const bool on = [] {
@@ -193,6 +207,11 @@ static int chunk_backward_typed(const void *go, const void *gs, const void *x, c
       (const T *)gs, s.G, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ds, B, nc);
   T2FW_CHECK_LAUNCH(1);
   const int dt = std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16;
+  if (c64_enabled()) {
+    const int rc = lfw_c64_backward_main(go, x, f, q, k, fk, state, ckpt, s.G, dx, df, dq, dk, dfk,
+                                         s.rowflag, B, T_, dt, st);
+    if (rc != T2FW_ERR_UNSUPPORTED) return rc;
+  }
   if (bwd_umma_enabled()) {
     const int rc = lfw_chunk_bwd_main_umma(go, x, f, q, k, fk, state, ckpt, s.G, dx, df, dq, dk, dfk,
                                            s.rowflag, B, T_, dt, st);

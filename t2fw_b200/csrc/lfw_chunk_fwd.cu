@@ -24,6 +24,17 @@ using namespace chunk;
 int lfw_chunk_output_persist(const void *x, const void *f, const void *q, const void *k, const void *fk,
                              const float *Sstart, void *out, int64_t B, int64_t T_, int dtype,
                              cudaStream_t st);
+// tcgen05 output phase on 64-step chunks (lfw_c64_fwd.cu)
+int lfw_c64_forward_out(const void *x, const void *f, const void *q, const void *k, const void *fk,
+                        const float *Sstart, void *out, int *rowflag, int64_t B, int64_t T_, int dtype,
+                        cudaStream_t st);
+static bool c64_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("T2FW_DISABLE_C64");
+    return !(e && e[0] == '1');
+  }();
+  return on && umma_enabled();
+}
 static bool persist_enabled() {
   const char *e = std::getenv("T2FW_DISABLE_PERSIST");
   return !(e && e[0] == '1');
@@ -301,7 +312,10 @@ static int chunk_forward_typed(const void *x, const void *f, const void *q, cons
       (const T *)state, s.L, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ckpt, B, nc);
   T2FW_CHECK_LAUNCH(1);
   int rc_out = T2FW_ERR_UNSUPPORTED;
-  if (persist_enabled())
+  if (c64_enabled())
+    rc_out = lfw_c64_forward_out(x, f, q, k, fk, s.L, out, s.rowflag, B, T_,
+                                 std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16, st);
+  if (rc_out == T2FW_ERR_UNSUPPORTED && persist_enabled())
     rc_out = lfw_chunk_output_persist(x, f, q, k, fk, s.L, out, B, T_,
                                       std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16, st);
   if (rc_out == T2FW_ERR_UNSUPPORTED) {
