@@ -3,6 +3,7 @@
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
+#include <initializer_list>
 
 #include "common.cuh"
 
@@ -114,6 +115,15 @@ size_t t2fw_dfw_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t 
   return scan;
 }
 
+// The tensor-core paths move data in 16-byte units (bulk copies, vector loads and stores).  A
+// pointer that is not 16-byte aligned (a view at an odd element offset) takes the scan kernels,
+// whose accesses are element-wise.
+static bool aligned16(std::initializer_list<const void *> ps) {
+  uintptr_t acc = 0;
+  for (const void *p : ps) acc |= reinterpret_cast<uintptr_t>(p);
+  return (acc & 15u) == 0;
+}
+
 static int check_common(int64_t B, int64_t T, int64_t D, int64_t K, int dtype) {
   T2FW_CHECK_ARG(dtype_size(dtype) != 0, "unknown dtype %d", dtype);
   T2FW_CHECK_ARG(B > 0 && T > 0 && D > 0 && K > 0, "sizes must be positive (B=%lld T=%lld D=%lld K=%lld)",
@@ -145,7 +155,7 @@ int t2fw_lfw_forward(const void *x, const void *f, const void *q, const void *k,
     }
   }
   const size_t need = t2fw_lfw_forward_scratch_bytes(B, T, D, K, dtype, ckpt_every);
-  if (need != 0) {
+  if (need != 0 && aligned16({x, f, q, k, f_key, state, outputs, ckpt_states, scratch})) {
     if (scratch == nullptr || scratch_bytes < need) {
       set_error("lfw forward needs %zu bytes of scratch, got %zu", need, scratch_bytes);
       return T2FW_ERR_SCRATCH;
@@ -179,7 +189,8 @@ int t2fw_lfw_backward(const void *grad_output, const void *grad_state, const voi
                  "null pointer argument");
   T2FW_CHECK_ARG(ckpt_every > 0, "ckpt_every must be positive");
   const size_t need = t2fw_lfw_backward_scratch_bytes(B, T, D, K, dtype, ckpt_every);
-  if (need != 0) {
+  if (need != 0 && aligned16({grad_output, grad_state, x, f, q, k, f_key, state, ckpt_states, d_x, d_f, d_q,
+                              d_k, d_f_key, d_state, scratch})) {
     if (scratch == nullptr || scratch_bytes < need) {
       set_error("lfw backward needs %zu bytes of scratch, got %zu", need, scratch_bytes);
       return T2FW_ERR_SCRATCH;
@@ -219,7 +230,7 @@ int t2fw_dfw_forward_ws(const void *q, const void *k, const void *v, const void 
   if (rc != T2FW_OK) return rc;
   T2FW_CHECK_ARG(q && k && v && state && outputs && final_state && delta, "null pointer argument");
   const size_t need = t2fw_dfw_forward_scratch_bytes(B, T, D, M, dtype);
-  if (need != 0) {
+  if (need != 0 && aligned16({q, k, v, state, outputs, final_state, delta, scratch})) {
     if (scratch == nullptr || scratch_bytes < need) {
       set_error("dfw forward needs %zu bytes of scratch, got %zu", need, scratch_bytes);
       return T2FW_ERR_SCRATCH;
@@ -249,7 +260,8 @@ int t2fw_dfw_backward(const void *grad_output, const void *grad_state, const voi
     }
     dv_acc = scratch;
   }
-  if (dfw_chunk_enabled() && dfw_chunk_supported(D, M, dtype))
+  if (dfw_chunk_enabled() && dfw_chunk_supported(D, M, dtype) &&
+      aligned16({grad_output, grad_state, q, k, delta, final_state, d_q, d_k, d_v, d_state, scratch}))
     return dfw_chunk_backward(grad_output, grad_state, q, k, delta, final_state, d_q, d_k, d_v, d_state,
                               B, T, dtype, scratch, static_cast<cudaStream_t>(stream));
   return dfw_scan_backward(grad_output, grad_state, q, k, delta, final_state, d_q, d_k, d_v,

@@ -61,24 +61,50 @@ __device__ __forceinline__ uint64_t desc_sw128(uint32_t addr) {
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
-// D[64 x 32] (+)= A[64 x 64] * B[rows n0 .. n0+31][64]^T over the 64 contraction columns (8 steps of 8)
-__device__ __forceinline__ void mma_64x32x64(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile, int n0,
-                                             bool accumulate) {
+// D[64 x 32] (+)= A[64 x 64] * B[rows n0 .. n0+31][64]^T over the 64 contraction columns (8 steps of 8).
+// da, db are the descriptors of the two tiles (desc_sw128 of the tile base); a k-step or a row
+// offset only moves the start-address field, which is the low word in units of 16 bytes.
+__device__ __forceinline__ void mma_64x32x64(uint32_t d_tmem, uint64_t da, uint64_t db, int n0, bool accumulate) {
   constexpr uint32_t idesc = umma::make_idesc_tf32(64, 32, false, false);
+  const uint64_t dbn = db + (uint64_t)(n0 * 128 >> 4);
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks) {
-    const uint32_t o = (uint32_t)((ks >> 2) * kColBlock + (ks & 3) * 32);
-    umma::mma_tf32(d_tmem, desc_sw128(a_tile + o), desc_sw128(b_tile + (uint32_t)n0 * 128u + o), idesc,
-                   accumulate || ks > 0);
+    const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
+    umma::mma_tf32(d_tmem, da + o, dbn + o, idesc, accumulate || ks > 0);
   }
 }
-// both 32-column halves of a 64 x 64 result: columns 0-31 into lanes 0-15 of every lane quarter,
-// columns 32-63 into lanes 16-31, both at tensor-memory column `col`
-__device__ __forceinline__ void mma_64x64x64(uint32_t tmem_base, int col, uint32_t a_tile, uint32_t b_tile,
-                                             bool accumulate) {
-  mma_64x32x64(umma::tmem_addr(tmem_base, 0, col), a_tile, b_tile, 0, accumulate);
-  mma_64x32x64(umma::tmem_addr(tmem_base, 16, col), a_tile, b_tile, 32, accumulate);
+
+// D[tmem] (+)= A[tmem] * B[smem]^T: the A operand is read from tensor memory (row r of an M = 64
+// operand in lane 32 * (r / 16) + r % 16 of a lane set, one 32-bit column per contraction index).
+__device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t desc_b, uint32_t idesc,
+                                            bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u, zero = 0u;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(desc_b), "r"(idesc), "r"(acc), "r"(zero)
+      : "memory");
 }
+
+// One lane of a converged warp.  The MMA-issuing code runs with the whole warp converged on
+// warp-uniform values (so the descriptors live in uniform registers) and only the instruction
+// itself is predicated on the elected lane.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+// warp index as a value the compiler knows to be the same in all lanes
+__device__ __forceinline__ int uniform_warp_idx() { return __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0); }
 
 __device__ __forceinline__ void sync_all() {
   umma::fence_before_sync();
@@ -86,35 +112,30 @@ __device__ __forceinline__ void sync_all() {
   umma::fence_after_sync();
 }
 
-// Gate products of one feature over one 16-step quarter of a chunk.
-//   g[j]   : sanitized gates of steps 16*tq + j (1 beyond the valid steps)
-//   returns the product of the quarter
+// ---- operand preparation, stage 1: ratios to the anchor ------------------------------------
+// Thread (feature, 16-step quarter tq).  g[j] = sanitized gate of step 16 * tq + j (the raw gate
+// blocks hold 1 beyond the valid steps); returns the product of the quarter.
 template <typename T>
-__device__ __forceinline__ float load_gates16(const T *gate_col, int tq, int nvalid, float (&g)[16]) {
+__device__ __forceinline__ float load_gates16(const T *gate_col, int tq, float (&g)[16]) {
   float p = 1.f;
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
-    const int t = 16 * tq + j;
-    g[j] = sanitize_gate(t < nvalid ? Elem<T>::ld(gate_col + t * kDim) : 1.f);
+    g[j] = sanitize_gate(Elem<T>::ld(gate_col + (16 * tq + j) * kDim));
     p *= g[j];
   }
   return p;
 }
 
-// Walks the 16 steps of quarter tq of one feature in the order in which the ratio to the anchor
-// is a running product (downwards from the anchor for tq < 2, upwards for tq >= 2) and calls
-//   fn(j, t, mulfac, divfac)      mulfac = pm[t] = G_t / G_REF,  divfac = 1 / pm[t]
-// with j the compile-time index into g[] (t = 16 * tq + j).  `carry` is the product of the
-// quarter between this one and the anchor (1 for the two inner quarters).
-// Returns false if a running product left [2^-100, 2^100] (or is not finite).
-template <typename F>
-__device__ __forceinline__ bool walk_quarter(int tq, const float (&g)[16], float carry, F &&fn) {
+// pm[j] = G_t / G_REF for t = 16 * tq + j: a running product downwards from the anchor for
+// tq < 2 (then inverted), upwards for tq >= 2.  `carry` is the product of the quarter between this
+// one and the anchor (1 for the two inner quarters).  Returns false if a running product left
+// [2^-100, 2^100] or is not finite.
+__device__ __forceinline__ bool ratios16(int tq, const float (&g)[16], float carry, float (&pm)[16]) {
   float s = carry, lo = fabsf(carry), hi = lo;
   if (tq < 2) {
 #pragma unroll
-    for (int jj = 0; jj < 16; ++jj) {
-      const int j = 15 - jj;
-      fn(j, 16 * tq + j, __fdividef(1.f, s), s);     // s = product of the gates after t, up to the anchor
+    for (int j = 15; j >= 0; --j) {
+      pm[j] = __fdividef(1.f, s);     // s = product of the gates after t, up to the anchor
       s *= g[j];
       lo = fminf(lo, fabsf(s));
       hi = fmaxf(hi, fabsf(s));
@@ -125,10 +146,61 @@ __device__ __forceinline__ bool walk_quarter(int tq, const float (&g)[16], float
       s *= g[j];
       lo = fminf(lo, fabsf(s));
       hi = fmaxf(hi, fabsf(s));
-      fn(j, 16 * tq + j, s, __fdividef(1.f, s));
+      pm[j] = s;
     }
   }
   return (lo >= kRangeLo) && (hi <= kRangeHi);     // false for NaN as well
+}
+
+// ---- stage 2: scaled operand tiles ------------------------------------------------------------
+template <typename T> struct Vec4;     // four consecutive 16-bit values -> four floats
+template <> struct Vec4<__half> {
+  static __device__ __forceinline__ float4 ld(const __half *p) {
+    const uint2 u = *reinterpret_cast<const uint2 *>(p);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 ld(const __nv_bfloat16 *p) {
+    const uint2 u = *reinterpret_cast<const uint2 *>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+};
+template <typename T> struct Vec2;     // two consecutive 16-bit values -> two floats
+template <> struct Vec2<__half> {
+  static __device__ __forceinline__ float2 ld(const __half *p) {
+    return __half22float2(*reinterpret_cast<const __half2 *>(p));
+  }
+};
+template <> struct Vec2<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 ld(const __nv_bfloat16 *p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p));
+  }
+};
+__device__ __forceinline__ float4 rna4(float4 v) {
+  return make_float4(rna_tf32(v.x), rna_tf32(v.y), rna_tf32(v.z), rna_tf32(v.w));
+}
+__device__ __forceinline__ float4 mul4(float4 a, float4 b) {
+  return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w);
+}
+__device__ __forceinline__ float4 rcp4(float4 a) {
+  return make_float4(__fdividef(1.f, a.x), __fdividef(1.f, a.y), __fdividef(1.f, a.z), __fdividef(1.f, a.w));
+}
+
+// A partial chunk (nvalid < 64): the steps beyond the valid ones become identity steps.  The raw
+// blocks are [nblk][64][64]; block i is a gate block if bit i of gate_mask is set.
+template <typename T>
+__device__ __forceinline__ void pad_raw_tail(T *raw, int nblk, unsigned gate_mask, int nvalid, int tid,
+                                             int nthreads) {
+  const int per = (kC - nvalid) * kDim;
+  for (int i = tid; i < nblk * per; i += nthreads) {
+    const int blk = i / per, o = i % per;
+    raw[blk * kC * kDim + nvalid * kDim + o] = (T)(((gate_mask >> blk) & 1u) ? 1.f : 0.f);
+  }
 }
 
 }  // namespace c64

@@ -27,7 +27,7 @@
 // One persistent CTA of 16 warps per SM; six raw 8 KB input blocks per chunk by bulk asynchronous
 // copy (the next chunk's are requested as soon as the second pass has consumed this chunk's);
 // operand tiles in shared memory (TF32, 128-byte swizzle), accumulators in tensor memory, MMAs
-// issued by three elected threads; the 16-bit results leave through staging tiles as bulk copies.
+// issued by four elected threads.
 #include <type_traits>
 
 #include "lfw_c64.cuh"
@@ -38,17 +38,32 @@ using namespace c64;
 
 int lfw_chunk_status_ptr(int **out);   // lfw_chunk_local_umma.cu
 
+#ifdef T2FW_C64_PROFILE
+__device__ long long g_c64_prof[32];
+#define PROF(i)                                                    \
+  do {                                                             \
+    if (threadIdx.x == 96 && blockIdx.x == 0) {                    \
+      const long long now_ = clock64();                            \
+      g_c64_prof[i] += now_ - tprev;                               \
+      tprev = now_;                                                \
+    }                                                              \
+  } while (0)
+#else
+#define PROF(i) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int kThreadsB = 512;
-constexpr int kPmLd = 68;              // row stride (floats) of the pm table
+constexpr int kPmLd = 68;              // row stride (floats) of the own-side ratio table
 constexpr int kFixCap = 128;           // tiny-gate entries per pass
 // shared-memory map (bytes from the 1024-byte aligned base)
-//   tiles: 0 Mo_mid -> Z[t][s]   1 Vo_mid -> Z^T[s][t]   2 Mo_start -> result staging   3 Vo_end
+//   tiles: 0 Mo_mid -> Z[t][s]   1 Vo_mid -> Z^T[s][t]   2 Mo_start   3 Vo_end
 //          4 Vw_mid [own][t]     5 Mw_mid [own][t]       6 S2 [own][other]              7 R2 [own][other]
 constexpr int oT = 0;
-constexpr int oPm = oT + 8 * kTile;                 // pm_w[own][t]
-constexpr int oQt = oPm + kDim * kPmLd * 4;         // quarter products [other, own][4][64]
+constexpr int oPm = oT + 8 * kTile;                 // pm_w[own][t]   (ratios of the own side)
+constexpr int oPmo = oPm + kDim * kPmLd * 4;        // pm_o[t][other] (ratios of the other side)
+constexpr int oQt = oPmo + kC * kDim * 4;           // quarter products [other, own][4][64]
 constexpr int oXc = oQt + 2 * 4 * kDim * 4;         // partial sums [3][8 ranges][64]
 constexpr int oBnd = oXc + 3 * 8 * kDim * 4;        // boundary-term partials [8][64]
 constexpr int oFixCode = oBnd + 8 * kDim * 4;       // [kFixCap] int
@@ -57,9 +72,7 @@ constexpr int oFixMask = oFixVal + kFixCap * 4;     // [64] one bit per step
 constexpr int oRaw = oFixMask + kDim * 8;           // x, f, q, k, fk, dO
 constexpr int kSmemB = oRaw + 6 * kRawBytes + 1024; // + slack for the 1024-byte alignment
 static_assert(oRaw % 128 == 0 && oFixMask % 8 == 0, "alignment");
-static_assert(kSmemB + 256 <= 227 * 1024, "shared memory limit");
-constexpr int oStg = oT + 2 * kTile;                // three [64][64] 16-bit staging tiles
-static_assert(3 * kRawBytes <= 2 * kTile, "staging fits the two dead tiles");
+static_assert(kSmemB + 128 <= 227 * 1024, "shared memory limit");
 
 constexpr int cZ = 0, cTQ1 = 32, cTQ2 = 64, cT2 = 96, cT7 = 128;   // tensor-memory columns
 constexpr int kTmemCols = 256;
@@ -78,8 +91,8 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
   __shared__ uint32_t tmem_slot;
   __shared__ int s_fail, s_bad, fix_n;
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // operand preparation: 0 = other side (time-major tiles), 1 = own side (feature-major tiles)
+  const int tid = threadIdx.x, warp = uniform_warp_idx(), lane = tid & 31;
+  // stage 1: 0 = other side, 1 = own side; 16-step quarter; feature
   const int gsw = warp >> 3, tq = (warp >> 1) & 3, feat = (warp & 1) * 32 + lane;
   // accumulator read-out: lane quarter, column part, lane set, row inside the quarter
   const int q4 = warp & 3, part = warp >> 2, h = lane >> 4, fl = lane & 15;
@@ -87,13 +100,14 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
   const int sr = tid & 63, sc0 = (tid >> 6) * 8;
 
   float *pmT = reinterpret_cast<float *>(sm + oPm);
+  float *pmo = reinterpret_cast<float *>(sm + oPmo);
   float *qtot = reinterpret_cast<float *>(sm + oQt);
   float *xc = reinterpret_cast<float *>(sm + oXc);
   float *bndp = reinterpret_cast<float *>(sm + oBnd);
   int *fix_code = reinterpret_cast<int *>(sm + oFixCode);
   float *fix_val = reinterpret_cast<float *>(sm + oFixVal);
   unsigned long long *fix_mask = reinterpret_cast<unsigned long long *>(sm + oFixMask);
-  const T *raw = reinterpret_cast<const T *>(sm + oRaw);     // [6][64][64]: x, f, q, k, fk, dO
+  T *raw = reinterpret_cast<T *>(sm + oRaw);     // [6][64][64]: x, f, q, k, fk, dO
 
   auto issue_raw = [&](int64_t ci) {     // thread 0 only
     const int64_t b = ci / nc, c = ci % nc, t0 = c * kC;
@@ -112,14 +126,14 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
 
   if (tid == 0) {
     umma::mbar_init(&barRaw, 1);
-    umma::mbar_init(&barZ, 1);
-    umma::mbar_init(&barM, 4);
+    umma::mbar_init(&barZ, 2);
+    umma::mbar_init(&barM, 6);
     umma::mbar_fence_init();
     s_fail = 0;
   }
   if (warp == 0) umma::tmem_alloc(&tmem_slot, kTmemCols);
   sync_all();
-  const uint32_t tb = tmem_slot;
+  const uint32_t tb = __shfl_sync(0xffffffffu, tmem_slot, 0);
   const uint32_t tl = umma::tmem_addr(tb, 32 * q4, 0);
   bool raw_pending = false;      // thread 0
   if (tid == 0 && (int64_t)blockIdx.x < total) {
@@ -127,12 +141,19 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
     raw_pending = true;
   }
   const uint32_t aT = umma::smem_u32(sm + oT);
+  uint64_t dT[8];      // descriptors of the eight tiles
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dT[i] = desc_sw128(aT + i * kTile);
   uint32_t pz = 0, pm_par = 0;   // mbarrier phase parities
 
+#ifdef T2FW_C64_PROFILE
+  long long tprev = clock64();
+#endif
   uint32_t it = 0;
   for (int64_t ci = blockIdx.x; ci < total; ci += gridDim.x, ++it) {
     const int64_t b = ci / nc, c = ci % nc, t0c = c * kC;
     const int nvalid = (int)((T_ - t0c < kC) ? T_ - t0c : kC);
+    PROF(0);
     const size_t base = ((size_t)b * T_ + t0c) * kDim;
     const T *s0p = (c == 0) ? state + (size_t)b * kDim * kDim : ckpt + ((size_t)b * nc + (c - 1)) * kDim * kDim;
     const float *rp = Rend + (size_t)ci * kDim * kDim;
@@ -141,100 +162,136 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
     if (tid == 0) raw_pending = false;
     __syncthreads();
     if (s_fail) break;
+    if (nvalid < kC) {      // partial chunk: identity steps beyond the valid ones
+      pad_raw_tail<T>(raw, 6, (1u << 1) | (1u << 4), nvalid, tid, kThreadsB);
+      __syncthreads();
+    }
+    PROF(1);
 
 #pragma unroll 1
     for (int ph = 0; ph < 2; ++ph) {
       // pass 0: own = k side (other = d side);  pass 1: own = d side
       const int blk_go = ph ? 4 : 1, blk_mo = ph ? 2 : 5, blk_vo = ph ? 3 : 0;   // other: gate, mul, div
       const int blk_gw = ph ? 1 : 4, blk_mw = ph ? 5 : 2, blk_vw = ph ? 0 : 3;   // own
-      // ---- start state and end gradient as S(own = sr, other = sc0 + j): requested now ----
-      float sv[8], rv[8];
+      // ---- start state and end gradient as S(own = sr, other = sc0 + j): requested now, converted
+      //      when they are used ----
+      unsigned short s16[8];     // pass 0: one 16-bit value per register (nothing depends on the loads yet)
+      uint4 s4 = make_uint4(0u, 0u, 0u, 0u);     // pass 1: eight packed values
+      float rv[8];
       if (ph == 0) {
+        const unsigned short *s0u = reinterpret_cast<const unsigned short *>(s0p);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          sv[j] = Elem<T>::ld(s0p + (sc0 + j) * kDim + sr);
+          s16[j] = s0u[(sc0 + j) * kDim + sr];
           rv[j] = rp[(sc0 + j) * kDim + sr];
         }
       } else {
-        const uint4 u = *reinterpret_cast<const uint4 *>(s0p + sr * kDim + sc0);
-        const T *e = reinterpret_cast<const T *>(&u);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) sv[j] = Elem<T>::ld(e + j);
+        for (int j = 0; j < 8; ++j) s16[j] = 0;
+        s4 = *reinterpret_cast<const uint4 *>(s0p + sr * kDim + sc0);
         const float4 r0 = *reinterpret_cast<const float4 *>(rp + sr * kDim + sc0);
         const float4 r1 = *reinterpret_cast<const float4 *>(rp + sr * kDim + sc0 + 4);
         rv[0] = r0.x; rv[1] = r0.y; rv[2] = r0.z; rv[3] = r0.w;
         rv[4] = r1.x; rv[5] = r1.y; rv[6] = r1.z; rv[7] = r1.w;
       }
 
-      // ---- gate products of the four quarters ----
+      // ---- stage 1: gate products of the four quarters, then the ratios to the anchor ----
       if (tid == 0) {
         s_bad = 0;
         fix_n = 0;
-        acp::bulk_wait_read<0>();        // the staging tiles of the previous pass have left
       }
       if (tid < kDim) fix_mask[tid] = 0ull;
       float g[16];
-      qtot[(gsw * 4 + tq) * kDim + feat] =
-          load_gates16<T>(raw + (gsw ? blk_gw : blk_go) * kC * kDim + feat, tq, nvalid, g);
+      qtot[(gsw * 4 + tq) * kDim + feat] = load_gates16<T>(raw + (gsw ? blk_gw : blk_go) * kC * kDim + feat, tq, g);
       __syncthreads();
-
-      // ---- operand tiles ----
+      PROF(2);
       {
         const float *qt = qtot + gsw * 4 * kDim + feat;
         const float carry = tq == 0 ? qt[kDim] : tq == 3 ? qt[2 * kDim] : 1.f;
-        bool ok;
+        float pm[16];
+        if (!ratios16(tq, g, carry, pm)) s_bad = 1;
         if (gsw == 0) {
-          const float o_ref = qt[0] * qt[kDim], oc_ref = qt[2 * kDim] * qt[3 * kDim];
-          const T *r_m = raw + blk_mo * kC * kDim + feat, *r_v = raw + blk_vo * kC * kDim + feat;
-          unsigned char *t0p = sm + oT, *t1p = t0p + kTile, *t2p = t0p + 2 * kTile, *t3p = t0p + 3 * kTile;
-          ok = walk_quarter(tq, g, carry, [&](int, int t, float mf, float dvf) {
-            const bool in = t < nvalid;
-            const float m = (in ? Elem<T>::ld(r_m + t * kDim) : 0.f) * mf;
-            const float v = (in ? Elem<T>::ld(r_v + t * kDim) : 0.f) * dvf;
-            const int o = toff(t, feat);
-            *reinterpret_cast<float *>(t0p + o) = rna_tf32(m);
-            *reinterpret_cast<float *>(t1p + o) = rna_tf32(v);
-            *reinterpret_cast<float *>(t2p + o) = rna_tf32(m * o_ref);
-            *reinterpret_cast<float *>(t3p + o) = rna_tf32(v * oc_ref);
-          });
+#pragma unroll
+          for (int j = 0; j < 16; ++j) pmo[(16 * tq + j) * kDim + feat] = pm[j];
         } else {
-          const T *r_m = raw + blk_mw * kC * kDim + feat, *r_v = raw + blk_vw * kC * kDim + feat;
-          unsigned char *t4p = sm + oT + 4 * kTile, *t5p = sm + oT + 5 * kTile;
-          float mb[4], vb[4], pb[4];
-          ok = walk_quarter(tq, g, carry, [&](int j, int t, float mf, float dvf) {
-            const bool in = t < nvalid;
-            mb[j & 3] = rna_tf32((in ? Elem<T>::ld(r_m + t * kDim) : 0.f) * mf);
-            vb[j & 3] = rna_tf32((in ? Elem<T>::ld(r_v + t * kDim) : 0.f) * dvf);
-            pb[j & 3] = mf;
-            if (in && fabsf(g[j]) < kTinyGate) {         // exact pair sum for this (step, feature) later
+#pragma unroll
+          for (int j = 0; j < 16; j += 4)
+            *reinterpret_cast<float4 *>(pmT + feat * kPmLd + 16 * tq + j) = make_float4(pm[j], pm[j + 1], pm[j + 2], pm[j + 3]);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (fabsf(g[j]) < kTinyGate && 16 * tq + j < nvalid) {   // exact pair sum for this (step, feature) later
               const int slot = atomicAdd(&fix_n, 1);
               if (slot < kFixCap) {
-                fix_code[slot] = (t << 8) | feat;
-                atomicOr(&fix_mask[feat], 1ull << t);
+                fix_code[slot] = ((16 * tq + j) << 8) | feat;
+                atomicOr(&fix_mask[feat], 1ull << (16 * tq + j));
               } else {
                 s_bad = 1;
               }
             }
-            if ((tq < 2 && (j & 3) == 0) || (tq >= 2 && (j & 3) == 3)) {
-              const int o = toff(feat, t & ~3);
-              *reinterpret_cast<float4 *>(t4p + o) = make_float4(vb[0], vb[1], vb[2], vb[3]);
-              *reinterpret_cast<float4 *>(t5p + o) = make_float4(mb[0], mb[1], mb[2], mb[3]);
-              *reinterpret_cast<float4 *>(pmT + feat * kPmLd + (t & ~3)) = make_float4(pb[0], pb[1], pb[2], pb[3]);
-            }
-          });
+          }
         }
-        if (!ok) s_bad = 1;
       }
+      __syncthreads();
+      PROF(3);
+
+      // ---- stage 2: operand tiles ----
+      {   // other side, time-major: this thread = four features, steps t and t + 32
+        const int f4 = (tid & 15) * 4;
+        const float4 o_ref = mul4(*reinterpret_cast<const float4 *>(qtot + f4),
+                                  *reinterpret_cast<const float4 *>(qtot + kDim + f4));
+        const float4 oc_ref = mul4(*reinterpret_cast<const float4 *>(qtot + 2 * kDim + f4),
+                                   *reinterpret_cast<const float4 *>(qtot + 3 * kDim + f4));
+        const T *r_m = raw + blk_mo * kC * kDim + f4, *r_v = raw + blk_vo * kC * kDim + f4;
+        unsigned char *t0p = sm + oT;
+#pragma unroll
+        for (int i2 = 0; i2 < 2; ++i2) {
+          const int t = (tid >> 4) + 32 * i2;
+          const float4 pv = *reinterpret_cast<const float4 *>(pmo + t * kDim + f4);
+          const float4 m = mul4(Vec4<T>::ld(r_m + t * kDim), pv);
+          const float4 v = mul4(Vec4<T>::ld(r_v + t * kDim), rcp4(pv));
+          const int o = toff(t, f4);
+          *reinterpret_cast<float4 *>(t0p + o) = rna4(m);
+          *reinterpret_cast<float4 *>(t0p + kTile + o) = rna4(v);
+          *reinterpret_cast<float4 *>(t0p + 2 * kTile + o) = rna4(mul4(m, o_ref));
+          *reinterpret_cast<float4 *>(t0p + 3 * kTile + o) = rna4(mul4(v, oc_ref));
+        }
+      }
+      {   // own side, feature-major: this thread = features 2 * lane, 2 * lane + 1, steps 4 * warp .. + 3
+        const int f0 = 2 * lane, t = 4 * warp;
+        const T *r_m = raw + blk_mw * kC * kDim + t * kDim + f0, *r_v = raw + blk_vw * kC * kDim + t * kDim + f0;
+        float2 m2[4], v2[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          m2[j] = Vec2<T>::ld(r_m + j * kDim);
+          v2[j] = Vec2<T>::ld(r_v + j * kDim);
+        }
+        const float4 p0 = *reinterpret_cast<const float4 *>(pmT + f0 * kPmLd + t);
+        const float4 p1 = *reinterpret_cast<const float4 *>(pmT + (f0 + 1) * kPmLd + t);
+        const float4 i0 = rcp4(p0), i1 = rcp4(p1);
+        unsigned char *t4p = sm + oT + 4 * kTile, *t5p = sm + oT + 5 * kTile;
+        const int o0 = toff(f0, t), o1 = toff(f0 + 1, t);
+        *reinterpret_cast<float4 *>(t5p + o0) = rna4(mul4(make_float4(m2[0].x, m2[1].x, m2[2].x, m2[3].x), p0));
+        *reinterpret_cast<float4 *>(t5p + o1) = rna4(mul4(make_float4(m2[0].y, m2[1].y, m2[2].y, m2[3].y), p1));
+        *reinterpret_cast<float4 *>(t4p + o0) = rna4(mul4(make_float4(v2[0].x, v2[1].x, v2[2].x, v2[3].x), i0));
+        *reinterpret_cast<float4 *>(t4p + o1) = rna4(mul4(make_float4(v2[0].y, v2[1].y, v2[2].y, v2[3].y), i1));
+      }
+      PROF(14);
       // ---- state tiles S2 = W_REF .* S0, R2 = W_63/W_REF .* R, boundary partial sums ----
       {
         const float w_ref = qtot[4 * kDim + sr] * qtot[5 * kDim + sr];
         const float wc_ref = qtot[6 * kDim + sr] * qtot[7 * kDim + sr];
         float s2[8], r2[8], acc = 0.f;
+        if (ph) {
+          s16[0] = (unsigned short)s4.x; s16[1] = (unsigned short)(s4.x >> 16);
+          s16[2] = (unsigned short)s4.y; s16[3] = (unsigned short)(s4.y >> 16);
+          s16[4] = (unsigned short)s4.z; s16[5] = (unsigned short)(s4.z >> 16);
+          s16[6] = (unsigned short)s4.w; s16[7] = (unsigned short)(s4.w >> 16);
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int o = sc0 + j;
           const float oc = (qtot[o] * qtot[kDim + o]) * (qtot[2 * kDim + o] * qtot[3 * kDim + o]);
-          s2[j] = rna_tf32(sv[j] * w_ref);
+          s2[j] = rna_tf32(Elem<T>::ld(reinterpret_cast<const T *>(&s16[j])) * w_ref);
           r2[j] = rna_tf32(rv[j] * wc_ref);
           acc = fmaf(oc * s2[j], r2[j], acc);
         }
@@ -246,29 +303,36 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
         *reinterpret_cast<float4 *>(t7p + o1) = make_float4(r2[4], r2[5], r2[6], r2[7]);
         bndp[(tid >> 6) * kDim + sr] = acc;
       }
+      PROF(4);
       umma::fence_async_smem();
       sync_all();       // tiles complete; in the second pass the raw blocks are consumed
+      PROF(5);
 
-      if (tid == 0) {
-        if (s_bad) atomicExch(rowflag + b, 1);      // the scan kernels redo this batch row
-        if (ph == 1 && ci + gridDim.x < total) {
-          issue_raw(ci + gridDim.x);
-          raw_pending = true;
+      // ---- first MMA round: one issuing thread per 32-column half ----
+      if (warp < 2) {
+        const uint32_t dh = umma::tmem_addr(tb, 16 * warp, 0);
+        if (elect_one()) {
+          mma_64x32x64(dh + cZ, dT[0], dT[1], 32 * warp, false);        // Z = Mo_mid Vo_mid^T
+          umma::mma_commit(&barZ);
+          mma_64x32x64(dh + cTQ1, dT[6], dT[2], 32 * warp, false);      // TQ1 = S2 Mo_start^T
+          mma_64x32x64(dh + cT7, dT[7], dT[3], 32 * warp, false);       // T7 = R2 Vo_end^T
+          umma::mma_commit(&barM);
         }
-        mma_64x64x64(tb, cZ, aT, aT + kTile, false);                       // Z = Mo_mid Vo_mid^T
-        umma::mma_commit(&barZ);
-      } else if (tid == 32) {
-        mma_64x64x64(tb, cTQ1, aT + 6 * kTile, aT + 2 * kTile, false);     // TQ1 = S2 Mo_start^T
-        umma::mma_commit(&barM);
-      } else if (tid == 64) {
-        mma_64x64x64(tb, cT7, aT + 7 * kTile, aT + 3 * kTile, false);      // T7 = R2 Vo_end^T
-        umma::mma_commit(&barM);
+        __syncwarp();
+        if (tid == 0) {
+          if (s_bad) atomicExch(rowflag + b, 1);      // the scan kernels redo this batch row
+          if (ph == 1 && ci + gridDim.x < total) {
+            issue_raw(ci + gridDim.x);
+            raw_pending = true;
+          }
+        }
       }
 
       // ---- Z: mask, round, store as [t][s] (tile 0) and [s][t] (tile 1) ----
       if (!umma::mbar_wait(&barZ, pz)) s_fail = 1;
       pz ^= 1u;
       umma::fence_after_sync();
+      PROF(6);
       {
         const int t = 16 * q4 + fl, s0 = 32 * h + 8 * part;
         float v[8];
@@ -282,16 +346,22 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
 #pragma unroll
         for (int j = 0; j < 8; ++j) *reinterpret_cast<float *>(t1p + toff(s0 + j, t)) = v[j];
       }
+      PROF(7);
       umma::fence_async_smem();
       sync_all();
       if (s_fail) break;
+      PROF(8);
 
-      if (tid == 0) {
-        mma_64x64x64(tb, cTQ2, aT + 4 * kTile, aT, false);                 // TQ2 = Vw_mid Z^T
-        umma::mma_commit(&barM);
-      } else if (tid == 32) {
-        mma_64x64x64(tb, cT2, aT + 5 * kTile, aT + kTile, false);          // T2 = Mw_mid Z
-        umma::mma_commit(&barM);
+      // ---- second MMA round: TQ2 = Vw_mid Z^T (warps 0, 1), T2 = Mw_mid Z (warps 2, 3) ----
+      if (warp < 4) {
+        const int hh = warp & 1;
+        const uint32_t dh = umma::tmem_addr(tb, 16 * hh, 0);
+        if (elect_one()) {
+          if (warp < 2) mma_64x32x64(dh + cTQ2, dT[4], dT[0], 32 * hh, false);
+          else mma_64x32x64(dh + cT2, dT[5], dT[1], 32 * hh, false);
+          umma::mma_commit(&barM);
+        }
+        __syncwarp();
       }
       // ---- tiny gates: pair terms i < t <= s summed directly (runs under the MMAs) ----
       {
@@ -299,32 +369,27 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
         const unsigned char *zt = sm + oT, *vw = sm + oT + 4 * kTile, *mw = sm + oT + 5 * kTile;
         for (int e = warp; e < n_fix; e += kThreadsB / 32) {
           const int code = fix_code[e], t = code >> 8, own = code & 0xff;
+          // sum_{s >= t} Mw[s] sum_{i < t} Z[s][i] Vw[i]: lanes over i, independent loads over s
           float acc = 0.f;
-#pragma unroll 1
-          for (int s = t + lane; s < kC; s += 32) {
-            float inner = 0.f;
-            for (int i = 0; i < t; ++i)
-              inner = fmaf(*reinterpret_cast<const float *>(zt + toff(s, i)),
-                           *reinterpret_cast<const float *>(vw + toff(own, i)), inner);
-            acc = fmaf(*reinterpret_cast<const float *>(mw + toff(own, s)), inner, acc);
+          for (int i = lane; i < t; i += 32) {
+            float a = 0.f;
+#pragma unroll 8
+            for (int s = t; s < kC; ++s)
+              a = fmaf(*reinterpret_cast<const float *>(mw + toff(own, s)),
+                       *reinterpret_cast<const float *>(zt + toff(s, i)), a);
+            acc = fmaf(a, *reinterpret_cast<const float *>(vw + toff(own, i)), acc);
           }
           acc = warp_sum(acc);
           if (lane == 0) fix_val[e] = acc;
         }
       }
+      PROF(9);
       __syncthreads();      // fix_val, bndp visible
+      PROF(10);
 
       // ---- feature-major epilogue: this thread = one own feature, 8 steps ----
-      if (!umma::mbar_wait(&barM, pm_par)) s_fail = 1;
-      pm_par ^= 1u;
-      umma::fence_after_sync();
       {
         const int own = 16 * q4 + fl, t0e = 32 * h + 8 * part, ridx = 4 * h + part;
-        float tq1[8], tq2[8], t2v[8], t7v[8];
-        umma::tmem_ld8(tl + cTQ1 + 8 * part, tq1);
-        umma::tmem_ld8(tl + cTQ2 + 8 * part, tq2);
-        umma::tmem_ld8(tl + cT2 + 8 * part, t2v);
-        umma::tmem_ld8(tl + cT7 + 8 * part, t7v);
         float mw[8], vw[8], pmv[9];
         {
           const unsigned char *t4p = sm + oT + 4 * kTile, *t5p = sm + oT + 5 * kTile;
@@ -344,15 +409,28 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
         float bnd = 0.f;
 #pragma unroll
         for (int r = 0; r < 8; ++r) bnd += bndp[r * kDim + own];
-        const unsigned long long mask = fix_mask[own];
-        umma::tmem_ld_wait();
-        float dmu[8], ddv[8], sa[8], sb[8], pre[8], gr[8];
+        const unsigned m8 = (unsigned)((fix_mask[own] >> t0e) & 0xffull);
+        float gr[8], ip[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float ip = __fdividef(1.f, pmv[j + 1]);
+          ip[j] = __fdividef(1.f, pmv[j + 1]);
+          gr[j] = pmv[j] * ip[j];                       // 1 / gate
+        }
+        if (!umma::mbar_wait(&barM, pm_par)) s_fail = 1;
+        pm_par ^= 1u;
+        umma::fence_after_sync();
+        PROF(11);
+        float tq1[8], tq2[8], t2v[8], t7v[8];
+        umma::tmem_ld8(tl + cTQ1 + 8 * part, tq1);
+        umma::tmem_ld8(tl + cTQ2 + 8 * part, tq2);
+        umma::tmem_ld8(tl + cT2 + 8 * part, t2v);
+        umma::tmem_ld8(tl + cT7 + 8 * part, t7v);
+        umma::tmem_ld_wait();
+        float dmu[8], ddv[8], sa[8], sb[8], pre[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
           dmu[j] = pmv[j + 1] * (tq1[j] + tq2[j]);
-          ddv[j] = (t2v[j] + t7v[j]) * ip;
-          gr[j] = pmv[j] * ip;                          // 1 / gate
+          ddv[j] = (t2v[j] + t7v[j]) * ip[j];
           sa[j] = mw[j] * tq1[j];
           sb[j] = mw[j] * tq2[j] - vw[j] * t2v[j];
           pre[j] = vw[j] * t7v[j];
@@ -375,43 +453,39 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
           addB += (r > ridx) ? vb2 : 0.f;
           addP += (r < ridx) ? vp : 0.f;        // earlier steps
         }
-        T *stg = reinterpret_cast<T *>(sm + oStg);
+        const float base_h = addA + addP + bnd;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sb[j] += addB;
+        if (m8) {        // some gate of this range is tiny: its pair terms were summed directly
+          const int n_fix = fix_n < kFixCap ? fix_n : kFixCap;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if ((m8 >> j) & 1u)
+              for (int e = 0; e < n_fix; ++e)
+                if (fix_code[e] == (((t0e + j) << 8) | own)) sb[j] = fix_val[e];
+        }
+        // 16 consecutive features of one step are 32 contiguous bytes: the results go straight out
+        T *o_mu = (ph ? nullptr : dq) , *o_dv = ph ? dx : dk, *o_gt = ph ? df : dfk;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int t = t0e + j;
-          float cross = sb[j] + addB;
-          if ((mask >> t) & 1ull) {
-            const int n_fix = fix_n < kFixCap ? fix_n : kFixCap;
-            for (int e = 0; e < n_fix; ++e)
-              if (fix_code[e] == ((t << 8) | own)) cross = fix_val[e];
+          const float H = sa[j] + sb[j] + pre[j] + base_h;
+          if (t < nvalid) {
+            const size_t o = base + (size_t)t * kDim + own;
+            if (ph == 0) o_mu[o] = (T)dmu[j];
+            o_dv[o] = (T)ddv[j];
+            o_gt[o] = (T)(H * gr[j]);
           }
-          const float H = (sa[j] + addA) + cross + (pre[j] + addP) + bnd;
-          if (ph == 0) stg[t * kDim + own] = (T)dmu[j];
-          stg[kC * kDim + t * kDim + own] = (T)ddv[j];
-          stg[2 * kC * kDim + t * kDim + own] = (T)(H * gr[j]);
         }
       }
-      umma::fence_async_smem();     // the staging tiles are read by the bulk-copy engine
+      PROF(12);
       sync_all();
       if (s_fail) break;
-      if (tid == 0) {
-        const uint32_t bytes = (uint32_t)nvalid * kDim * sizeof(T);
-        const T *stg = reinterpret_cast<const T *>(sm + oStg);
-        if (ph == 0) {
-          acp::bulk_s2g(dq + base, stg, bytes);
-          acp::bulk_s2g(dk + base, stg + kC * kDim, bytes);
-          acp::bulk_s2g(dfk + base, stg + 2 * kC * kDim, bytes);
-        } else {
-          acp::bulk_s2g(dx + base, stg + kC * kDim, bytes);
-          acp::bulk_s2g(df + base, stg + 2 * kC * kDim, bytes);
-        }
-        acp::bulk_commit();
-      }
+      PROF(13);
     }
     if (s_fail) break;
   }
   if (tid == 0) {
-    acp::bulk_wait_all();         // every result is in global memory
     if (s_fail) {
       atomicExch(status, 1);
       if (raw_pending) acp::mbar_wait(&barRaw, it & 1u);   // bounded: let the copies in flight land
@@ -464,3 +538,9 @@ int lfw_c64_backward_main(const void *go, const void *x, const void *f, const vo
 }
 
 }  // namespace t2fw
+
+#ifdef T2FW_C64_PROFILE
+extern "C" int t2fw_debug_c64_prof(long long *out) {
+  return (int)cudaMemcpyFromSymbol(out, t2fw::g_c64_prof, sizeof(long long) * 32);
+}
+#endif

@@ -13,7 +13,8 @@
 // One persistent CTA of 16 warps per SM.  The five raw 8 KB input blocks of a chunk arrive by bulk
 // asynchronous copies into one of two buffers (the next chunk is fetched while this one is
 // computed); thread (gate side, 16-step quarter, feature) walks its steps with a running gate
-// product and writes the operand tiles; two elected threads issue the MMAs; the accumulators come
+// product (stage 1: ratio tables), then the operand tiles are written element-wise with 16-byte
+// stores (stage 2); two elected threads issue the MMAs; the accumulators come
 // back time-major (a thread owns one step and eight features), so the 16-bit outputs leave as
 // 16-byte stores.
 #include <type_traits>
@@ -29,11 +30,13 @@ int lfw_chunk_status_ptr(int **out);   // lfw_chunk_local_umma.cu
 namespace {
 
 constexpr int kThreadsF = 512;
-constexpr int kPmLd = 68;                          // row stride (floats) of the pm_a table
-// shared-memory map
+constexpr int kPmLd = 68;                          // row stride (floats) of the padded ratio tables
+// shared-memory map (bytes from the 1024-byte aligned base)
 constexpr int oT = 0;                              // tiles: 0 Qmid -> P, 1 Kmid, 2 Qstart, 3 Xmid (feature-major), 4 S0'
-constexpr int oPm = oT + 5 * kTile;                // pm_a[t][d]
-constexpr int oQt = oPm + kC * kPmLd * 4;          // quarter products [2 sides][4][64]
+constexpr int oPmk = oT + 5 * kTile;               // pm_g[t][k]
+constexpr int oPmF = oPmk + kC * kDim * 4;         // pm_a[d][t]
+constexpr int oPmA = oPmF + kDim * kPmLd * 4;      // pm_a[t][d]
+constexpr int oQt = oPmA + kC * kPmLd * 4;         // quarter products [2 sides][4][64]
 constexpr int oRaw = oQt + 2 * 4 * kDim * 4;       // [2 buffers] x, f, q, k, fk
 constexpr int kSmemF = oRaw + 2 * 5 * kRawBytes + 1024;   // + slack for the 1024-byte alignment
 static_assert(oRaw % 128 == 0, "bulk-copy destination alignment");
@@ -53,15 +56,17 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
   __shared__ uint32_t tmem_slot;
   __shared__ int s_fail, s_bad;
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // operand preparation: gate side (0: k side, 1: d side), quarter of the chunk, feature
+  const int tid = threadIdx.x, warp = uniform_warp_idx(), lane = tid & 31;
+  // stage 1: gate side (0: k side, 1: d side), quarter of the chunk, feature
   const int gs = warp >> 3, tq = (warp >> 1) & 3, feat = (warp & 1) * 32 + lane;
   // accumulator read-out: lane quarter, column part, column half (lane set), row in the quarter
   const int q4 = warp & 3, part = warp >> 2, h = lane >> 4, fl = lane & 15;
   // state tile: row d, eight columns
   const int sr = tid & 63, sc0 = (tid >> 6) * 8;
 
-  float *pmT = reinterpret_cast<float *>(sm + oPm);
+  float *pmk = reinterpret_cast<float *>(sm + oPmk);
+  float *pmF = reinterpret_cast<float *>(sm + oPmF);
+  float *pmA = reinterpret_cast<float *>(sm + oPmA);
   float *qtot = reinterpret_cast<float *>(sm + oQt);
 
   auto issue_raw = [&](int64_t ci, int buf) {     // thread 0 only
@@ -81,14 +86,14 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
   if (tid == 0) {
     umma::mbar_init(&barRaw[0], 1);
     umma::mbar_init(&barRaw[1], 1);
-    umma::mbar_init(&barP, 1);
-    umma::mbar_init(&barO, 1);
+    umma::mbar_init(&barP, 2);
+    umma::mbar_init(&barO, 2);
     umma::mbar_fence_init();
     s_fail = 0;
   }
   if (warp == 0) umma::tmem_alloc(&tmem_slot, 64);
   sync_all();
-  const uint32_t tb = tmem_slot;
+  const uint32_t tb = __shfl_sync(0xffffffffu, tmem_slot, 0);
   const uint32_t tl = umma::tmem_addr(tb, 32 * q4, 0);
   uint32_t n_issued[2] = {0u, 0u}, n_landed[2] = {0u, 0u};      // thread 0: bulk-copy rounds per buffer
   if (tid == 0 && (int64_t)blockIdx.x < total) {
@@ -96,13 +101,15 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
     ++n_issued[0];
   }
   const uint32_t aT = umma::smem_u32(sm + oT);
+  const uint64_t dT0 = desc_sw128(aT), dT1 = desc_sw128(aT + kTile), dT2 = desc_sw128(aT + 2 * kTile);
+  const uint64_t dT3 = desc_sw128(aT + 3 * kTile), dT4 = desc_sw128(aT + 4 * kTile);
 
   uint32_t it = 0;
   for (int64_t ci = blockIdx.x; ci < total; ci += gridDim.x, ++it) {
     const int buf = it & 1;
     const int64_t b = ci / nc, c = ci % nc, t0c = c * kC;
     const int nvalid = (int)((T_ - t0c < kC) ? T_ - t0c : kC);
-    const T *raw = reinterpret_cast<const T *>(sm + oRaw + buf * 5 * kRawBytes);
+    T *raw = reinterpret_cast<T *>(sm + oRaw + buf * 5 * kRawBytes);
 
     // start-of-chunk state: requested now, used after the operand tiles
     const float4 *sp = reinterpret_cast<const float4 *>(Sstart + (size_t)ci * kDim * kDim + sr * kDim + sc0);
@@ -122,45 +129,63 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
     }
     __syncthreads();
     if (s_fail) break;
+    if (nvalid < kC) {      // partial chunk: identity steps beyond the valid ones
+      pad_raw_tail<T>(raw, 5, (1u << 1) | (1u << 4), nvalid, tid, kThreadsF);
+      __syncthreads();
+    }
 
-    // ---- gate products of the four quarters ----
-    const T *r_gate = raw + (gs ? 1 : 4) * kC * kDim + feat;
+    // ---- stage 1: gate products of the four quarters, then the ratios to the anchor ----
     float g[16];
-    qtot[(gs * 4 + tq) * kDim + feat] = load_gates16<T>(r_gate, tq, nvalid, g);
+    qtot[(gs * 4 + tq) * kDim + feat] = load_gates16<T>(raw + (gs ? 1 : 4) * kC * kDim + feat, tq, g);
     __syncthreads();
-
-    // ---- operand tiles ----
     {
       const float *qt = qtot + gs * 4 * kDim + feat;
       const float carry = tq == 0 ? qt[kDim] : tq == 3 ? qt[2 * kDim] : 1.f;
-      bool ok;
+      float pm[16];
+      if (!ratios16(tq, g, carry, pm)) s_bad = 1;
       if (gs == 0) {
-        const float g_ref = qt[0] * qt[kDim];
-        const T *r_q = raw + 2 * kC * kDim + feat, *r_k = raw + 3 * kC * kDim + feat;
-        unsigned char *tQ = sm + oT, *tK = sm + oT + kTile, *tQs = sm + oT + 2 * kTile;
-        ok = walk_quarter(tq, g, carry, [&](int, int t, float mf, float df) {
-          const bool in = t < nvalid;
-          const float qv = in ? Elem<T>::ld(r_q + t * kDim) : 0.f;
-          const float kv = in ? Elem<T>::ld(r_k + t * kDim) : 0.f;
-          const int o = toff(t, feat);
-          const float qm = qv * mf;
-          *reinterpret_cast<float *>(tQ + o) = rna_tf32(qm);
-          *reinterpret_cast<float *>(tK + o) = rna_tf32(kv * df);
-          *reinterpret_cast<float *>(tQs + o) = rna_tf32(qm * g_ref);
-        });
+#pragma unroll
+        for (int j = 0; j < 16; ++j) pmk[(16 * tq + j) * kDim + feat] = pm[j];
       } else {
-        const T *r_x = raw + feat;
-        unsigned char *tX = sm + oT + 3 * kTile;
-        float xb[4];
-        ok = walk_quarter(tq, g, carry, [&](int j, int t, float mf, float df) {
-          const float xv = t < nvalid ? Elem<T>::ld(r_x + t * kDim) : 0.f;
-          pmT[t * kPmLd + feat] = mf;
-          xb[j & 3] = rna_tf32(xv * df);
-          if ((tq < 2 && (j & 3) == 0) || (tq >= 2 && (j & 3) == 3))
-            *reinterpret_cast<float4 *>(tX + toff(feat, t & ~3)) = make_float4(xb[0], xb[1], xb[2], xb[3]);
-        });
+#pragma unroll
+        for (int j = 0; j < 16; ++j) pmA[(16 * tq + j) * kPmLd + feat] = pm[j];
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<float4 *>(pmF + feat * kPmLd + 16 * tq + j) = make_float4(pm[j], pm[j + 1], pm[j + 2], pm[j + 3]);
       }
-      if (!ok) s_bad = 1;
+    }
+    __syncthreads();
+
+    // ---- stage 2: operand tiles ----
+    {   // k side, time-major: this thread = four features, steps t and t + 32
+      const int f4 = (tid & 15) * 4;
+      const float4 g_ref = mul4(*reinterpret_cast<const float4 *>(qtot + f4),
+                                *reinterpret_cast<const float4 *>(qtot + kDim + f4));
+      const T *r_q = raw + 2 * kC * kDim + f4, *r_k = raw + 3 * kC * kDim + f4;
+      unsigned char *t0p = sm + oT;
+#pragma unroll
+      for (int i2 = 0; i2 < 2; ++i2) {
+        const int t = (tid >> 4) + 32 * i2;
+        const float4 pv = *reinterpret_cast<const float4 *>(pmk + t * kDim + f4);
+        const float4 qm = mul4(Vec4<T>::ld(r_q + t * kDim), pv);
+        const float4 km = mul4(Vec4<T>::ld(r_k + t * kDim), rcp4(pv));
+        const int o = toff(t, f4);
+        *reinterpret_cast<float4 *>(t0p + o) = rna4(qm);
+        *reinterpret_cast<float4 *>(t0p + kTile + o) = rna4(km);
+        *reinterpret_cast<float4 *>(t0p + 2 * kTile + o) = rna4(mul4(qm, g_ref));
+      }
+    }
+    {   // d side, feature-major: this thread = features 2 * lane, 2 * lane + 1, steps 4 * warp .. + 3
+      const int f0 = 2 * lane, t = 4 * warp;
+      const T *r_x = raw + t * kDim + f0;
+      float2 x2[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) x2[j] = Vec2<T>::ld(r_x + j * kDim);
+      const float4 i0 = rcp4(*reinterpret_cast<const float4 *>(pmF + f0 * kPmLd + t));
+      const float4 i1 = rcp4(*reinterpret_cast<const float4 *>(pmF + (f0 + 1) * kPmLd + t));
+      unsigned char *tX = sm + oT + 3 * kTile;
+      *reinterpret_cast<float4 *>(tX + toff(f0, t)) = rna4(mul4(make_float4(x2[0].x, x2[1].x, x2[2].x, x2[3].x), i0));
+      *reinterpret_cast<float4 *>(tX + toff(f0 + 1, t)) = rna4(mul4(make_float4(x2[0].y, x2[1].y, x2[2].y, x2[3].y), i1));
     }
     // ---- state tile S0' = A_REF .* S0 ----
     {
@@ -176,11 +201,15 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
     umma::fence_async_smem();
     sync_all();       // tiles complete, raw buffer consumed
 
-    if (tid == 0) {
-      if (s_bad) atomicExch(rowflag + b, 1);      // the scan kernel redoes this batch row
-      mma_64x64x64(tb, cP, aT, aT + kTile, false);                    // P = Qmid Kmid^T
-      umma::mma_commit(&barP);
-      mma_64x64x64(tb, cO, aT + 2 * kTile, aT + 4 * kTile, false);    // O^ = Qstart S0'^T
+    if (warp < 2) {     // one issuing thread per 32-column half
+      const uint32_t dh = umma::tmem_addr(tb, 16 * warp, 0);
+      if (elect_one()) {
+        mma_64x32x64(dh + cP, dT0, dT1, 32 * warp, false);      // P = Qmid Kmid^T
+        umma::mma_commit(&barP);
+        mma_64x32x64(dh + cO, dT2, dT4, 32 * warp, false);      // O^ = Qstart S0'^T
+      }
+      __syncwarp();
+      if (tid == 0 && s_bad) atomicExch(rowflag + b, 1);      // the scan kernel redoes this batch row
     }
     // ---- P: mask, round, store as the [t][s] operand (over Qmid, which only the P product reads) ----
     if (!umma::mbar_wait(&barP, it & 1u)) s_fail = 1;
@@ -199,18 +228,22 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
     umma::fence_async_smem();
     sync_all();
     if (s_fail) break;
-    if (tid == 0) {
-      mma_64x64x64(tb, cO, aT, aT + 3 * kTile, true);                 // O^ += P Xmid
-      umma::mma_commit(&barO);
+    if (warp < 2) {     // same lanes as above: O^ += P Xmid follows O^ = ... in issue order
+      const uint32_t dh = umma::tmem_addr(tb, 16 * warp, cO);
+      if (elect_one()) {
+        mma_64x32x64(dh, dT0, dT3, 32 * warp, true);
+        umma::mma_commit(&barO);
+      }
+      __syncwarp();
     }
-    if (!umma::mbar_wait(&barO, it & 1u)) s_fail = 1;
-    umma::fence_after_sync();
     {
       const int t = 16 * q4 + fl, d0 = 32 * h + 8 * part;
+      const float4 p0 = *reinterpret_cast<const float4 *>(pmA + t * kPmLd + d0);
+      const float4 p1 = *reinterpret_cast<const float4 *>(pmA + t * kPmLd + d0 + 4);
+      if (!umma::mbar_wait(&barO, it & 1u)) s_fail = 1;
+      umma::fence_after_sync();
       float v[8];
       umma::tmem_ld8(tl + cO + 8 * part, v);
-      const float4 p0 = *reinterpret_cast<const float4 *>(pmT + t * kPmLd + d0);
-      const float4 p1 = *reinterpret_cast<const float4 *>(pmT + t * kPmLd + d0 + 4);
       umma::tmem_ld_wait();
       if (t < nvalid) {
         __align__(16) T o[8];

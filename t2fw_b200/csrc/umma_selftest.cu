@@ -8,6 +8,7 @@
 // shared memory either as K-major or as MN-major core-matrix tiles, so that all four operand
 // orientations of the production kernels can be checked against a host matrix product.
 #include "common.cuh"
+#include "lfw_c64.cuh"
 #include "umma.cuh"
 
 namespace t2fw {
@@ -169,11 +170,96 @@ umma_selftest16_kernel(const float *__restrict__ A1, const float *__restrict__ B
   if (warp == 0) tmem_dealloc(tbase, 64);
 }
 
+// A operand from tensor memory: D[64 x 64] = A[64 x 64] * B[64 x 64]^T with A written into tensor
+// memory by tcgen05.st and B a 128-byte-swizzle tile in shared memory.  The tensor core reads row r
+// of A from the lane in which it produces row r of D, so A and D of one instruction share a lane
+// set: A is stored twice (lanes 0-15 and lanes 16-31 of every lane quarter) and each lane set
+// computes one 32-column half of D.
+__global__ void __launch_bounds__(128)
+umma_ts_selftest_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__restrict__ D,
+                        int *__restrict__ status) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char *tB = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_fail;
+  const int warp = c64::uniform_warp_idx(), lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 2);
+    mbar_fence_init();
+    s_fail = 0;
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 128);
+  for (int idx = threadIdx.x; idx < 64 * 64; idx += blockDim.x)
+    *reinterpret_cast<float *>(tB + c64::toff(idx / 64, idx % 64)) = B[idx];
+  fence_async_smem();
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tbase = __shfl_sync(0xffffffffu, tmem_slot, 0);
+  constexpr int cA = 32, cD = 0;
+  {   // A -> tensor memory: both lane sets of this warp's lane quarter hold rows 16 * warp .. + 15
+    const int row = 16 * warp + (lane & 15);
+    for (int c0 = 0; c0 < 64; c0 += 16) {
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = A[row * 64 + c0 + j];
+      tmem_st16(tmem_addr(tbase, 32 * warp, cA + c0), v);
+    }
+    tmem_st_wait();
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  if (warp < 2) {      // one issuing lane per 32-column half
+    const uint64_t db = c64::desc_sw128(smem_u32(tB)) + (uint64_t)(warp * 32 * 128 >> 4);
+    constexpr uint32_t idesc = make_idesc_tf32(64, 32, false, false);
+    const uint32_t d = tmem_addr(tbase, 16 * warp, cD), a0 = tmem_addr(tbase, 16 * warp, cA);
+    if (c64::elect_one()) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t o = (uint64_t)(((ks >> 2) * c64::kColBlock + (ks & 3) * 32) >> 4);
+        c64::mma_tf32_ts(d, a0 + 8 * ks, db + o, idesc, ks > 0);
+      }
+      mma_commit(&bar);
+    }
+    __syncwarp();
+  }
+  if (!mbar_wait(&bar, 0)) s_fail = 1;
+  __syncthreads();
+  fence_after_sync();
+  if (!s_fail) {
+    // every lane executes the warp-collective load; lanes 0-15 hold columns 0-31, lanes 16-31 columns 32-63
+    const int row = 16 * warp + (lane & 15), half = lane >> 4;
+    for (int c0 = 0; c0 < 32; c0 += 16) {
+      float v[16];
+      tmem_ld16(tmem_addr(tbase, 32 * warp, cD + c0), v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) D[row * 64 + 32 * half + c0 + j] = v[j];
+    }
+  } else if (threadIdx.x == 0) {
+    atomicExch(status, 1);
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 128);
+}
+
 }  // namespace
 
 }  // namespace t2fw
 
 using namespace t2fw;
+
+extern "C" int t2fw_selftest_umma_ts(const float *A, const float *B, float *D, int *status, void *stream) {
+  T2FW_CHECK_ARG(A && B && D && status, "null pointer argument");
+  const int smem = 64 * 64 * 4 + 1024;
+  T2FW_CHECK_CUDA(cudaFuncSetAttribute(umma_ts_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  umma_ts_selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(A, B, D, status);
+  T2FW_CHECK_LAUNCH(1);
+  return T2FW_OK;
+}
 
 extern "C" int t2fw_selftest_umma16(const float *A1, const float *B1, const float *A2, const float *B2,
                                     float *D1, float *D2, int N, int Kc, int a_mn, int b_mn,
