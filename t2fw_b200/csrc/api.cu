@@ -23,11 +23,6 @@ void set_error(const char *fmt, ...) {
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
-bool umma_enabled() {
-  const char *e = std::getenv("T2FW_DISABLE_UMMA");
-  return !(e && e[0] == '1');
-}
-
 }  // namespace t2fw
 
 using namespace t2fw;

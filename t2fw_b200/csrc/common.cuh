@@ -121,7 +121,6 @@ int lfw_chunk_local_umma(bool backward, const void *val_d, const void *gate_d, c
                          const void *gate_k, float *M, float *Ac, float *Gc, int *flags, int64_t B,
                          int64_t T, int dtype, cudaStream_t st);
 int lfw_chunk_umma_status();
-bool umma_enabled();
 bool lfw_decode_bulk_supported(int64_t B, int64_t D, int64_t K, int dtype);
 int lfw_decode_bulk_forward(const void *x, const void *f, const void *q, const void *k,
                             const void *fk, const void *state, void *out, void *new_state,

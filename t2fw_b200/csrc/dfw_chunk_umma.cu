@@ -25,7 +25,7 @@ namespace t2fw {
 
 using namespace chunk;
 
-int lfw_chunk_status_ptr(int **out);   // lfw_chunk_local_umma.cu
+int lfw_chunk_status_ptr(int **out);   // lfw_c64_local.cu
 
 #ifdef T2FW_DFW_PROFILE
 __device__ long long g_dfw_prof[48];

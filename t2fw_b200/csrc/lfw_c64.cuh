@@ -89,6 +89,52 @@ __device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, ui
       : "memory");
 }
 
+// D[64 x 32] (+)= A * B[rows n0 .. n0+31][64]^T with the 64 x 64 A operand in tensor memory (64 columns
+// starting at a_tmem, whose lane field selects the lane set that also receives D)
+__device__ __forceinline__ void mma_ts_64x32x64(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, int n0,
+                                                bool accumulate) {
+  constexpr uint32_t idesc = umma::make_idesc_tf32(64, 32, false, false);
+  const uint64_t dbn = db + (uint64_t)(n0 * 128 >> 4);
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
+    mma_tf32_ts(d_tmem, a_tmem + 8 * ks, dbn + o, idesc, accumulate || ks > 0);
+  }
+}
+
+__device__ __forceinline__ void tmem_st8(uint32_t addr, const float (&v)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n" ::"r"(addr),
+               "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+               "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+               "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7]))
+               : "memory");
+}
+
+// An A operand row block in tensor memory, stored twice.  The tensor core reads row r of A from
+// the lane in which it produces row r of D, and the two 32-column halves of every result live in
+// the two lane sets (lanes 0-15 / 16-31 of a lane quarter), so both lane sets need all 64 columns
+// of A.  Lane fl of the lower half warp holds columns 8 * part .. + 7 of row 16 * q4 + fl, lane
+// fl + 16 holds columns 32 + 8 * part .. + 7 of the same row; a tcgen05.st names ONE column range
+// for the whole warp, so the halves swap their values by shuffle and store twice.
+__device__ __forceinline__ void tmem_put_dup(uint32_t lane_base_col, int part, int h, const float (&v)[8]) {
+  float lo[8], hi[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float p = __shfl_xor_sync(0xffffffffu, v[j], 16);
+    lo[j] = h ? p : v[j];
+    hi[j] = h ? v[j] : p;
+  }
+  tmem_st8(lane_base_col + 8 * part, lo);
+  tmem_st8(lane_base_col + 32 + 8 * part, hi);
+}
+
+// 16-byte asynchronous copy global -> shared (no register, no scoreboard)
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(umma::smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // One lane of a converged warp.  The MMA-issuing code runs with the whole warp converged on
 // warp-uniform values (so the descriptors live in uniform registers) and only the instruction
 // itself is predicated on the elected lane.

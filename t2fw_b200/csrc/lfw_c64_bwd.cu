@@ -27,7 +27,7 @@
 // One persistent CTA of 16 warps per SM; six raw 8 KB input blocks per chunk by bulk asynchronous
 // copy (the next chunk's are requested as soon as the second pass has consumed this chunk's);
 // operand tiles in shared memory (TF32, 128-byte swizzle), accumulators in tensor memory, MMAs
-// issued by four elected threads.
+// issued by one elected lane.
 #include <type_traits>
 
 #include "lfw_c64.cuh"
@@ -36,7 +36,7 @@ namespace t2fw {
 
 using namespace c64;
 
-int lfw_chunk_status_ptr(int **out);   // lfw_chunk_local_umma.cu
+int lfw_chunk_status_ptr(int **out);   // lfw_c64_local.cu
 
 #ifdef T2FW_C64_PROFILE
 __device__ long long g_c64_prof[32];
@@ -57,11 +57,12 @@ namespace {
 constexpr int kThreadsB = 512;
 constexpr int kPmLd = 68;              // row stride (floats) of the own-side ratio table
 constexpr int kFixCap = 128;           // tiny-gate entries per pass
+constexpr int kS0Ld = 144;             // row stride (bytes) of the start-state landing zone (64 x 16-bit + pad)
+constexpr int kRLd = 272;              // row stride (bytes) of the end-gradient landing zone (64 x fp32 + pad)
 // shared-memory map (bytes from the 1024-byte aligned base)
-//   tiles: 0 Mo_mid -> Z[t][s]   1 Vo_mid -> Z^T[s][t]   2 Mo_start   3 Vo_end
-//          4 Vw_mid [own][t]     5 Mw_mid [own][t]       6 S2 [own][other]              7 R2 [own][other]
+//   tiles: 0 Mo_mid -> Z[t][s]   1 Vo_mid -> Z^T[s][t]   2 Mo_start   3 Vo_end     (B operands)
 constexpr int oT = 0;
-constexpr int oPm = oT + 8 * kTile;                 // pm_w[own][t]   (ratios of the own side)
+constexpr int oPm = oT + 4 * kTile;                 // pm_w[own][t]   (ratios of the own side)
 constexpr int oPmo = oPm + kDim * kPmLd * 4;        // pm_o[t][other] (ratios of the other side)
 constexpr int oQt = oPmo + kC * kDim * 4;           // quarter products [other, own][4][64]
 constexpr int oXc = oQt + 2 * 4 * kDim * 4;         // partial sums [3][8 ranges][64]
@@ -69,13 +70,18 @@ constexpr int oBnd = oXc + 3 * 8 * kDim * 4;        // boundary-term partials [8
 constexpr int oFixCode = oBnd + 8 * kDim * 4;       // [kFixCap] int
 constexpr int oFixVal = oFixCode + kFixCap * 4;     // [kFixCap] float
 constexpr int oFixMask = oFixVal + kFixCap * 4;     // [64] one bit per step
-constexpr int oRaw = oFixMask + kDim * 8;           // x, f, q, k, fk, dO
+constexpr int oFixRow = oFixMask + kDim * 8;        // [16 warps][2][64] floats: operand rows of a tiny-gate entry
+constexpr int oS0L = oFixRow + 16 * 2 * kDim * 4;   // start state of the chunk, [64][kS0Ld]
+constexpr int oRL = oS0L + kDim * kS0Ld;            // end state gradient of the chunk, [64][kRLd]
+constexpr int oRaw = oRL + kDim * kRLd;             // x, f, q, k, fk, dO
 constexpr int kSmemB = oRaw + 6 * kRawBytes + 1024; // + slack for the 1024-byte alignment
-static_assert(oRaw % 128 == 0 && oFixMask % 8 == 0, "alignment");
+static_assert(oRaw % 128 == 0 && oFixMask % 8 == 0 && oS0L % 16 == 0 && oRL % 16 == 0, "alignment");
 static_assert(kSmemB + 128 <= 227 * 1024, "shared memory limit");
 
-constexpr int cZ = 0, cTQ1 = 32, cTQ2 = 64, cT2 = 96, cT7 = 128;   // tensor-memory columns
-constexpr int kTmemCols = 256;
+// tensor-memory columns: the four A operands [own][64] (both lane sets), then the accumulators
+constexpr int cS2 = 0, cR2 = 64, cVw = 128, cMw = 192;
+constexpr int cZ = 256, cTQ1 = 288, cTQ2 = 320, cT2 = 352, cT7 = 384;
+constexpr int kTmemCols = 512;
 
 template <typename T>
 __global__ void __launch_bounds__(kThreadsB, 1)
@@ -94,10 +100,11 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
   const int tid = threadIdx.x, warp = uniform_warp_idx(), lane = tid & 31;
   // stage 1: 0 = other side, 1 = own side; 16-step quarter; feature
   const int gsw = warp >> 3, tq = (warp >> 1) & 3, feat = (warp & 1) * 32 + lane;
-  // accumulator read-out: lane quarter, column part, lane set, row inside the quarter
+  // tensor-memory rows: lane quarter, column part, lane set, row inside the quarter.  Thread
+  // (q4, part, h, fl) owns row 16 * q4 + fl and the eight columns 8 * (4 * h + part) .. + 7 of the
+  // own-side operands, of the state blocks and of every result.
   const int q4 = warp & 3, part = warp >> 2, h = lane >> 4, fl = lane & 15;
-  // state tiles: own row, eight other columns
-  const int sr = tid & 63, sc0 = (tid >> 6) * 8;
+  const int own = 16 * q4 + fl, cg = 4 * h + part, c0 = 8 * cg;
 
   float *pmT = reinterpret_cast<float *>(sm + oPm);
   float *pmo = reinterpret_cast<float *>(sm + oPmo);
@@ -107,6 +114,7 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
   int *fix_code = reinterpret_cast<int *>(sm + oFixCode);
   float *fix_val = reinterpret_cast<float *>(sm + oFixVal);
   unsigned long long *fix_mask = reinterpret_cast<unsigned long long *>(sm + oFixMask);
+  float *fix_row = reinterpret_cast<float *>(sm + oFixRow) + warp * 2 * kDim;
   T *raw = reinterpret_cast<T *>(sm + oRaw);     // [6][64][64]: x, f, q, k, fk, dO
 
   auto issue_raw = [&](int64_t ci) {     // thread 0 only
@@ -123,11 +131,25 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
     acp::bulk_g2s(r + 4 * kRawBytes, fk + base, vb, &barRaw);
     acp::bulk_g2s(r + 5 * kRawBytes, go + base, vb, &barRaw);
   };
+  // start state (16-bit, 8 KB) and end state gradient (fp32, 16 KB) of a chunk into the padded
+  // landing zones: three 16-byte asynchronous copies per thread
+  auto issue_state = [&](int64_t ci) {   // every thread
+    const int64_t b = ci / nc, c = ci % nc;
+    const T *s0p = (c == 0) ? state + (size_t)b * kDim * kDim : ckpt + ((size_t)b * nc + (c - 1)) * kDim * kDim;
+    const float *rp = Rend + (size_t)ci * kDim * kDim;
+    cp_async16(sm + oS0L + (tid >> 3) * kS0Ld + (tid & 7) * 16, s0p + (tid >> 3) * kDim + (tid & 7) * 8);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c16 = tid + i * kThreadsB;
+      cp_async16(sm + oRL + (c16 >> 4) * kRLd + (c16 & 15) * 16, rp + (c16 >> 4) * kDim + (c16 & 15) * 4);
+    }
+    cp_async_commit();
+  };
 
   if (tid == 0) {
     umma::mbar_init(&barRaw, 1);
-    umma::mbar_init(&barZ, 2);
-    umma::mbar_init(&barM, 6);
+    umma::mbar_init(&barZ, 1);
+    umma::mbar_init(&barM, 2);
     umma::mbar_fence_init();
     s_fail = 0;
   }
@@ -136,14 +158,17 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
   const uint32_t tb = __shfl_sync(0xffffffffu, tmem_slot, 0);
   const uint32_t tl = umma::tmem_addr(tb, 32 * q4, 0);
   bool raw_pending = false;      // thread 0
-  if (tid == 0 && (int64_t)blockIdx.x < total) {
-    issue_raw(blockIdx.x);
-    raw_pending = true;
+  if ((int64_t)blockIdx.x < total) {
+    if (tid == 0) {
+      issue_raw(blockIdx.x);
+      raw_pending = true;
+    }
+    issue_state(blockIdx.x);
   }
   const uint32_t aT = umma::smem_u32(sm + oT);
-  uint64_t dT[8];      // descriptors of the eight tiles
+  uint64_t dT[4];      // descriptors of the four tiles
 #pragma unroll
-  for (int i = 0; i < 8; ++i) dT[i] = desc_sw128(aT + i * kTile);
+  for (int i = 0; i < 4; ++i) dT[i] = desc_sw128(aT + i * kTile);
   uint32_t pz = 0, pm_par = 0;   // mbarrier phase parities
 
 #ifdef T2FW_C64_PROFILE
@@ -155,11 +180,10 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
     const int nvalid = (int)((T_ - t0c < kC) ? T_ - t0c : kC);
     PROF(0);
     const size_t base = ((size_t)b * T_ + t0c) * kDim;
-    const T *s0p = (c == 0) ? state + (size_t)b * kDim * kDim : ckpt + ((size_t)b * nc + (c - 1)) * kDim * kDim;
-    const float *rp = Rend + (size_t)ci * kDim * kDim;
 
     if (!acp::mbar_wait(&barRaw, it & 1u)) s_fail = 1;
     if (tid == 0) raw_pending = false;
+    cp_async_wait_all();       // this thread's share of the chunk's start state and end gradient
     __syncthreads();
     if (s_fail) break;
     if (nvalid < kC) {      // partial chunk: identity steps beyond the valid ones
@@ -173,27 +197,6 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
       // pass 0: own = k side (other = d side);  pass 1: own = d side
       const int blk_go = ph ? 4 : 1, blk_mo = ph ? 2 : 5, blk_vo = ph ? 3 : 0;   // other: gate, mul, div
       const int blk_gw = ph ? 1 : 4, blk_mw = ph ? 5 : 2, blk_vw = ph ? 0 : 3;   // own
-      // ---- start state and end gradient as S(own = sr, other = sc0 + j): requested now, converted
-      //      when they are used ----
-      unsigned short s16[8];     // pass 0: one 16-bit value per register (nothing depends on the loads yet)
-      uint4 s4 = make_uint4(0u, 0u, 0u, 0u);     // pass 1: eight packed values
-      float rv[8];
-      if (ph == 0) {
-        const unsigned short *s0u = reinterpret_cast<const unsigned short *>(s0p);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          s16[j] = s0u[(sc0 + j) * kDim + sr];
-          rv[j] = rp[(sc0 + j) * kDim + sr];
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) s16[j] = 0;
-        s4 = *reinterpret_cast<const uint4 *>(s0p + sr * kDim + sc0);
-        const float4 r0 = *reinterpret_cast<const float4 *>(rp + sr * kDim + sc0);
-        const float4 r1 = *reinterpret_cast<const float4 *>(rp + sr * kDim + sc0 + 4);
-        rv[0] = r0.x; rv[1] = r0.y; rv[2] = r0.z; rv[3] = r0.w;
-        rv[4] = r1.x; rv[5] = r1.y; rv[6] = r1.z; rv[7] = r1.w;
-      }
 
       // ---- stage 1: gate products of the four quarters, then the ratios to the anchor ----
       if (tid == 0) {
@@ -234,8 +237,8 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
       __syncthreads();
       PROF(3);
 
-      // ---- stage 2: operand tiles ----
-      {   // other side, time-major: this thread = four features, steps t and t + 32
+      // ---- stage 2: operands ----
+      {   // other side, time-major tiles in shared memory: this thread = four features, steps t and t + 32
         const int f4 = (tid & 15) * 4;
         const float4 o_ref = mul4(*reinterpret_cast<const float4 *>(qtot + f4),
                                   *reinterpret_cast<const float4 *>(qtot + kDim + f4));
@@ -256,77 +259,93 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
           *reinterpret_cast<float4 *>(t0p + 3 * kTile + o) = rna4(mul4(v, oc_ref));
         }
       }
-      {   // own side, feature-major: this thread = features 2 * lane, 2 * lane + 1, steps 4 * warp .. + 3
-        const int f0 = 2 * lane, t = 4 * warp;
-        const T *r_m = raw + blk_mw * kC * kDim + t * kDim + f0, *r_v = raw + blk_vw * kC * kDim + t * kDim + f0;
-        float2 m2[4], v2[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          m2[j] = Vec2<T>::ld(r_m + j * kDim);
-          v2[j] = Vec2<T>::ld(r_v + j * kDim);
-        }
-        const float4 p0 = *reinterpret_cast<const float4 *>(pmT + f0 * kPmLd + t);
-        const float4 p1 = *reinterpret_cast<const float4 *>(pmT + (f0 + 1) * kPmLd + t);
-        const float4 i0 = rcp4(p0), i1 = rcp4(p1);
-        unsigned char *t4p = sm + oT + 4 * kTile, *t5p = sm + oT + 5 * kTile;
-        const int o0 = toff(f0, t), o1 = toff(f0 + 1, t);
-        *reinterpret_cast<float4 *>(t5p + o0) = rna4(mul4(make_float4(m2[0].x, m2[1].x, m2[2].x, m2[3].x), p0));
-        *reinterpret_cast<float4 *>(t5p + o1) = rna4(mul4(make_float4(m2[0].y, m2[1].y, m2[2].y, m2[3].y), p1));
-        *reinterpret_cast<float4 *>(t4p + o0) = rna4(mul4(make_float4(v2[0].x, v2[1].x, v2[2].x, v2[3].x), i0));
-        *reinterpret_cast<float4 *>(t4p + o1) = rna4(mul4(make_float4(v2[0].y, v2[1].y, v2[2].y, v2[3].y), i1));
-      }
       PROF(14);
-      // ---- state tiles S2 = W_REF .* S0, R2 = W_63/W_REF .* R, boundary partial sums ----
-      {
-        const float w_ref = qtot[4 * kDim + sr] * qtot[5 * kDim + sr];
-        const float wc_ref = qtot[6 * kDim + sr] * qtot[7 * kDim + sr];
-        float s2[8], r2[8], acc = 0.f;
-        if (ph) {
-          s16[0] = (unsigned short)s4.x; s16[1] = (unsigned short)(s4.x >> 16);
-          s16[2] = (unsigned short)s4.y; s16[3] = (unsigned short)(s4.y >> 16);
-          s16[4] = (unsigned short)s4.z; s16[5] = (unsigned short)(s4.z >> 16);
-          s16[6] = (unsigned short)s4.w; s16[7] = (unsigned short)(s4.w >> 16);
-        }
+      {   // own side, feature-major A operands in tensor memory: row `own`, steps c0 .. c0 + 7
+        const T *r_m = raw + blk_mw * kC * kDim + c0 * kDim + own, *r_v = raw + blk_vw * kC * kDim + c0 * kDim + own;
+        const float4 p0 = *reinterpret_cast<const float4 *>(pmT + own * kPmLd + c0);
+        const float4 p1 = *reinterpret_cast<const float4 *>(pmT + own * kPmLd + c0 + 4);
+        const float pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+        float mw[8], vw[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const int o = sc0 + j;
+          mw[j] = rna_tf32(Elem<T>::ld(r_m + j * kDim) * pv[j]);
+          vw[j] = rna_tf32(Elem<T>::ld(r_v + j * kDim) * __fdividef(1.f, pv[j]));
+        }
+        tmem_put_dup(tl + cMw, part, h, mw);
+        tmem_put_dup(tl + cVw, part, h, vw);
+      }
+      // ---- state blocks S2 = W_REF .* S0, R2 = W_63/W_REF .* R as A operands, boundary partial sums ----
+      {
+        const float w_ref = qtot[4 * kDim + own] * qtot[5 * kDim + own];
+        const float wc_ref = qtot[6 * kDim + own] * qtot[7 * kDim + own];
+        float sv[8], rv[8];
+        if (ph == 0) {        // S(own = k, other = d = c0 + j): a column of the stored blocks
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            sv[j] = Elem<T>::ld(reinterpret_cast<const T *>(sm + oS0L + (c0 + j) * kS0Ld) + own);
+            rv[j] = *(reinterpret_cast<const float *>(sm + oRL + (c0 + j) * kRLd) + own);
+          }
+        } else {              // S(own = d, other = k = c0 + j): a row segment
+          const uint4 u = *reinterpret_cast<const uint4 *>(sm + oS0L + own * kS0Ld + c0 * 2);
+          const T *e = reinterpret_cast<const T *>(&u);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sv[j] = Elem<T>::ld(e + j);
+          const float4 r0 = *reinterpret_cast<const float4 *>(sm + oRL + own * kRLd + c0 * 4);
+          const float4 r1 = *reinterpret_cast<const float4 *>(sm + oRL + own * kRLd + c0 * 4 + 16);
+          rv[0] = r0.x; rv[1] = r0.y; rv[2] = r0.z; rv[3] = r0.w;
+          rv[4] = r1.x; rv[5] = r1.y; rv[6] = r1.z; rv[7] = r1.w;
+        }
+        float s2[8], r2[8], acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int o = c0 + j;
           const float oc = (qtot[o] * qtot[kDim + o]) * (qtot[2 * kDim + o] * qtot[3 * kDim + o]);
-          s2[j] = rna_tf32(Elem<T>::ld(reinterpret_cast<const T *>(&s16[j])) * w_ref);
+          s2[j] = rna_tf32(sv[j] * w_ref);
           r2[j] = rna_tf32(rv[j] * wc_ref);
           acc = fmaf(oc * s2[j], r2[j], acc);
         }
-        unsigned char *t6p = sm + oT + 6 * kTile, *t7p = sm + oT + 7 * kTile;
-        const int o0 = toff(sr, sc0), o1 = toff(sr, sc0 + 4);
-        *reinterpret_cast<float4 *>(t6p + o0) = make_float4(s2[0], s2[1], s2[2], s2[3]);
-        *reinterpret_cast<float4 *>(t6p + o1) = make_float4(s2[4], s2[5], s2[6], s2[7]);
-        *reinterpret_cast<float4 *>(t7p + o0) = make_float4(r2[0], r2[1], r2[2], r2[3]);
-        *reinterpret_cast<float4 *>(t7p + o1) = make_float4(r2[4], r2[5], r2[6], r2[7]);
-        bndp[(tid >> 6) * kDim + sr] = acc;
+        tmem_put_dup(tl + cS2, part, h, s2);
+        tmem_put_dup(tl + cR2, part, h, r2);
+        bndp[cg * kDim + own] = acc;
       }
+      umma::tmem_st_wait();
       PROF(4);
       umma::fence_async_smem();
-      sync_all();       // tiles complete; in the second pass the raw blocks are consumed
+      sync_all();       // operands complete; in the second pass the raw blocks and the state blocks are consumed
       PROF(5);
 
-      // ---- first MMA round: one issuing thread per 32-column half ----
-      if (warp < 2) {
-        const uint32_t dh = umma::tmem_addr(tb, 16 * warp, 0);
+      // ---- first MMA round.  A product is a chain of eight dependent instructions (one per 8
+      //      contraction columns, accumulating in place); the tensor core executes instructions in
+      //      issue order, so the six independent chains of this round are issued interleaved by ONE
+      //      lane and overlap in the pipeline instead of running one after the other. ----
+      if (warp == 0) {
+        const uint32_t d0 = tb, d1 = umma::tmem_addr(tb, 16, 0);
+        constexpr uint32_t idesc = umma::make_idesc_tf32(64, 32, false, false);
+        constexpr uint64_t n1 = (uint64_t)(32 * 128 >> 4);     // B rows 32..63
         if (elect_one()) {
-          mma_64x32x64(dh + cZ, dT[0], dT[1], 32 * warp, false);        // Z = Mo_mid Vo_mid^T
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
+            umma::mma_tf32(d0 + cZ, dT[0] + o, dT[1] + o, idesc, ks > 0);                 // Z = Mo_mid Vo_mid^T
+            umma::mma_tf32(d1 + cZ, dT[0] + o, dT[1] + n1 + o, idesc, ks > 0);
+            mma_tf32_ts(d0 + cTQ1, d0 + cS2 + 8 * ks, dT[2] + o, idesc, ks > 0);          // TQ1 = S2 Mo_start^T
+            mma_tf32_ts(d1 + cTQ1, d1 + cS2 + 8 * ks, dT[2] + n1 + o, idesc, ks > 0);
+            mma_tf32_ts(d0 + cT7, d0 + cR2 + 8 * ks, dT[3] + o, idesc, ks > 0);           // T7 = R2 Vo_end^T
+            mma_tf32_ts(d1 + cT7, d1 + cR2 + 8 * ks, dT[3] + n1 + o, idesc, ks > 0);
+          }
           umma::mma_commit(&barZ);
-          mma_64x32x64(dh + cTQ1, dT[6], dT[2], 32 * warp, false);      // TQ1 = S2 Mo_start^T
-          mma_64x32x64(dh + cT7, dT[7], dT[3], 32 * warp, false);       // T7 = R2 Vo_end^T
           umma::mma_commit(&barM);
         }
         __syncwarp();
-        if (tid == 0) {
-          if (s_bad) atomicExch(rowflag + b, 1);      // the scan kernels redo this batch row
-          if (ph == 1 && ci + gridDim.x < total) {
-            issue_raw(ci + gridDim.x);
-            raw_pending = true;
-          }
-        }
       }
+      if (ph == 1 && ci + gridDim.x < total) {      // the next chunk's inputs and state blocks
+        if (tid == 0) {
+          issue_raw(ci + gridDim.x);
+          raw_pending = true;
+        }
+        issue_state(ci + gridDim.x);
+      }
+      if (tid == 0 && s_bad) atomicExch(rowflag + b, 1);      // the scan kernels redo this batch row
 
       // ---- Z: mask, round, store as [t][s] (tile 0) and [s][t] (tile 1) ----
       if (!umma::mbar_wait(&barZ, pz)) s_fail = 1;
@@ -334,7 +353,7 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
       umma::fence_after_sync();
       PROF(6);
       {
-        const int t = 16 * q4 + fl, s0 = 32 * h + 8 * part;
+        const int t = own, s0 = 32 * h + 8 * part;
         float v[8];
         umma::tmem_ld8(tl + cZ + 8 * part, v);
         umma::tmem_ld_wait();
@@ -352,69 +371,99 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
       if (s_fail) break;
       PROF(8);
 
-      // ---- second MMA round: TQ2 = Vw_mid Z^T (warps 0, 1), T2 = Mw_mid Z (warps 2, 3) ----
-      if (warp < 4) {
-        const int hh = warp & 1;
-        const uint32_t dh = umma::tmem_addr(tb, 16 * hh, 0);
+      // ---- second MMA round: TQ2 = Vw_mid Z^T, T2 = Mw_mid Z, four interleaved chains ----
+      if (warp == 0) {
+        const uint32_t d0 = tb, d1 = umma::tmem_addr(tb, 16, 0);
+        constexpr uint32_t idesc = umma::make_idesc_tf32(64, 32, false, false);
+        constexpr uint64_t n1 = (uint64_t)(32 * 128 >> 4);
         if (elect_one()) {
-          if (warp < 2) mma_64x32x64(dh + cTQ2, dT[4], dT[0], 32 * hh, false);
-          else mma_64x32x64(dh + cT2, dT[5], dT[1], 32 * hh, false);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
+            mma_tf32_ts(d0 + cTQ2, d0 + cVw + 8 * ks, dT[0] + o, idesc, ks > 0);
+            mma_tf32_ts(d1 + cTQ2, d1 + cVw + 8 * ks, dT[0] + n1 + o, idesc, ks > 0);
+            mma_tf32_ts(d0 + cT2, d0 + cMw + 8 * ks, dT[1] + o, idesc, ks > 0);
+            mma_tf32_ts(d1 + cT2, d1 + cMw + 8 * ks, dT[1] + n1 + o, idesc, ks > 0);
+          }
           umma::mma_commit(&barM);
         }
         __syncwarp();
       }
-      // ---- tiny gates: pair terms i < t <= s summed directly (runs under the MMAs) ----
+      // ---- tiny gates: pair terms i < t <= s summed directly (runs under the MMAs).  The operand
+      //      rows of the entry's feature are in the tensor-memory lanes of one lane quarter, so a
+      //      warp of that quarter copies them to shared memory first. ----
       {
         const int n_fix = fix_n < kFixCap ? fix_n : kFixCap;
-        const unsigned char *zt = sm + oT, *vw = sm + oT + 4 * kTile, *mw = sm + oT + 5 * kTile;
-        for (int e = warp; e < n_fix; e += kThreadsB / 32) {
-          const int code = fix_code[e], t = code >> 8, own = code & 0xff;
+        const unsigned char *zt = sm + oT;
+        for (int e = 0; e < n_fix; ++e) {
+          const int code = fix_code[e], t = code >> 8, fo = code & 0xff;
+          if (warp != (fo >> 4) + 4 * (e & 3)) continue;      // warp-uniform
+#pragma unroll
+          for (int cc = 0; cc < kDim; cc += 16) {
+            float a[16], bq[16];
+            umma::tmem_ld16(tl + cMw + cc, a);
+            umma::tmem_ld16(tl + cVw + cc, bq);
+            umma::tmem_ld_wait();
+            if (lane == (fo & 15)) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                fix_row[cc + j] = a[j];
+                fix_row[kDim + cc + j] = bq[j];
+              }
+            }
+          }
+          __syncwarp();
           // sum_{s >= t} Mw[s] sum_{i < t} Z[s][i] Vw[i]: lanes over i, independent loads over s
           float acc = 0.f;
           for (int i = lane; i < t; i += 32) {
             float a = 0.f;
 #pragma unroll 8
-            for (int s = t; s < kC; ++s)
-              a = fmaf(*reinterpret_cast<const float *>(mw + toff(own, s)),
-                       *reinterpret_cast<const float *>(zt + toff(s, i)), a);
-            acc = fmaf(a, *reinterpret_cast<const float *>(vw + toff(own, i)), acc);
+            for (int s = t; s < kC; ++s) a = fmaf(fix_row[s], *reinterpret_cast<const float *>(zt + toff(s, i)), a);
+            acc = fmaf(a, fix_row[kDim + i], acc);
           }
           acc = warp_sum(acc);
           if (lane == 0) fix_val[e] = acc;
+          __syncwarp();
         }
       }
       PROF(9);
       __syncthreads();      // fix_val, bndp visible
       PROF(10);
 
-      // ---- feature-major epilogue: this thread = one own feature, 8 steps ----
+      // ---- feature-major epilogue: this thread = row `own`, steps c0 .. c0 + 7 ----
       {
-        const int own = 16 * q4 + fl, t0e = 32 * h + 8 * part, ridx = 4 * h + part;
-        float mw[8], vw[8], pmv[9];
+        float pmv[9];
         {
-          const unsigned char *t4p = sm + oT + 4 * kTile, *t5p = sm + oT + 5 * kTile;
-          const float4 a0 = *reinterpret_cast<const float4 *>(t5p + toff(own, t0e));
-          const float4 a1 = *reinterpret_cast<const float4 *>(t5p + toff(own, t0e + 4));
-          const float4 b0 = *reinterpret_cast<const float4 *>(t4p + toff(own, t0e));
-          const float4 b1 = *reinterpret_cast<const float4 *>(t4p + toff(own, t0e + 4));
-          mw[0] = a0.x; mw[1] = a0.y; mw[2] = a0.z; mw[3] = a0.w; mw[4] = a1.x; mw[5] = a1.y; mw[6] = a1.z; mw[7] = a1.w;
-          vw[0] = b0.x; vw[1] = b0.y; vw[2] = b0.z; vw[3] = b0.w; vw[4] = b1.x; vw[5] = b1.y; vw[6] = b1.z; vw[7] = b1.w;
-          const float4 p0 = *reinterpret_cast<const float4 *>(pmT + own * kPmLd + t0e);
-          const float4 p1 = *reinterpret_cast<const float4 *>(pmT + own * kPmLd + t0e + 4);
+          const float4 p0 = *reinterpret_cast<const float4 *>(pmT + own * kPmLd + c0);
+          const float4 p1 = *reinterpret_cast<const float4 *>(pmT + own * kPmLd + c0 + 4);
           pmv[1] = p0.x; pmv[2] = p0.y; pmv[3] = p0.z; pmv[4] = p0.w; pmv[5] = p1.x; pmv[6] = p1.y; pmv[7] = p1.z; pmv[8] = p1.w;
           // ratio of the step before this range; before step 0 it is 1 / W_REF
-          pmv[0] = t0e ? pmT[own * kPmLd + t0e - 1]
-                       : __fdividef(1.f, qtot[4 * kDim + own] * qtot[5 * kDim + own]);
+          pmv[0] = c0 ? pmT[own * kPmLd + c0 - 1] : __fdividef(1.f, qtot[4 * kDim + own] * qtot[5 * kDim + own]);
         }
         float bnd = 0.f;
 #pragma unroll
         for (int r = 0; r < 8; ++r) bnd += bndp[r * kDim + own];
-        const unsigned m8 = (unsigned)((fix_mask[own] >> t0e) & 0xffull);
+        const unsigned m8 = (unsigned)((fix_mask[own] >> c0) & 0xffull);
         float gr[8], ip[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           ip[j] = __fdividef(1.f, pmv[j + 1]);
           gr[j] = pmv[j] * ip[j];                       // 1 / gate
+        }
+        // own-side operand values: both lane sets hold all 64 columns, the load names one range per warp
+        float mw[8], vw[8];
+        {
+          float m0[8], m1[8], v0[8], v1[8];
+          umma::tmem_ld8(tl + cMw + 8 * part, m0);
+          umma::tmem_ld8(tl + cMw + 32 + 8 * part, m1);
+          umma::tmem_ld8(tl + cVw + 8 * part, v0);
+          umma::tmem_ld8(tl + cVw + 32 + 8 * part, v1);
+          umma::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            mw[j] = h ? m1[j] : m0[j];
+            vw[j] = h ? v1[j] : v0[j];
+          }
         }
         if (!umma::mbar_wait(&barM, pm_par)) s_fail = 1;
         pm_par ^= 1u;
@@ -440,18 +489,18 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
         float run = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) { const float v = pre[j]; pre[j] = run; run += v; }   // exclusive prefix
-        xc[(0 * 8 + ridx) * kDim + own] = sa[0];
-        xc[(1 * 8 + ridx) * kDim + own] = sb[0];
-        xc[(2 * 8 + ridx) * kDim + own] = run;
+        xc[(0 * 8 + cg) * kDim + own] = sa[0];
+        xc[(1 * 8 + cg) * kDim + own] = sb[0];
+        xc[(2 * 8 + cg) * kDim + own] = run;
         umma::named_barrier(1 + q4, 128);       // the four warps that share this lane quarter
         float addA = 0.f, addB = 0.f, addP = 0.f;
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
           const float va = xc[(0 * 8 + r) * kDim + own], vb2 = xc[(1 * 8 + r) * kDim + own];
           const float vp = xc[(2 * 8 + r) * kDim + own];
-          addA += (r > ridx) ? va : 0.f;        // later steps
-          addB += (r > ridx) ? vb2 : 0.f;
-          addP += (r < ridx) ? vp : 0.f;        // earlier steps
+          addA += (r > cg) ? va : 0.f;        // later steps
+          addB += (r > cg) ? vb2 : 0.f;
+          addP += (r < cg) ? vp : 0.f;        // earlier steps
         }
         const float base_h = addA + addP + bnd;
 #pragma unroll
@@ -462,13 +511,13 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
           for (int j = 0; j < 8; ++j)
             if ((m8 >> j) & 1u)
               for (int e = 0; e < n_fix; ++e)
-                if (fix_code[e] == (((t0e + j) << 8) | own)) sb[j] = fix_val[e];
+                if (fix_code[e] == (((c0 + j) << 8) | own)) sb[j] = fix_val[e];
         }
         // 16 consecutive features of one step are 32 contiguous bytes: the results go straight out
         T *o_mu = (ph ? nullptr : dq) , *o_dv = ph ? dx : dk, *o_gt = ph ? df : dfk;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const int t = t0e + j;
+          const int t = c0 + j;
           const float H = sa[j] + sb[j] + pre[j] + base_h;
           if (t < nvalid) {
             const size_t o = base + (size_t)t * kDim + own;
@@ -485,11 +534,10 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
     }
     if (s_fail) break;
   }
-  if (tid == 0) {
-    if (s_fail) {
-      atomicExch(status, 1);
-      if (raw_pending) acp::mbar_wait(&barRaw, it & 1u);   // bounded: let the copies in flight land
-    }
+  cp_async_wait_all();
+  if (tid == 0 && s_fail) {
+    atomicExch(status, 1);
+    if (raw_pending) acp::mbar_wait(&barRaw, it & 1u);   // bounded: let the copies in flight land
   }
   sync_all();
   if (warp == 0) umma::tmem_dealloc(tb, kTmemCols);

@@ -3,7 +3,8 @@
 // chunks.  Replaces the reference's materialised states and output einsum
 // (t2fw/csrc/lfw_kernel.cu:43-57, t2fw/csrc/lfw.cpp:45).
 //
-// Per chunk, with S0 the state at the chunk start (notation of lfw_c64.cuh):
+// Per chunk, with S0 the state at the chunk start (the caller's state or the 16-bit checkpoint the
+// carry wrote; notation of lfw_c64.cuh):
 //     P   = tril( (q pm_g) (k / pm_g)^T )                       in-chunk decays, k side
 //     O^  = (q G_t) (A_REF .* S0)^T  +  P (x / pm_a)            [t][d]
 //     o_t = pm_a[t] .* O^_t
@@ -14,7 +15,7 @@
 // asynchronous copies into one of two buffers (the next chunk is fetched while this one is
 // computed); thread (gate side, 16-step quarter, feature) walks its steps with a running gate
 // product (stage 1: ratio tables), then the operand tiles are written element-wise with 16-byte
-// stores (stage 2); two elected threads issue the MMAs; the accumulators come
+// stores (stage 2); one elected lane issues the MMAs; the accumulators come
 // back time-major (a thread owns one step and eight features), so the 16-bit outputs leave as
 // 16-byte stores.
 #include <type_traits>
@@ -25,7 +26,7 @@ namespace t2fw {
 
 using namespace c64;
 
-int lfw_chunk_status_ptr(int **out);   // lfw_chunk_local_umma.cu
+int lfw_chunk_status_ptr(int **out);   // lfw_c64_local.cu
 
 namespace {
 
@@ -37,9 +38,11 @@ constexpr int oPmk = oT + 5 * kTile;               // pm_g[t][k]
 constexpr int oPmF = oPmk + kC * kDim * 4;         // pm_a[d][t]
 constexpr int oPmA = oPmF + kDim * kPmLd * 4;      // pm_a[t][d]
 constexpr int oQt = oPmA + kC * kPmLd * 4;         // quarter products [2 sides][4][64]
-constexpr int oRaw = oQt + 2 * 4 * kDim * 4;       // [2 buffers] x, f, q, k, fk
+constexpr int kS0Ld = 144;                         // row stride (bytes) of the start-state landing zone
+constexpr int oS0L = oQt + 2 * 4 * kDim * 4;       // start state of a chunk, [64][kS0Ld] 16-bit
+constexpr int oRaw = oS0L + kDim * kS0Ld;           // [2 buffers] x, f, q, k, fk
 constexpr int kSmemF = oRaw + 2 * 5 * kRawBytes + 1024;   // + slack for the 1024-byte alignment
-static_assert(oRaw % 128 == 0, "bulk-copy destination alignment");
+static_assert(oRaw % 128 == 0 && oS0L % 16 == 0, "copy destination alignment");
 static_assert(kSmemF + 256 <= 227 * 1024, "shared memory limit");
 
 constexpr int cP = 0, cO = 32;                     // tensor-memory columns
@@ -47,8 +50,8 @@ constexpr int cP = 0, cO = 32;                     // tensor-memory columns
 template <typename T>
 __global__ void __launch_bounds__(kThreadsF, 1)
 lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__restrict__ q,
-                   const T *__restrict__ k, const T *__restrict__ fk, const float *__restrict__ Sstart,
-                   T *__restrict__ out, int *__restrict__ rowflag, int *__restrict__ status, int64_t T_,
+                   const T *__restrict__ k, const T *__restrict__ fk, const T *__restrict__ state,
+                   const T *__restrict__ ckpt, T *__restrict__ out, int *__restrict__ rowflag, int *__restrict__ status, int64_t T_,
                    int64_t nc, int64_t total) {
   extern __shared__ __align__(1024) unsigned char sm_raw[];
   unsigned char *sm = sm_raw + ((1024u - (umma::smem_u32(sm_raw) & 1023u)) & 1023u);   // swizzle atoms are 1024-byte aligned
@@ -83,11 +86,20 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
     acp::bulk_g2s(r + 4 * kRawBytes, fk + base, vb, &barRaw[buf]);
   };
 
+  // start state of a chunk (the caller's state for the first chunk of a row, else the checkpoint
+  // written by the carry): one 16-byte asynchronous copy per thread into the padded landing zone
+  auto issue_state = [&](int64_t ci) {   // every thread
+    const int64_t b = ci / nc, c = ci % nc;
+    const T *s0p = (c == 0) ? state + (size_t)b * kDim * kDim : ckpt + ((size_t)b * nc + (c - 1)) * kDim * kDim;
+    cp_async16(sm + oS0L + (tid >> 3) * kS0Ld + (tid & 7) * 16, s0p + (tid >> 3) * kDim + (tid & 7) * 8);
+    cp_async_commit();
+  };
+
   if (tid == 0) {
     umma::mbar_init(&barRaw[0], 1);
     umma::mbar_init(&barRaw[1], 1);
-    umma::mbar_init(&barP, 2);
-    umma::mbar_init(&barO, 2);
+    umma::mbar_init(&barP, 1);
+    umma::mbar_init(&barO, 1);
     umma::mbar_fence_init();
     s_fail = 0;
   }
@@ -96,9 +108,12 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
   const uint32_t tb = __shfl_sync(0xffffffffu, tmem_slot, 0);
   const uint32_t tl = umma::tmem_addr(tb, 32 * q4, 0);
   uint32_t n_issued[2] = {0u, 0u}, n_landed[2] = {0u, 0u};      // thread 0: bulk-copy rounds per buffer
-  if (tid == 0 && (int64_t)blockIdx.x < total) {
-    issue_raw(blockIdx.x, 0);
-    ++n_issued[0];
+  if ((int64_t)blockIdx.x < total) {
+    if (tid == 0) {
+      issue_raw(blockIdx.x, 0);
+      ++n_issued[0];
+    }
+    issue_state(blockIdx.x);
   }
   const uint32_t aT = umma::smem_u32(sm + oT);
   const uint64_t dT0 = desc_sw128(aT), dT1 = desc_sw128(aT + kTile), dT2 = desc_sw128(aT + 2 * kTile);
@@ -111,10 +126,6 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
     const int nvalid = (int)((T_ - t0c < kC) ? T_ - t0c : kC);
     T *raw = reinterpret_cast<T *>(sm + oRaw + buf * 5 * kRawBytes);
 
-    // start-of-chunk state: requested now, used after the operand tiles
-    const float4 *sp = reinterpret_cast<const float4 *>(Sstart + (size_t)ci * kDim * kDim + sr * kDim + sc0);
-    const float4 s_lo = sp[0], s_hi = sp[1];
-
     if (tid == 0) {
       s_bad = 0;
       if (ci + gridDim.x < total) {      // the other buffer was released at the end of the previous chunk
@@ -122,6 +133,7 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
         ++n_issued[buf ^ 1];
       }
     }
+    cp_async_wait_all();       // this thread's share of this chunk's start state (requested one chunk ahead)
     if (acp::mbar_wait(&barRaw[buf], (it >> 1) & 1u)) {
       if (tid == 0) ++n_landed[buf];
     } else {
@@ -190,6 +202,10 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
     // ---- state tile S0' = A_REF .* S0 ----
     {
       const float a_ref = qtot[4 * kDim + sr] * qtot[5 * kDim + sr];
+      const uint4 u = *reinterpret_cast<const uint4 *>(sm + oS0L + sr * kS0Ld + sc0 * 2);
+      const T *e = reinterpret_cast<const T *>(&u);
+      const float4 s_lo = make_float4(Elem<T>::ld(e), Elem<T>::ld(e + 1), Elem<T>::ld(e + 2), Elem<T>::ld(e + 3));
+      const float4 s_hi = make_float4(Elem<T>::ld(e + 4), Elem<T>::ld(e + 5), Elem<T>::ld(e + 6), Elem<T>::ld(e + 7));
       unsigned char *tS = sm + oT + 4 * kTile;
       *reinterpret_cast<float4 *>(tS + toff(sr, sc0)) =
           make_float4(rna_tf32(s_lo.x * a_ref), rna_tf32(s_lo.y * a_ref), rna_tf32(s_lo.z * a_ref),
@@ -199,14 +215,25 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
                       rna_tf32(s_hi.w * a_ref));
     }
     umma::fence_async_smem();
-    sync_all();       // tiles complete, raw buffer consumed
+    sync_all();       // tiles complete, raw buffer and start state consumed
+    if (ci + gridDim.x < total) issue_state(ci + gridDim.x);
 
-    if (warp < 2) {     // one issuing thread per 32-column half
-      const uint32_t dh = umma::tmem_addr(tb, 16 * warp, 0);
+    // A product is a chain of eight dependent instructions; the tensor core executes in issue
+    // order, so one lane issues the independent chains interleaved and they overlap in the pipeline.
+    if (warp == 0) {
+      const uint32_t d0 = tb, d1 = umma::tmem_addr(tb, 16, 0);
+      constexpr uint32_t idesc = umma::make_idesc_tf32(64, 32, false, false);
+      constexpr uint64_t n1 = (uint64_t)(32 * 128 >> 4);     // B rows 32..63
       if (elect_one()) {
-        mma_64x32x64(dh + cP, dT0, dT1, 32 * warp, false);      // P = Qmid Kmid^T
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
+          umma::mma_tf32(d0 + cP, dT0 + o, dT1 + o, idesc, ks > 0);             // P = Qmid Kmid^T
+          umma::mma_tf32(d1 + cP, dT0 + o, dT1 + n1 + o, idesc, ks > 0);
+          umma::mma_tf32(d0 + cO, dT2 + o, dT4 + o, idesc, ks > 0);             // O^ = Qstart S0'^T
+          umma::mma_tf32(d1 + cO, dT2 + o, dT4 + n1 + o, idesc, ks > 0);
+        }
         umma::mma_commit(&barP);
-        mma_64x32x64(dh + cO, dT2, dT4, 32 * warp, false);      // O^ = Qstart S0'^T
       }
       __syncwarp();
       if (tid == 0 && s_bad) atomicExch(rowflag + b, 1);      // the scan kernel redoes this batch row
@@ -228,10 +255,17 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
     umma::fence_async_smem();
     sync_all();
     if (s_fail) break;
-    if (warp < 2) {     // same lanes as above: O^ += P Xmid follows O^ = ... in issue order
-      const uint32_t dh = umma::tmem_addr(tb, 16 * warp, cO);
+    if (warp == 0) {     // the same lane as above: O^ += P Xmid follows O^ = ... in issue order
+      const uint32_t d0 = tb, d1 = umma::tmem_addr(tb, 16, 0);
+      constexpr uint32_t idesc = umma::make_idesc_tf32(64, 32, false, false);
+      constexpr uint64_t n1 = (uint64_t)(32 * 128 >> 4);
       if (elect_one()) {
-        mma_64x32x64(dh, dT0, dT3, 32 * warp, true);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
+          umma::mma_tf32(d0 + cO, dT0 + o, dT3 + o, idesc, true);
+          umma::mma_tf32(d1 + cO, dT0 + o, dT3 + n1 + o, idesc, true);
+        }
         umma::mma_commit(&barO);
       }
       __syncwarp();
@@ -255,6 +289,7 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
     sync_all();       // accumulators and tiles free for the next chunk
     if (s_fail) break;
   }
+  cp_async_wait_all();
   if (tid == 0) {
     if (s_fail) atomicExch(status, 1);
     // bounded: let copies that are still in flight land before the CTA leaves
@@ -272,10 +307,10 @@ int g_sms_f[64] = {};
 
 // Returns T2FW_ERR_UNSUPPORTED (without launching) if a pointer is not 16-byte aligned.
 int lfw_c64_forward_out(const void *x, const void *f, const void *q, const void *k, const void *fk,
-                        const float *Sstart, void *out, int *rowflag, int64_t B, int64_t T_, int dtype,
-                        cudaStream_t st) {
-  if (!(aligned16(x) && aligned16(f) && aligned16(q) && aligned16(k) && aligned16(fk) && aligned16(Sstart) &&
-        aligned16(out)))
+                        const void *state, const void *ckpt, void *out, int *rowflag, int64_t B, int64_t T_,
+                        int dtype, cudaStream_t st) {
+  if (!(aligned16(x) && aligned16(f) && aligned16(q) && aligned16(k) && aligned16(fk) && aligned16(state) &&
+        aligned16(ckpt) && aligned16(out)))
     return T2FW_ERR_UNSUPPORTED;
   int dev = 0;
   T2FW_CHECK_CUDA(cudaGetDevice(&dev));
@@ -295,7 +330,8 @@ int lfw_c64_forward_out(const void *x, const void *f, const void *q, const void 
     T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_c64_fwd_kernel<TT>,                                     \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemF));      \
     lfw_c64_fwd_kernel<TT><<<grid, kThreadsF, kSmemF, st>>>(                                         \
-        (const TT *)x, (const TT *)f, (const TT *)q, (const TT *)k, (const TT *)fk, Sstart, (TT *)out, \
+        (const TT *)x, (const TT *)f, (const TT *)q, (const TT *)k, (const TT *)fk, (const TT *)state,     \
+        (const TT *)ckpt, (TT *)out, \
         rowflag, status, T_, nc, total);                                                             \
   } while (0)
   if (dtype == T2FW_F16) T2FW_LAUNCH(__half); else T2FW_LAUNCH(__nv_bfloat16);
