@@ -14,6 +14,12 @@
  *   ckpt_states ................................ [B, n_slots, D, K], slot j = state after step
  *                                                min((j+1)*ckpt_every, T); the last slot is S_T
  *
+ * Limits: D <= 512 and K <= 512 in every entry point (T2FW_ERR_BAD_ARG otherwise; forward and
+ * backward share the limit, so a training step never fails only at its backward call).
+ * Alignment: any element-aligned pointer is accepted; the tensor-core paths need all pointers
+ * (scratch included) 16-byte aligned and the library takes its element-wise scan kernels, which
+ * are much slower, when one is not.
+ *
  * Each function below names the reference interface it replaces (path inside the reference
  * project : lines).
  */
@@ -141,7 +147,10 @@ int t2fw_dfw_backward(const void *grad_output, const void *grad_state,
  * Delta rule backward without caller-provided scratch.  No counterpart in the reference
  * (its backward allocates freely through ATen).
  *
- * Same inputs, outputs and results as t2fw_dfw_backward, for hosts that cannot give the call
+ * Same inputs and outputs as t2fw_dfw_backward and the same mathematical result; it always runs
+ * the sequential scan kernels (never the chunked tensor-core kernels, which need far more
+ * scratch), so on D = M = 64 16-bit problems it is an order of magnitude slower than
+ * t2fw_dfw_backward and its rounding differs within the documented tolerance.  It is for hosts that cannot give the call
  * any device memory beyond the operator's own tensors and cannot call cudaMalloc themselves:
  * a runtime that reserved the entire GPU for its own pool when it started, a latency-critical
  * loop that must avoid the device-wide synchronisation an allocation implies, or a foreign
@@ -167,6 +176,23 @@ int t2fw_dfw_backward_noalloc(const void *grad_output, const void *grad_state,
                               void *d_q, void *d_k, void *d_v, void *d_state,
                               int64_t B, int64_t T, int64_t D, int64_t M, int dtype,
                               void *stream);
+
+/*
+ * Diagnostic: launches a one-warp kernel that waits, with a limit of `polls` polls, on a barrier
+ * that nothing arrives on.  The wait runs out, the kernel sets *status (device int; NULL = the
+ * library's own status word, the one t2fw_device_status reports) and returns: the give-up path of
+ * the bounded waits with nothing in flight.  No counterpart in the reference.
+ */
+int t2fw_selftest_bounded_wait(int polls, int *status, void *stream);
+
+/*
+ * Diagnostic: D = A * B^T with the A operand [64 x 64] read from tensor memory (written there by
+ * tcgen05.st, stored in both lane sets) and B [64 x 64] a 128-byte-swizzle shared-memory tile: the
+ * operand forms of the decay rule's 64-step chunk kernels.  All row-major fp32 device arrays, used
+ * at TF32 precision.  *status (device int) is set to 1 if a bounded wait expired.  No counterpart
+ * in the reference.
+ */
+int t2fw_selftest_umma_ts(const float *A, const float *B, float *D, int *status, void *stream);
 
 /*
  * Diagnostic: exercises the tensor-core building blocks of the chunked kernels in isolation

@@ -123,6 +123,10 @@ static int check_common(int64_t B, int64_t T, int64_t D, int64_t K, int dtype) {
   T2FW_CHECK_ARG(dtype_size(dtype) != 0, "unknown dtype %d", dtype);
   T2FW_CHECK_ARG(B > 0 && T > 0 && D > 0 && K > 0, "sizes must be positive (B=%lld T=%lld D=%lld K=%lld)",
                  (long long)B, (long long)T, (long long)D, (long long)K);
+  // one limit for every entry point, so that a forward call never succeeds on a shape whose
+  // backward call would be refused
+  T2FW_CHECK_ARG(D <= 512 && K <= 512, "state extents up to 512 x 512 are supported (D=%lld, K=%lld)",
+                 (long long)D, (long long)K);
   return T2FW_OK;
 }
 

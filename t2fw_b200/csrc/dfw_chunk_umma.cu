@@ -26,6 +26,7 @@ namespace t2fw {
 using namespace chunk;
 
 int lfw_chunk_status_ptr(int **out);   // lfw_c64_local.cu
+int lfw_chunk_sm_count(int *out);
 
 #ifdef T2FW_DFW_PROFILE
 __device__ long long g_dfw_prof[48];
@@ -911,13 +912,16 @@ int dfw_chunk_bwd_par_umma(const void *go, const void *q, const void *k, const v
   int dev = 0;
   T2FW_CHECK_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return T2FW_ERR_UNSUPPORTED;
-  static int sms[64] = {};
-  if (sms[dev] == 0) T2FW_CHECK_CUDA(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
+  int n_sm = 0;
+  {
+    const int rc_sm = lfw_chunk_sm_count(&n_sm);     // cached per device under a lock
+    if (rc_sm != T2FW_OK) return rc_sm;
+  }
   int *status = nullptr;
   int rc = lfw_chunk_status_ptr(&status);
   if (rc != T2FW_OK) return rc;
   const int64_t nc = ceil_div64(T_, kC), total = B * nc;
-  const unsigned grid = (unsigned)(total < sms[dev] ? total : sms[dev]);     // one persistent CTA per SM
+  const unsigned grid = (unsigned)(total < n_sm ? total : n_sm);     // one persistent CTA per SM
 #define T2FW_LAUNCH(TT)                                                                                  \
   do {                                                                                                   \
     T2FW_CHECK_CUDA(cudaFuncSetAttribute(dfw_chunk_bwd_par_umma_kernel<TT>,                              \

@@ -62,7 +62,11 @@ int t2fw_dfw_backward_noalloc(const void *grad_output, const void *grad_state, c
                  "null pointer argument");
   void *dv_acc = d_v;  // float / double outputs are their own accumulation-type copy
   if (dtype == T2FW_F16 || dtype == T2FW_BF16) {
-    const unsigned long long need = (unsigned long long)B * T * D;
+    // each factor is bounded first, so that the product below cannot wrap around
+    const bool fits = (unsigned long long)B <= kMaxElems && (unsigned long long)T <= kMaxElems &&
+                      (unsigned long long)D <= kMaxElems &&
+                      (unsigned long long)B * (unsigned long long)T <= kMaxElems;
+    const unsigned long long need = fits ? (unsigned long long)B * T * D : ~0ull;
     if (need > kMaxElems) {
       t2fw::set_error(
           "dfw backward (no-alloc): B*T*D = %llu exceeds the built-in scratch of %zu elements; "

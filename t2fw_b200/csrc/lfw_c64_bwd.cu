@@ -37,6 +37,7 @@ namespace t2fw {
 using namespace c64;
 
 int lfw_chunk_status_ptr(int **out);   // lfw_c64_local.cu
+int lfw_chunk_sm_count(int *out);
 
 #ifdef T2FW_C64_PROFILE
 __device__ long long g_c64_prof[32];
@@ -544,7 +545,6 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
 }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-int g_sms_b[64] = {};
 
 }  // namespace
 
@@ -557,19 +557,14 @@ int lfw_c64_backward_main(const void *go, const void *x, const void *f, const vo
         aligned16(state) && aligned16(ckpt) && aligned16(Rend) && aligned16(dx) && aligned16(df) &&
         aligned16(dq) && aligned16(dk) && aligned16(dfk)))
     return T2FW_ERR_UNSUPPORTED;
-  int dev = 0;
-  T2FW_CHECK_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return T2FW_ERR_UNSUPPORTED;
-  if (g_sms_b[dev] == 0) {
-    int n = 0;
-    T2FW_CHECK_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
-    g_sms_b[dev] = n;
-  }
   int *status = nullptr;
   int rc = lfw_chunk_status_ptr(&status);
   if (rc != T2FW_OK) return rc;
+  int n_sm = 0;
+  rc = lfw_chunk_sm_count(&n_sm);
+  if (rc != T2FW_OK) return rc;
   const int64_t nc = ceil_div64(T_, kC), total = B * nc;
-  const unsigned grid = (unsigned)(total < g_sms_b[dev] ? total : g_sms_b[dev]);
+  const unsigned grid = (unsigned)(total < n_sm ? total : n_sm);
 #define T2FW_LAUNCH(TT)                                                                               \
   do {                                                                                                \
     T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_c64_bwd_kernel<TT>,                                      \

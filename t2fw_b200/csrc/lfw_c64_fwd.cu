@@ -27,6 +27,7 @@ namespace t2fw {
 using namespace c64;
 
 int lfw_chunk_status_ptr(int **out);   // lfw_c64_local.cu
+int lfw_chunk_sm_count(int *out);
 
 namespace {
 
@@ -301,7 +302,6 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
 }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-int g_sms_f[64] = {};
 
 }  // namespace
 
@@ -312,19 +312,14 @@ int lfw_c64_forward_out(const void *x, const void *f, const void *q, const void 
   if (!(aligned16(x) && aligned16(f) && aligned16(q) && aligned16(k) && aligned16(fk) && aligned16(state) &&
         aligned16(ckpt) && aligned16(out)))
     return T2FW_ERR_UNSUPPORTED;
-  int dev = 0;
-  T2FW_CHECK_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return T2FW_ERR_UNSUPPORTED;
-  if (g_sms_f[dev] == 0) {
-    int n = 0;
-    T2FW_CHECK_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
-    g_sms_f[dev] = n;
-  }
   int *status = nullptr;
   int rc = lfw_chunk_status_ptr(&status);
   if (rc != T2FW_OK) return rc;
+  int n_sm = 0;
+  rc = lfw_chunk_sm_count(&n_sm);
+  if (rc != T2FW_OK) return rc;
   const int64_t nc = ceil_div64(T_, kC), total = B * nc;
-  const unsigned grid = (unsigned)(total < g_sms_f[dev] ? total : g_sms_f[dev]);
+  const unsigned grid = (unsigned)(total < n_sm ? total : n_sm);
 #define T2FW_LAUNCH(TT)                                                                              \
   do {                                                                                               \
     T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_c64_fwd_kernel<TT>,                                     \

@@ -35,8 +35,8 @@ void check_status(int rc, const char *what) {
 }
 
 void check_same(const at::Tensor &a, const at::Tensor &ref, const char *name) {
-  TORCH_CHECK(a.scalar_type() == ref.scalar_type(), name, ": dtype differs from value's");
-  TORCH_CHECK(a.device() == ref.device(), name, ": device differs from value's");
+  TORCH_CHECK(a.scalar_type() == ref.scalar_type(), name, ": dtype differs from the first tensor's");
+  TORCH_CHECK(a.device() == ref.device(), name, ": device differs from the first tensor's");
 }
 
 int64_t ckpt_interval(int64_t T, int64_t D, int64_t K, int dtype) {
@@ -107,9 +107,16 @@ std::vector<at::Tensor> lfw_backward(at::Tensor grad_output, at::Tensor grad_sta
   TORCH_CHECK(value.dim() == 3 && query.dim() == 3 && state.dim() == 3 && ckpt_states.dim() == 4, "bad ranks");
   const int64_t B = value.size(0), T = value.size(1), D = value.size(2), K = query.size(2);
   TORCH_CHECK(grad_output.sizes() == value.sizes(), "grad_output must be [B,T,D]");
+  TORCH_CHECK(forget.sizes() == value.sizes() && outputs.sizes() == value.sizes(), "forget and outputs must be [B,T,D]");
+  TORCH_CHECK(query.size(0) == B && query.size(1) == T, "query must be [B,T,K]");
+  TORCH_CHECK(key.sizes() == query.sizes() && f_key.sizes() == query.sizes(), "key and f_key must have query's shape");
+  TORCH_CHECK(state.size(0) == B && state.size(1) == D && state.size(2) == K, "state must be [B,D,K]");
   TORCH_CHECK(grad_state.sizes() == state.sizes(), "grad_state must be [B,D,K]");
   check_same(grad_output, value, "grad_output"); check_same(grad_state, value, "grad_state");
+  check_same(forget, value, "forget"); check_same(query, value, "query"); check_same(key, value, "key");
+  check_same(f_key, value, "f_key"); check_same(outputs, value, "outputs"); check_same(state, value, "state");
   check_same(ckpt_states, value, "ckpt_states");
+  TORCH_CHECK(B > 0 && T > 0 && D > 0 && K > 0, "empty tensors are not supported");
 
   const c10::cuda::CUDAGuard guard(value.device());
   const int dt = dtype_code(value);
@@ -117,6 +124,8 @@ std::vector<at::Tensor> lfw_backward(at::Tensor grad_output, at::Tensor grad_sta
   TORCH_CHECK(ckpt_states.size(0) == B && ckpt_states.size(1) == t2fw_lfw_ckpt_slots(T, C) &&
                   ckpt_states.size(2) == D && ckpt_states.size(3) == K,
               "ckpt_states does not match the checkpoint interval in use");
+  // separate allocations: views of one buffer would be flagged by autograd when a caller later
+  // modifies a gradient in place
   at::Tensor d_x = at::empty_like(value), d_f = at::empty_like(forget);
   at::Tensor d_q = at::empty_like(query), d_k = at::empty_like(key), d_fk = at::empty_like(f_key);
   at::Tensor d_s = at::empty_like(state);
@@ -131,6 +140,42 @@ std::vector<at::Tensor> lfw_backward(at::Tensor grad_output, at::Tensor grad_sta
                                  ptr_or_null(scratch), sb, stream.stream()),
                "lfw.backward");
   return {d_x, d_f, d_q, d_k, d_fk, d_s};
+}
+
+// One decode step (T = 1) into caller-owned buffers: outputs [B,1,D] and state_out [B,D,K] are
+// written, nothing is allocated, so a loop that alternates two state buffers can be captured in a
+// CUDA graph and replayed.  Additive: the reference has no counterpart (its recurrent use is
+// LFWFunction.apply with the returned state fed back, t2fw/functional_lfw.py:65).
+void lfw_decode_step(at::Tensor x, at::Tensor f, at::Tensor query, at::Tensor key, at::Tensor f_key,
+                     at::Tensor state_in, at::Tensor state_out, at::Tensor outputs) {
+  T2FW_CHECK_INPUT(x);
+  T2FW_CHECK_INPUT(f);
+  T2FW_CHECK_INPUT(query);
+  T2FW_CHECK_INPUT(key);
+  T2FW_CHECK_INPUT(f_key);
+  T2FW_CHECK_INPUT(state_in);
+  T2FW_CHECK_INPUT(state_out);
+  T2FW_CHECK_INPUT(outputs);
+  TORCH_CHECK(x.dim() == 3 && x.size(1) == 1 && query.dim() == 3 && state_in.dim() == 3,
+              "expected x [B,1,D], query [B,1,K], state [B,D,K]");
+  const int64_t B = x.size(0), D = x.size(2), K = query.size(2);
+  TORCH_CHECK(f.sizes() == x.sizes() && outputs.sizes() == x.sizes(), "f and outputs must have x's shape");
+  TORCH_CHECK(query.size(0) == B && query.size(1) == 1, "query must be [B,1,K]");
+  TORCH_CHECK(key.sizes() == query.sizes() && f_key.sizes() == query.sizes(), "key and f_key must have query's shape");
+  TORCH_CHECK(state_in.size(0) == B && state_in.size(1) == D && state_in.size(2) == K, "state_in must be [B,D,K]");
+  TORCH_CHECK(state_out.sizes() == state_in.sizes(), "state_out must have state_in's shape");
+  TORCH_CHECK(state_out.data_ptr() != state_in.data_ptr(), "state_out must not be state_in: alternate two buffers");
+  check_same(f, x, "f"); check_same(query, x, "query"); check_same(key, x, "key"); check_same(f_key, x, "f_key");
+  check_same(state_in, x, "state_in"); check_same(state_out, x, "state_out"); check_same(outputs, x, "outputs");
+  TORCH_CHECK(B > 0 && D > 0 && K > 0, "empty tensors are not supported");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int dt = dtype_code(x);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  // T = 1: one checkpoint slot, which is the new state
+  check_status(t2fw_lfw_forward(x.data_ptr(), f.data_ptr(), query.data_ptr(), key.data_ptr(), f_key.data_ptr(),
+                                state_in.data_ptr(), outputs.data_ptr(), state_out.data_ptr(), B, 1, D, K, dt, 1,
+                                nullptr, 0, stream.stream()),
+               "lfw.decode_step");
 }
 
 // ---- delta rule ---------------------------------------------------------------------------
@@ -181,7 +226,12 @@ std::vector<at::Tensor> dfw_backward(at::Tensor grad_output, at::Tensor grad_sta
   const int64_t B = grad_output.size(0), T = grad_output.size(1), D = grad_output.size(2),
                 M = query.size(2);
   TORCH_CHECK(delta_value.sizes() == grad_output.sizes(), "delta_value must be [B,T,D]");
+  TORCH_CHECK(query.size(0) == B && query.size(1) == T && key.sizes() == query.sizes(), "query/key must be [B,T,M]");
+  TORCH_CHECK(final_state.size(0) == B && final_state.size(1) == D && final_state.size(2) == M, "final_state must be [B,D,M]");
   TORCH_CHECK(grad_state.sizes() == final_state.sizes(), "grad_state must be [B,D,M]");
+  check_same(key, query, "key");
+  TORCH_CHECK(delta_value.device() == query.device(), "delta_value: device differs from query's");
+  TORCH_CHECK(B > 0 && T > 0 && D > 0 && M > 0, "empty tensors are not supported");
   TORCH_CHECK(delta_value.scalar_type() == acc_type(query), "delta_value must be the tensor dfw.forward returned");
   check_same(grad_output, query, "grad_output"); check_same(grad_state, query, "grad_state");
   check_same(final_state, query, "final_state");
@@ -206,6 +256,7 @@ std::vector<at::Tensor> dfw_backward(at::Tensor grad_output, at::Tensor grad_sta
 TORCH_LIBRARY(lfw, m) {
   m.def("forward", lfw_forward);
   m.def("backward", lfw_backward);
+  m.def("decode_step", lfw_decode_step);
 }
 
 TORCH_LIBRARY(dfw, m) {

@@ -145,8 +145,8 @@ __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
 __device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 constexpr uint32_t kSpinLimit = 1u << 19;
 // bounded wait for the phase with the given parity; false on timeout
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = kSpinLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t ok;
     asm volatile(
         "{\n"

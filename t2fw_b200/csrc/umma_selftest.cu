@@ -252,6 +252,35 @@ umma_ts_selftest_kernel(const float *__restrict__ A, const float *__restrict__ B
 
 using namespace t2fw;
 
+namespace t2fw {
+int lfw_chunk_status_ptr(int **out);   // lfw_c64_local.cu
+namespace {
+// A wait that cannot complete: the barrier expects one arrival and nothing ever arrives.  Nothing
+// else is in flight, so giving up is harmless; the kernel reports it exactly as the production
+// kernels do (through the status word) and returns.
+__global__ void bounded_wait_selftest_kernel(uint32_t limit, int *status) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (!mbar_wait(&bar, 0, limit) && threadIdx.x == 0) atomicExch(status, 1);
+}
+}  // namespace
+}  // namespace t2fw
+
+extern "C" int t2fw_selftest_bounded_wait(int polls, int *status, void *stream) {
+  T2FW_CHECK_ARG(polls >= 1 && polls <= 4096, "selftest_bounded_wait: polls in [1, 4096]");
+  if (status == nullptr) {      // report through the library's own status word (t2fw_device_status)
+    const int rc = lfw_chunk_status_ptr(&status);
+    if (rc != T2FW_OK) return rc;
+  }
+  bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>((uint32_t)polls, status);
+  T2FW_CHECK_LAUNCH(1);
+  return T2FW_OK;
+}
+
 extern "C" int t2fw_selftest_umma_ts(const float *A, const float *B, float *D, int *status, void *stream) {
   T2FW_CHECK_ARG(A && B && D && status, "null pointer argument");
   const int smem = 64 * 64 * 4 + 1024;

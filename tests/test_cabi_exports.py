@@ -41,7 +41,7 @@ def test_library_is_not_an_instrumented_build():
     from t2fw_b200 import _lib
 
     lib = ctypes.CDLL(_lib.CORE_PATH)
-    for name in ("t2fw_debug_prof", "t2fw_debug_dfw_prof"):
+    for name in ("t2fw_debug_prof", "t2fw_debug_dfw_prof", "t2fw_debug_c64_prof", "t2fw_debug_loc_prof"):
         assert not hasattr(lib, name), name + ": rebuild without the profiling macro"
 
 

@@ -83,3 +83,26 @@ def test_umma16_products(cuda, N, Kc, a_mn, b_mn):
         ref = (A.double() @ B.double().T)
         assert torch.isfinite(D).all()
         assert (D.double() - ref).abs().max().item() <= 1e-4 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.gpu
+def test_umma_a_operand_from_tensor_memory(cuda):
+    """A [64 x 64] written into tensor memory (both lane sets), B a 128-byte-swizzle shared-memory
+    tile: the operand forms of the 64-step chunk kernels."""
+    from t2fw_b200 import _lib
+
+    lib = _lib.load_core()
+    fn = lib.t2fw_selftest_umma_ts
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_void_p, ctypes.c_void_p]
+    g = torch.Generator().manual_seed(11)
+    A = _tf32(torch.randn(64, 64, generator=g)).to(cuda)
+    B = _tf32(torch.randn(64, 64, generator=g)).to(cuda)
+    D = torch.full((64, 64), float("nan"), device=cuda)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    rc = fn(A.data_ptr(), B.data_ptr(), D.data_ptr(), status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.t2fw_last_error().decode()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded wait expired"
+    ref = A.double() @ B.double().T
+    assert (D.double() - ref).abs().max().item() <= 1e-4 * max(1.0, ref.abs().max().item())

@@ -3,14 +3,18 @@
 It exists for hosts that cannot allocate device memory when they call the operator and cannot
 pass scratch through their bridge; its scratch is a fixed array inside the library.  The test
 drives it through the C ABI exactly as such a host would (raw pointers, no scratch argument)
-and compares every gradient with the regular entry point, twice in a row on different data so
-that whatever the first call left in the shared array is shown not to matter.  This file sorts
+and compares every gradient with the regular entry point AND with the float64 oracle, twice in a
+row on different data so that whatever the first call left in the shared array is shown not to
+matter.  The second problem is D = M = 64, where the regular entry point runs the chunked
+tensor-core kernels and this one the sequential scan kernels: two different computations of the
+same gradients.  This file sorts
 last on purpose: a run that stops at the first failure has then already run everything else.
 """
 import pytest
 import torch
 
 from helpers import GRAD_TOL, dfw_inputs, max_rel_err, to_dev
+from oracle import fw_oracle
 
 
 def _call_noalloc(lib, go, gs, q, k, delta, fin):
@@ -34,15 +38,17 @@ def test_noalloc_matches_regular_entry_point_twice(cuda, dtype):
     from t2fw_b200 import _lib, cabi
 
     lib = _lib.load_core()
-    for seed, (B, T, D, M) in ((31, (6, 200, 64, 32)), (32, (3, 333, 40, 24))):
+    for seed, (B, T, D, M) in ((31, (6, 200, 64, 32)), (32, (5, 300, 64, 64)), (34, (3, 333, 40, 24))):
         q, k, v, s, go, gs = to_dev(dfw_inputs(B, T, D, M, "scaled", 0.3, seed), dtype, cuda)
         _, fin, delta = cabi.dfw_forward(q, k, v, s)
         want = cabi.dfw_backward(go, gs, q, k, delta, fin)
         got = _call_noalloc(lib, go, gs, q, k, delta, fin)
         torch.cuda.synchronize()
-        for g, w, name in zip(got, want, ("d_q", "d_k", "d_v", "d_state")):
+        oracle = fw_oracle.dfw_backward(go, gs, q, k, v, s)
+        for g, w, o, name in zip(got, want, oracle, ("d_q", "d_k", "d_v", "d_state")):
             assert torch.isfinite(g).all(), name
             assert max_rel_err(g, w) <= GRAD_TOL[dtype], name
+            assert max_rel_err(g, o) <= GRAD_TOL[dtype], name + " (oracle)"
 
 
 @pytest.mark.gpu
@@ -73,3 +79,6 @@ def test_noalloc_rejects_oversized_problems():
     assert rc == 3
     msg = lib.t2fw_last_error().decode()
     assert "exceeds the built-in scratch" in msg and "t2fw_dfw_backward" in msg
+    # sizes whose product wraps around 64 bits are refused as well
+    rc = lib.t2fw_dfw_backward_noalloc(*ptrs, 1 << 32, 1 << 32, 1, 8, 0, None)
+    assert rc == 3
