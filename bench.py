@@ -16,12 +16,19 @@ a step is one forward + backward over the whole batch.  Prints ONE JSON line on 
               copies outputs, next state and the six gradients back
   roofline .. algorithmic bytes of the slower of the two calls (forward / backward) over its
               measured duration, against the measured HBM copy bandwidth
-  cpu_baseline  the per-step PyTorch restatement of the reference's TorchScript path
-              (oracle/torch_port.py) on this machine's host cores, on a bounded sample
+  value_api . the same step through LFWFunction.apply + autograd with device-resident tensors,
+              eager and replayed from a CUDA graph
+  extra.decode  the T=1 decode step (B*H=4096) measured in the same run: us/step over 1000 chained
+              steps through the allocation-free decode loop (graph replay), GB/s and fraction
+  cpu_baseline  the reference's own TorchScript CPU path (oracle/_ref, placed there by
+              oracle/make_ref.py; kind "reference") or, where that is absent, its restatement
+              oracle/torch_port.py (kind "port"), on this machine's host cores, on a bounded sample
+  strong .... (N > 1) the same workload with its batch*head rows split over the ranks
 
-`--impl reference` times that CPU path alone and prints the same line with "impl": "reference".
-Under torchrun each rank runs the full workload on its own GPU (weak scaling, no collective on
-the data path); rank 0 reports the aggregate.
+`--impl reference` times that CPU path alone on the whole workload (all rows; the row count is
+reduced, and said so, only if K+W calls would not finish within a few minutes) and prints the
+same line with "impl": "reference".  Under torchrun each rank runs the full workload on its own
+GPU (weak scaling, no collective on the data path); rank 0 reports the aggregate.
 """
 import argparse
 import json
@@ -179,41 +186,66 @@ class ClockSampler:
         return out
 
 
-def cpu_reference_run(workload, gates, steps, warmup, seed):
-    """Times oracle/torch_port (the port of the reference's TorchScript CPU path) on a bounded
-    sample of the workload; returns (tokens/s or steps/s, description dict)."""
+def cpu_reference_run(workload, gates, steps, warmup, seed, rows=None, budget_s=None):
+    """Times the reference's CPU path (oracle/_ref when present, else oracle/torch_port) on the host
+    cores.  rows=None: the workload's bounded sample; budget_s: shrink the row count so that
+    warmup + steps calls fit the budget.  Returns (tokens/s, description dict)."""
     import torch
-    from oracle import torch_port
+    from oracle import make_ref, torch_port
 
+    ref = make_ref.load()
     B, T, D, K = WORKLOADS[workload]
-    rows = min(B, CPU_SAMPLE_ROWS[workload])
+    rows = min(B, rows if rows is not None else CPU_SAMPLE_ROWS[workload])
     # launchers such as torchrun pin OMP_NUM_THREADS=1; the CPU baseline uses every host core
     torch.set_num_threads(max(1, os.cpu_count() or 1))
-    ins = [t[:rows].contiguous() for t in make_inputs(torch, rows, T, D, K, gates, seed, workload)]
-    if workload != "dfw":
-        x, f, q, k, fk, s, go, gs = ins
-    times = []
-    for i in range(warmup + steps):
-        t0 = time.perf_counter()
+    full = make_inputs(torch, B, T, D, K, gates, seed, workload)
+
+    def one_call(ins):
         if workload == "dfw":
-            torch_port.dfw_fwd_bwd(*ins)
-        elif workload == "decode":
+            if ref is None:
+                return torch_port.dfw_fwd_bwd(*ins)
+            leaves = [t.detach().clone().requires_grad_(True) for t in ins[:4]]
+            out, fin = ref.t2dfw_torch(*leaves)
+            return torch.autograd.grad([out, fin], leaves, [ins[4], ins[5]])
+        x, f, q, k, fk, s, go, gs = ins
+        if workload == "decode":
             with torch.no_grad():
-                torch_port.lfw_loop(x, f, q, k, fk, s)
-        else:
-            torch_port.lfw_fwd_bwd(x, f, q, k, fk, s, go, gs)
-        dt = time.perf_counter() - t0
-        if i >= warmup:
-            times.append(dt)
+                return (ref.t2fw_torch if ref is not None else torch_port.lfw_loop)(x, f, q, k, fk, s)
+        if ref is None:
+            return torch_port.lfw_fwd_bwd(x, f, q, k, fk, s, go, gs)
+        leaves = [t.detach().clone().requires_grad_(True) for t in (x, f, q, k, fk, s)]
+        out, fin = ref.t2fw_torch(*leaves)
+        return torch.autograd.grad([out, fin], leaves, [go, gs])
+
+    shrunk = None
+    while True:
+        ins = [t[:rows].contiguous() for t in full]
+        times = []
+        restart = False
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            one_call(ins)
+            dt = time.perf_counter() - t0
+            if i >= warmup:
+                times.append(dt)
+            if budget_s is not None and i == 0 and dt * (warmup + steps) > budget_s and rows > 8:
+                shrunk = rows
+                rows = max(8, int(rows * budget_s / (dt * (warmup + steps))))
+                restart = True
+                break
+        if not restart:
+            break
     med = statistics.median(times)
     value = rows * T / med
     desc = {
         "value": value, "unit": "tokens/s", "cores": torch.get_num_threads(),
-        "host_cpus": os.cpu_count(), "kind": "port",
-        "sample": "%d of %d batch rows, T=%d, D=K=%d, fp32, %s; median of %d calls after %d warm-up"
-                  % (rows, B, T, D, "forward only" if workload == "decode" else "forward+backward",
-                     len(times), warmup),
-        "s_per_call": med,
+        "host_cpus": os.cpu_count(), "kind": "reference" if ref is not None else "port",
+        "sample": "%d of %d batch rows%s, T=%d, D=K=%d, fp32, %s; median of %d calls after %d warm-up; %s"
+                  % (rows, B, "" if shrunk is None else " (reduced from %d to fit the time budget)" % shrunk,
+                     T, D, "forward only" if workload == "decode" else "forward+backward", len(times), warmup,
+                     "the reference's TorchScript functions (t2fw/torch.py) + autograd" if ref is not None
+                     else "oracle/torch_port.py (the reference module is not present)"),
+        "s_per_call": med, "rows": rows,
     }
     return value, desc
 
@@ -342,10 +374,12 @@ def run_reference(args):
         print(json.dumps({"impl": "reference", "unavailable": "the reference ships no model: the end-to-end "
                           "GPT-2 configuration has no reference implementation and no CPU baseline"}))
         return
-    steps = max(1, min(args.steps, 5))
-    warmup = max(2, min(args.warmup, 3))
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
     B, T, D, K = WORKLOADS[args.workload]
-    value, desc = cpu_reference_run(args.workload, args.gates, steps, warmup, args.seed)
+    # the whole workload (all batch rows), the requested number of calls; the row count is reduced
+    # only if those calls would not finish within a few minutes on this host
+    rows = B if args.workload in ("train", "decode", "dfw") else CPU_SAMPLE_ROWS[args.workload]
+    value, desc = cpu_reference_run(args.workload, args.gates, steps, warmup, args.seed, rows=rows, budget_s=300.0)
     line = {
         "impl": "reference", "metric": metric_name(args.workload), "value": value,
         "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
@@ -395,14 +429,14 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     from t2fw_b200 import _lib, cabi
+    from t2fw_b200.decode import LFWDecodeLoop
     from t2fw_b200.functional_dfw import DFWFunction
     from t2fw_b200.functional_lfw import LFWFunction
-    from t2fw_b200.parallel import max_over_ranks
+    from t2fw_b200.parallel import max_over_ranks, row_shard
 
     lib = _lib.load_core()
     B, T, D, K = WORKLOADS[args.workload]
     if args.scaling == "strong":        # contiguous share of the batch x head rows for this rank
-        from t2fw_b200.parallel import row_shard
         r0, r1 = row_shard(B, world, rank)
         B = r1 - r0
         if B == 0:
@@ -579,6 +613,134 @@ def run_ours(args):
     total_ms = max_over_ranks(total_ms, dev)
     value = rows_all * T * args.steps / (total_ms * 1e-3)     # all ranks' rows over the slowest rank's time
 
+    # ---- batch rows that left the tensor-core path (gate products out of range -> scan kernels) ----
+    flagged = None
+    if not dfw and not decode and D == 64 and K == 64 and fsb and bsb:
+        nc_ = (T + 63) // 64
+        off = B * nc_ * 4096 + 2 * B * nc_ * 64 + B * nc_       # rowflag follows M, Ac, Gc, flags
+        flagged = {"forward": int(fscr.view(torch.int32)[off:off + B].sum().item()),
+                   "backward": int(bscr.view(torch.int32)[off:off + B].sum().item()), "of_rows": B}
+
+    # ---- the same step through the autograd wrapper, tensors resident on the device -------------
+    value_api = None
+    if not decode:
+        Fn, n_in = (DFWFunction, 4) if dfw else (LFWFunction, 6)
+        n_api = max(3, min(args.steps, 10))
+
+        def api_step(i):
+            t = sets[i % n_sets]
+            leaves = [u.detach().requires_grad_(True) for u in t[:n_in]]
+            out, nxt = Fn.apply(*leaves)
+            return torch.autograd.grad([out, nxt], leaves, [t[n_in], t[n_in + 1]])
+
+        for i in range(3):
+            api_step(i)
+        barrier()
+        a0, a1 = ev(), ev()
+        a0.record()
+        for i in range(n_api):
+            api_step(i)
+        a1.record()
+        torch.cuda.synchronize()
+        eager_ms = a0.elapsed_time(a1) / n_api
+        graph_ms = None
+        try:
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                api_step(0)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            ga = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(ga):
+                keep_api = [api_step(i) for i in range(n_api)]
+            ga.replay()
+            torch.cuda.synchronize()
+            a0.record()
+            ga.replay()
+            a1.record()
+            torch.cuda.synchronize()
+            graph_ms = a0.elapsed_time(a1) / n_api
+            del keep_api, ga
+        except Exception as exc:
+            sys.stderr.write("bench.py: API graph capture failed (%s)\n" % exc)
+            torch.cuda.synchronize()
+        best = graph_ms if graph_ms is not None else eager_ms
+        value_api = {"value": B * T / (best * 1e-3) * (world if args.scaling == "weak" else 1), "unit": "tokens/s",
+                     "eager_ms_per_step": eager_ms, "graph_ms_per_step": graph_ms, "steps": n_api,
+                     "api": ("DFWFunction" if dfw else "LFWFunction") + ".apply + torch.autograd.grad, device-resident "
+                            "tensors; `value` is this rank's figure times the number of ranks"}
+
+    # ---- the decode step (BASELINE's second metric) in the same run -------------------------------
+    extra = None
+    if args.workload == "train":
+        Bd, Dd, Kd, ring, trips = WORKLOADS["decode"][0], 64, 64, 10, 100
+        gd = torch.Generator().manual_seed(args.seed + 7 + 1000 * rank)
+        loop = LFWDecodeLoop((torch.randn(Bd, Dd, Kd, generator=gd) * 0.1).to(dtype).to(dev), ring=ring)
+        loop.x.copy_(torch.randn(ring, Bd, 1, Dd, generator=gd).to(dtype))
+        loop.query.copy_((torch.randn(ring, Bd, 1, Kd, generator=gd) / 8).to(dtype))
+        loop.key.copy_((torch.randn(ring, Bd, 1, Kd, generator=gd) / 8).to(dtype))
+        # gates in (0, 1): with the literal N(0,1) gate a chained 16-bit state overflows after a few
+        # hundred steps (in the reference too); the step's cost does not depend on the values
+        loop.f_key.copy_(torch.sigmoid(torch.randn(ring, Bd, 1, Kd, generator=gd)).to(dtype))
+        if args.gates != "raw_f1":
+            loop.f.copy_(torch.sigmoid(torch.randn(ring, Bd, 1, Dd, generator=gd)).to(dtype))
+        loop.run_ring()                 # eager trip, then capture
+        loop.run_ring()
+        torch.cuda.synchronize()
+        d0, d1 = ev(), ev()
+        d0.record()
+        for _ in range(trips):
+            loop.run_ring()
+        d1.record()
+        torch.cuda.synchronize()
+        us = d0.elapsed_time(d1) * 1e3 / (trips * ring)
+        dbytes = 2 * (2 * Bd * Dd * Kd) + 2 * Bd * (2 * Dd + 3 * Kd) + 2 * Bd * Dd
+        peak_d, kind_d = measured_hbm_peak()
+        extra = {"decode": {
+            "us_per_step": us, "steps": trips * ring, "tokens_per_s": Bd / (us * 1e-6),
+            "achieved_gbs": dbytes / (us * 1e-6) / 1e9, "frac": dbytes / (us * 1e-6) / 1e9 / peak_d,
+            "peak": peak_d, "peak_kind": kind_d + " copy bandwidth", "algorithmic_bytes_per_step": dbytes,
+            "workload": "decode: B*H=%d, T=1, D=K=64, fp16 I/O, fp32 state arithmetic; %d chained steps, fresh "
+                        "inputs from a ring of %d slots (f_key = sigmoid(N(0,1))); the state is chained through two 67 MB "
+                        "buffers, so part of a step's output is still in the 126 MB L2 when the next step reads it "
+                        "(--workload decode times the step with nothing in L2)"
+                        % (Bd, trips * ring, ring),
+            "api": "t2fw_b200.decode.LFWDecodeLoop (torch.ops.lfw.decode_step, one CUDA-graph replay per %d steps)" % ring,
+            "finite": bool(torch.isfinite(loop.state).all().item())}}
+        del loop
+
+    # ---- strong scaling: the same rows split over the ranks (N > 1) -------------------------------
+    strong = None
+    if world > 1 and args.scaling == "weak" and not dfw and not decode:
+        r0, r1 = row_shard(B, world, rank)
+        sl = lambda t: t[r0:r1]
+
+        def strong_step(i):
+            j = i % n_sets
+            x, f, q, k, fk, s0, go, gs = [sl(t) for t in sets[j]]
+            cabi.lfw_forward(x, f, q, k, fk, s0, ckpt_every=C, out=sl(outs[j]), ckpt=sl(ckpts[j]), scratch=fscr)
+            cabi.lfw_backward(go, gs, x, f, q, k, fk, s0, sl(ckpts[j]), ckpt_every=C,
+                              grads=[sl(t) for t in grads[j]], scratch=bscr)
+
+        for i in range(3):
+            strong_step(i)
+        barrier()
+        gs_ = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gs_):
+            for i in range(args.steps):
+                strong_step(i)
+        gs_.replay()
+        barrier()
+        s0e, s1e = ev(), ev()
+        s0e.record()
+        gs_.replay()
+        s1e.record()
+        barrier()
+        sms = max_over_ranks(s0e.elapsed_time(s1e), dev)
+        strong = {"value": B * T * args.steps / (sms * 1e-3), "unit": "tokens/s", "ms_per_step": sms / args.steps,
+                  "rows_total": B, "rows_this_rank": r1 - r0, "steps": args.steps,
+                  "note": "the workload's %d batch*head rows split contiguously over %d GPUs, no collective" % (B, world)}
+
     # ---- end to end through the public API with host buffers -------------------------------
     e2e = None
     if not args.no_e2e:
@@ -678,13 +840,20 @@ def run_ours(args):
     else:
         which, alg, dur = "forward call (all kernels of t2fw_%s_forward)" % ("dfw" if dfw else "lfw"), fb, f_ms
     achieved = alg / (dur * 1e-3) / 1e9
-    # DRAM bytes (read + write) per call from the committed ncu captures of exactly this workload
-    # (profiles/): sum over the kernels of the timed call; None where no capture exists.
-    traffic = {("train", "backward"): 220.3e6, ("decode", "forward"): 37.0e6}.get(
-        (args.workload, which.split()[0]))
+    # DRAM bytes (read + write) per call, summed over the kernels of the call, from the ncu capture
+    # recorded beside the kernel versions it was taken on; None where no capture exists
+    traffic, traffic_src = None, None
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as fh:
+            tj = json.load(fh)
+        traffic = tj.get(args.workload, {}).get(which.split()[0])
+        traffic_src = {"captured_on_commit": tj.get("captured_on_commit"), "command": tj.get("command")}
+    except Exception:
+        pass
     roofline = {
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-        "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind + " copy bandwidth",
+        "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_src,
+        "peak_kind": peak_kind + " copy bandwidth",
         "kernel": which, "algorithmic_bytes_per_launch": alg, "avg_ms": dur,
         "fwd_ms": f_ms, "bwd_ms": b_ms, "split_timing": split_kind,
         "whole_step_frac": ((fb + (0 if decode else bb)) / ((f_ms + b_ms) * 1e-3) / 1e9) / peak,
@@ -701,10 +870,14 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "f32 state arithmetic, f16 I/O", "data": "synthetic",
         "config": dict(workload_config(args, B, T, D, K),
                        l2="inputs larger than L2: %d rotating input/output sets" % n_sets,
-                       ckpt_every=C, cuda_graph=graph is not None),
+                       ckpt_every=C, cuda_graph=graph is not None, flagged_rows=flagged),
         "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
-        "roofline": roofline, "cpu_baseline": cpu,
+        "roofline": roofline, "cpu_baseline": cpu, "value_api": value_api,
     }
+    if extra is not None:
+        line["extra"] = extra
+    if strong is not None:
+        line["strong"] = strong
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
