@@ -108,6 +108,35 @@ int t2fw_lfw_backward(const void *grad_output, const void *grad_state,
                       void *scratch, size_t scratch_bytes, void *stream);
 
 /*
+ * Fused decay-rule layer, d_head = 64 (additive; the reference has no counterpart: its wrapper
+ * "assumes the input is already gated", t2fw/functional_lfw.py:26-29, and leaves the head fold, the
+ * gate activation and the query scaling to the caller).
+ *
+ *   qkvg  [B, T, 4*H*64]  one row per (batch item, step): query | key | value | gate, each H*64
+ *                         wide with head h at columns 64h .. 64h+63 - the output of the layer's
+ *                         projection, read in place (no folded [B*H, T, 64] copies are made)
+ *   state [B*H, 64, 64]   initial state per (batch item, head), row index b*H + h
+ *   outputs [B, T, H*64]  heads already unfolded, ready for the output projection
+ *   ckpt_states [B*H, ceil(T/64), 64, 64]; the last slot is the next state
+ *
+ * Computes, per (b, h), the decay rule with  x = value,  forget gate 1,  query scaled by 1/8
+ * (= 1/sqrt(64)),  f_key = max(sigmoid(gate), 1/8).  The floor keeps every 32-step gate product
+ * inside the range of the chunked kernels, so this entry point never needs the scan fallback.
+ * The result equals t2fw_lfw_forward on the folded, activated tensors (rounded to the storage
+ * type) bit for bit.  16-bit dtypes only; all pointers 16-byte aligned (T2FW_ERR_UNSUPPORTED
+ * otherwise).  The backward returns d_qkvg [B, T, 4*H*64] (same layout, chain rule through the
+ * activations included) and d_state.
+ */
+size_t t2fw_lfw_fused_scratch_bytes(int64_t B, int64_t T, int64_t H, int dtype);
+int t2fw_lfw_fused_forward(const void *qkvg, const void *state, void *outputs, void *ckpt_states,
+                           int64_t B, int64_t T, int64_t H, int dtype,
+                           void *scratch, size_t scratch_bytes, void *stream);
+int t2fw_lfw_fused_backward(const void *grad_output, const void *grad_state, const void *qkvg,
+                            const void *state, const void *ckpt_states, void *d_qkvg, void *d_state,
+                            int64_t B, int64_t T, int64_t H, int dtype,
+                            void *scratch, size_t scratch_bytes, void *stream);
+
+/*
  * Delta rule forward:  o_t = S_{t-1} q_t ,  delta_t = v_t - S_{t-1} k_t ,
  *                      S_t = S_{t-1} + delta_t k_t^T.
  * Replaces torch.ops.dfw.forward = lfw_forward (t2fw/csrc/dfw.cpp:27-39) and its kernel

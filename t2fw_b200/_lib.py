@@ -22,6 +22,7 @@ EXPORTS = (
     "t2fw_lfw_forward", "t2fw_lfw_backward", "t2fw_dfw_forward", "t2fw_dfw_backward",
     "t2fw_dfw_forward_ws", "t2fw_dfw_forward_scratch_bytes",
     "t2fw_dfw_backward_noalloc_max_elems", "t2fw_dfw_backward_noalloc",
+    "t2fw_lfw_fused_scratch_bytes", "t2fw_lfw_fused_forward", "t2fw_lfw_fused_backward",
 )
 
 _core = None
@@ -73,6 +74,12 @@ def load_core():
     lib.t2fw_dfw_backward_noalloc_max_elems.argtypes = []
     lib.t2fw_dfw_backward_noalloc.restype = _int
     lib.t2fw_dfw_backward_noalloc.argtypes = [_vp] * 10 + [_i64] * 4 + [_int, _vp]
+    lib.t2fw_lfw_fused_scratch_bytes.restype = _sz
+    lib.t2fw_lfw_fused_scratch_bytes.argtypes = [_i64, _i64, _i64, _int]
+    lib.t2fw_lfw_fused_forward.restype = _int
+    lib.t2fw_lfw_fused_forward.argtypes = [_vp] * 4 + [_i64] * 3 + [_int, _vp, _sz, _vp]
+    lib.t2fw_lfw_fused_backward.restype = _int
+    lib.t2fw_lfw_fused_backward.argtypes = [_vp] * 7 + [_i64] * 3 + [_int, _vp, _sz, _vp]
     _core = lib
     return lib
 

@@ -211,6 +211,60 @@ int t2fw_lfw_backward(const void *grad_output, const void *grad_state, const voi
                            static_cast<cudaStream_t>(stream));
 }
 
+// ---- fused decay-rule layer (heads read in place from the projection output) -------------------
+static int check_fused(int64_t B, int64_t T, int64_t H, int dtype) {
+  T2FW_CHECK_ARG(B > 0 && T > 0 && H > 0, "sizes must be positive (B=%lld T=%lld H=%lld)", (long long)B,
+                 (long long)T, (long long)H);
+  if (dtype != T2FW_F16 && dtype != T2FW_BF16) {
+    set_error("fused layer: 16-bit storage only (dtype %d)", dtype);
+    return T2FW_ERR_UNSUPPORTED;
+  }
+  return T2FW_OK;
+}
+
+size_t t2fw_lfw_fused_scratch_bytes(int64_t B, int64_t T, int64_t H, int dtype) {
+  if (B <= 0 || T <= 0 || H <= 0 || (dtype != T2FW_F16 && dtype != T2FW_BF16)) return 0;
+  return lfw_fused_scratch_bytes(B, T, (int)H);
+}
+
+int t2fw_lfw_fused_forward(const void *qkvg, const void *state, void *outputs, void *ckpt_states, int64_t B,
+                           int64_t T, int64_t H, int dtype, void *scratch, size_t scratch_bytes, void *stream) {
+  int rc = check_fused(B, T, H, dtype);
+  if (rc != T2FW_OK) return rc;
+  T2FW_CHECK_ARG(qkvg && state && outputs && ckpt_states, "null pointer argument");
+  const size_t need = lfw_fused_scratch_bytes(B, T, (int)H);
+  if (scratch == nullptr || scratch_bytes < need) {
+    set_error("lfw fused forward needs %zu bytes of scratch, got %zu", need, scratch_bytes);
+    return T2FW_ERR_SCRATCH;
+  }
+  if (!aligned16({qkvg, state, outputs, ckpt_states, scratch})) {
+    set_error("lfw fused forward: all pointers must be 16-byte aligned");
+    return T2FW_ERR_UNSUPPORTED;
+  }
+  return lfw_fused_forward(qkvg, state, outputs, ckpt_states, B, T, (int)H, dtype, scratch,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int t2fw_lfw_fused_backward(const void *grad_output, const void *grad_state, const void *qkvg, const void *state,
+                            const void *ckpt_states, void *d_qkvg, void *d_state, int64_t B, int64_t T, int64_t H,
+                            int dtype, void *scratch, size_t scratch_bytes, void *stream) {
+  int rc = check_fused(B, T, H, dtype);
+  if (rc != T2FW_OK) return rc;
+  T2FW_CHECK_ARG(grad_output && grad_state && qkvg && state && ckpt_states && d_qkvg && d_state,
+                 "null pointer argument");
+  const size_t need = lfw_fused_scratch_bytes(B, T, (int)H);
+  if (scratch == nullptr || scratch_bytes < need) {
+    set_error("lfw fused backward needs %zu bytes of scratch, got %zu", need, scratch_bytes);
+    return T2FW_ERR_SCRATCH;
+  }
+  if (!aligned16({grad_output, grad_state, qkvg, state, ckpt_states, d_qkvg, d_state, scratch})) {
+    set_error("lfw fused backward: all pointers must be 16-byte aligned");
+    return T2FW_ERR_UNSUPPORTED;
+  }
+  return lfw_fused_backward(grad_output, grad_state, qkvg, state, ckpt_states, d_qkvg, d_state, B, T, (int)H, dtype,
+                            scratch, static_cast<cudaStream_t>(stream));
+}
+
 int t2fw_dfw_forward(const void *q, const void *k, const void *v, const void *state,
                      void *outputs, void *final_state, void *delta, int64_t B, int64_t T,
                      int64_t D, int64_t M, int dtype, void *stream) {

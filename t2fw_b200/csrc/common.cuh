@@ -116,10 +116,13 @@ int lfw_blocked_backward(const void *go, const void *gs, const void *x, const vo
                          const void *k, const void *fk, const void *state, const void *ckpt, void *dx,
                          void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B, int64_t T,
                          int64_t D, int64_t K, int dtype, void *scratch, cudaStream_t st);
-// tcgen05 versions of the two chunk-local kernels (same scratch layout as the mma.sync ones)
-int lfw_chunk_local_umma(bool backward, const void *val_d, const void *gate_d, const void *val_k,
-                         const void *gate_k, float *M, float *Ac, float *Gc, int *flags, int64_t B,
-                         int64_t T, int dtype, cudaStream_t st);
+// fused layer form of the chunked path: qkvg [B][T][4*H*64] read in place (lfw_c64_host.cu)
+size_t lfw_fused_scratch_bytes(int64_t B, int64_t T, int H);
+int lfw_fused_forward(const void *qkvg, const void *state, void *out, void *ckpt, int64_t B, int64_t T, int H,
+                      int dtype, void *scratch, cudaStream_t st);
+int lfw_fused_backward(const void *go, const void *gs, const void *qkvg, const void *state, const void *ckpt,
+                       void *d_qkvg, void *ds, int64_t B, int64_t T, int H, int dtype, void *scratch,
+                       cudaStream_t st);
 int lfw_chunk_umma_status();
 bool lfw_decode_bulk_supported(int64_t B, int64_t D, int64_t K, int dtype);
 int lfw_decode_bulk_forward(const void *x, const void *f, const void *q, const void *k,

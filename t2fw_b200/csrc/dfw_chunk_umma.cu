@@ -28,37 +28,6 @@ using namespace chunk;
 int lfw_chunk_status_ptr(int **out);   // lfw_c64_local.cu
 int lfw_chunk_sm_count(int *out);
 
-#ifdef T2FW_DFW_PROFILE
-__device__ long long g_dfw_prof[48];
-#define PROF(i)                                                    \
-  do {                                                             \
-    if (threadIdx.x == 0 && blockIdx.x == 0) {                     \
-      const long long now_ = clock64();                            \
-      g_dfw_prof[i] += now_ - tprev;                               \
-      tprev = now_;                                                \
-    }                                                              \
-  } while (0)
-#define PROFB(i)                                                   \
-  do {                                                             \
-    if (threadIdx.x == 0 && blockIdx.x == 0) {                     \
-      const long long now_ = clock64();                            \
-      g_dfw_prof[16 + i] += now_ - tprev;                          \
-      tprev = now_;                                                \
-    }                                                              \
-  } while (0)
-#define PROFP(i)                                                   \
-  do {                                                             \
-    if (threadIdx.x == 0 && blockIdx.x == 0) {                     \
-      const long long now_ = clock64();                            \
-      g_dfw_prof[32 + i] += now_ - tprev;                          \
-      tprev = now_;                                                \
-    }                                                              \
-  } while (0)
-#else
-#define PROF(i)
-#define PROFB(i)
-#define PROFP(i)
-#endif
 
 namespace {
 
@@ -183,18 +152,13 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
     if (!s_fail && !umma::mbar_wait(bar, par)) s_fail = 1;
   };
 
-#ifdef T2FW_DFW_PROFILE
-  long long tprev = clock64();
-#endif
   for (int64_t c = 0; c < nc; ++c) {
     const int64_t t0 = c * kC;
     const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
     const size_t base = ((size_t)b * T_ + t0) * kDim;
-    PROF(0);
     if (!umma::mbar_wait(&bar_raw, par)) s_fail = 1;    // also after a failure: no copy stays in flight
     __syncthreads();
     if (s_fail) break;
-    PROF(1);
 
     // ---- raw blocks -> TF32 tiles, in pieces of 4 consecutive columns (1024 per block) -------------
 #pragma unroll
@@ -228,10 +192,8 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
       }
     }
     if (c > 0) copy_out_o(c - 1);     // staged by the previous chunk, ordered by the barrier above
-    PROF(2);
     umma::fence_async_smem();
     sync_all();                       // tiles complete (the S tile since the end of the last chunk)
-    PROF(3);
 
     // ---- first round: W S^T (lane set A, columns 0-63) and Q [K; S]^T (lane set B, all columns),
     //      one issuing thread each ---------------------------------------------------------------------
@@ -245,10 +207,8 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
       umma::mma_commit(&bar_m1);
     }
     if (warp == kCopyWarp && lane == 0 && c + 1 < nc) issue_raw(c + 1);
-    PROF(4);
     wait_bar(&bar_m1);
     umma::fence_after_sync();
-    PROF(5);
     {
       // lane set A: Dl = U - W S^T (row t = `row`, columns d);  lane set B: scores (row t, columns i)
       float v[32];
@@ -272,10 +232,8 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
           *reinterpret_cast<float4 *>(sm + oAs + umma::tile_off(row, c0 + j, kC)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
       }
     }
-    PROF(6);
     umma::fence_async_smem();
     sync_all();
-    PROF(7);
     // ---- second round: O += A Dl, S += Dl^T K ---------------------------------------------------------
     if (lane == 0 && warp < 2) {
       const uint32_t idesc = umma::make_idesc_tf32(kDim, kDim, false, false);
@@ -295,10 +253,8 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
       if (r < nvalid)
         *reinterpret_cast<float4 *>(delta + base + (size_t)r * kDim + c4) = *reinterpret_cast<const float4 *>(sm + oStgD + r * kRow32 + c4 * 4);
     }
-    PROF(8);
     wait_bar(&bar_m2);
     umma::fence_after_sync();
-    PROF(9);
     {
       // lane set B: O (row t, columns d) -> staging;  lane set A: S (row d, columns m) -> TF32 tile
       float v[32];
@@ -324,7 +280,6 @@ dfw_chunk_fwd_umma_kernel(const T *__restrict__ q, const T *__restrict__ k, cons
     }
     par ^= 1u;
     umma::fence_before_sync();   // accumulator reads are ordered before the next chunk's MMAs
-    PROF(10);
   }
   __syncthreads();
   if (!s_fail && nc > 0) copy_out_o(nc - 1);
@@ -438,18 +393,13 @@ dfw_chunk_bwd_seq_umma_kernel(const T *__restrict__ go, const T *__restrict__ gs
   auto wait_bar = [&](uint64_t *bar) {
     if (!s_fail && !umma::mbar_wait(bar, par)) s_fail = 1;
   };
-#ifdef T2FW_DFW_PROFILE
-  long long tprev = clock64();
-#endif
   for (int64_t c = nc - 1; c >= 0; --c) {
     const int64_t t0 = c * kC;
     const int nvalid = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
     const size_t base = ((size_t)b * T_ + t0) * kDim, tile = ((size_t)b * nc + c) * kC * kDim;
-    PROFB(0);
     if (!umma::mbar_wait(&bar_raw, par)) s_fail = 1;    // also after a failure: no copy stays in flight
     __syncthreads();
     if (s_fail) break;
-    PROFB(1);
 
     // ---- raw blocks -> TF32 tiles.  A warp covers 8 column pieces x 4 steps per instruction. ---------
 #pragma unroll
@@ -485,10 +435,8 @@ dfw_chunk_bwd_seq_umma_kernel(const T *__restrict__ go, const T *__restrict__ gs
         uv[j] = u4.x; uv[j + 1] = u4.y; uv[j + 2] = u4.z; uv[j + 3] = u4.w;
       }
     }
-    PROFB(2);
     umma::fence_async_smem();
     sync_all();                       // tiles complete (the R tile since the end of the chunk before)
-    PROFB(3);
 
     // ---- first round, one issuing thread per product -------------------------------------------------
     if (lane == 0 && warp < 3) {
@@ -508,10 +456,8 @@ dfw_chunk_bwd_seq_umma_kernel(const T *__restrict__ go, const T *__restrict__ gs
       umma::mma_commit(&bar_m1);
     }
     if (warp == kCopyWarp && lane == 0 && c > 0) issue_raw(c - 1);
-    PROFB(4);
     wait_bar(&bar_m1);
     umma::fence_after_sync();
-    PROFB(5);
     {
       // lane set A: E = Ub + Wb R_end^T (row t = `row`, columns d);  lane set B: S0 (row d, columns m)
       float v[32];
@@ -531,10 +477,8 @@ dfw_chunk_bwd_seq_umma_kernel(const T *__restrict__ go, const T *__restrict__ gs
         store_t(ScT + tile, v);
       }
     }
-    PROFB(6);
     umma::fence_async_smem();
     sync_all();
-    PROFB(7);
     // ---- second round: R -= E^T K ----------------------------------------------------------------------
     if (tid == 0) {
       const uint32_t idesc = umma::make_idesc_tf32(kDim, kDim, false, false);
@@ -557,10 +501,8 @@ dfw_chunk_bwd_seq_umma_kernel(const T *__restrict__ go, const T *__restrict__ gs
         *reinterpret_cast<uint2 *>(dv + base + (size_t)r * kDim + c4) = pk;
       }
     }
-    PROFB(8);
     wait_bar(&bar_m2);
     umma::fence_after_sync();
-    PROFB(9);
     {
       // R_start (row d, columns m) = R_end of the chunk before, or the state gradient at the start
       float v[32];
@@ -580,7 +522,6 @@ dfw_chunk_bwd_seq_umma_kernel(const T *__restrict__ go, const T *__restrict__ gs
     }
     par ^= 1u;
     umma::fence_before_sync();   // accumulator reads are ordered before the next chunk's MMAs
-    PROFB(10);
   }
   if (s_fail && tid == 0) atomicExch(status, 1);
   sync_all();
@@ -723,14 +664,9 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
   }
   uint32_t par = 0;
   uint32_t tb = 0, tl = 0;
-#ifdef T2FW_DFW_PROFILE
-  long long tprev = clock64();
-#endif
   for (; ci < total; ci += gridDim.x) {
-    PROFP(0);
     umma::fence_async_smem();
     sync_all();                   // tiles complete; staging rows of the chunk before complete
-    PROFP(1);
     tb = tmem_slot;
     tl = umma::tmem_addr(tb, 32 * qd, 0);
     if (s_fail) break;
@@ -752,13 +688,10 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
     }
     const int64_t next = ci + gridDim.x;
     const bool has_next = next < total;
-    PROFP(2);
     if (has_next) load_a(next);
     if (prev >= 0) copy_out(prev);
-    PROFP(3);
     if (!umma::mbar_wait(&bar_m1, par)) s_fail = 1;
     umma::fence_after_sync();
-    PROFP(4);
     {
       // lane set B: dO Dl^T (row t, columns i) -> X1 and X1^T;  lane set A: -X2 (row t, columns i) -> -Y
       float v[32];
@@ -784,10 +717,8 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
         }
       }
     }
-    PROFP(5);
     umma::fence_async_smem();
     sync_all();
-    PROFP(6);
     // ---- second round --------------------------------------------------------------------------------
     if (lane == 0 && warp < 2) {
       const uint32_t idesc = umma::make_idesc_tf32(kDim, kDim, false, false);
@@ -808,15 +739,12 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
       }
       umma::mma_commit(&bar_m2);
     }
-    PROFP(7);
     if (has_next) {                   // the first round has finished with these tiles
       store_a();
       load_b(next);
     }
-    PROFP(8);
     if (!s_fail && !umma::mbar_wait(&bar_m2, par)) s_fail = 1;
     umma::fence_after_sync();
-    PROFP(9);
     {
       // lane set A: d_key, lane set B: d_query (row t, columns m) -> padded 16-bit staging rows
       float v[32];
@@ -831,12 +759,10 @@ dfw_chunk_bwd_par_umma_kernel(const T *__restrict__ go, const T *__restrict__ q,
       for (int j = 0; j < 4; ++j)
         *reinterpret_cast<uint4 *>(stg + 16 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
     }
-    PROFP(10);
     if (has_next) {                   // both rounds have finished with the tiles
       store_sr();
       store_trans();
     }
-    PROFP(11);
     prev = ci;
     par ^= 1u;
     umma::fence_before_sync();
@@ -938,8 +864,3 @@ int dfw_chunk_bwd_par_umma(const void *go, const void *q, const void *k, const v
 
 }  // namespace t2fw
 
-#ifdef T2FW_DFW_PROFILE
-extern "C" int t2fw_debug_dfw_prof(long long *out) {
-  return (int)cudaMemcpyFromSymbol(out, t2fw::g_dfw_prof, sizeof(long long) * 48);
-}
-#endif

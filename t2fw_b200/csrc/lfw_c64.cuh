@@ -152,6 +152,21 @@ __device__ __forceinline__ bool elect_one() {
 // warp index as a value the compiler knows to be the same in all lanes
 __device__ __forceinline__ int uniform_warp_idx() { return __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0); }
 
+// Work item -> (problem row, chunk) and problem row -> (batch item, head) with 32-bit divisions
+// (the launchers refuse problems with 2^31 or more chunks or rows).
+struct Item {
+  int bh, c, b, h;
+};
+__device__ __forceinline__ Item split_item(int64_t ci, int64_t nc, int heads) {
+  Item it;
+  const uint32_t u = (uint32_t)ci, n = (uint32_t)nc;
+  it.bh = (int)(u / n);
+  it.c = (int)(u - (uint32_t)it.bh * n);
+  it.b = (int)((uint32_t)it.bh / (uint32_t)heads);
+  it.h = it.bh - it.b * heads;
+  return it;
+}
+
 __device__ __forceinline__ void sync_all() {
   umma::fence_before_sync();
   __syncthreads();

@@ -31,6 +31,7 @@
 #include <type_traits>
 
 #include "lfw_c64.cuh"
+#include "seq_layout.cuh"
 
 namespace t2fw {
 
@@ -39,19 +40,6 @@ using namespace c64;
 int lfw_chunk_status_ptr(int **out);   // lfw_c64_local.cu
 int lfw_chunk_sm_count(int *out);
 
-#ifdef T2FW_C64_PROFILE
-__device__ long long g_c64_prof[32];
-#define PROF(i)                                                    \
-  do {                                                             \
-    if (threadIdx.x == 96 && blockIdx.x == 0) {                    \
-      const long long now_ = clock64();                            \
-      g_c64_prof[i] += now_ - tprev;                               \
-      tprev = now_;                                                \
-    }                                                              \
-  } while (0)
-#else
-#define PROF(i) do { } while (0)
-#endif
 
 namespace {
 
@@ -74,8 +62,8 @@ constexpr int oFixMask = oFixVal + kFixCap * 4;     // [64] one bit per step
 constexpr int oFixRow = oFixMask + kDim * 8;        // [16 warps][2][64] floats: operand rows of a tiny-gate entry
 constexpr int oS0L = oFixRow + 16 * 2 * kDim * 4;   // start state of the chunk, [64][kS0Ld]
 constexpr int oRL = oS0L + kDim * kS0Ld;            // end state gradient of the chunk, [64][kRLd]
-constexpr int oRaw = oRL + kDim * kRLd;             // x, f, q, k, fk, dO
-constexpr int kSmemB = oRaw + 6 * kRawBytes + 1024; // + slack for the 1024-byte alignment
+constexpr int oRaw = oRL + kDim * kRLd;             // x, f, q, k, fk, dO, and (fused layer) the gate pre-activations
+constexpr int kSmemB = oRaw + 7 * kRawBytes + 1024; // + slack for the 1024-byte alignment
 static_assert(oRaw % 128 == 0 && oFixMask % 8 == 0 && oS0L % 16 == 0 && oRL % 16 == 0, "alignment");
 static_assert(kSmemB + 128 <= 227 * 1024, "shared memory limit");
 
@@ -86,12 +74,10 @@ constexpr int kTmemCols = 512;
 
 template <typename T>
 __global__ void __launch_bounds__(kThreadsB, 1)
-lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *__restrict__ f,
-                   const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ fk,
-                   const T *__restrict__ state, const T *__restrict__ ckpt, const float *__restrict__ Rend,
-                   T *__restrict__ dx, T *__restrict__ df, T *__restrict__ dq, T *__restrict__ dk,
-                   T *__restrict__ dfk, int *__restrict__ rowflag, int *__restrict__ status, int64_t T_,
-                   int64_t nc, int64_t total) {
+lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ state, const T *__restrict__ ckpt,
+                   const float *__restrict__ Rend, const seq::Out<T> dx, const seq::Out<T> df, const seq::Out<T> dq,
+                   const seq::Out<T> dk, const seq::Out<T> dfk, int *__restrict__ rowflag, int *__restrict__ status,
+                   int64_t T_, int64_t nc, int64_t total) {
   extern __shared__ __align__(1024) unsigned char sm_raw[];
   unsigned char *sm = sm_raw + ((1024u - (umma::smem_u32(sm_raw) & 1023u)) & 1023u);
   __shared__ __align__(8) uint64_t barRaw, barZ, barM;
@@ -118,24 +104,28 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
   float *fix_row = reinterpret_cast<float *>(sm + oFixRow) + warp * 2 * kDim;
   T *raw = reinterpret_cast<T *>(sm + oRaw);     // [6][64][64]: x, f, q, k, fk, dO
 
-  auto issue_raw = [&](int64_t ci) {     // thread 0 only
-    const int64_t b = ci / nc, c = ci % nc, t0 = c * kC;
-    const int nv = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
-    const uint32_t vb = (uint32_t)nv * kDim * sizeof(T);
-    const size_t base = ((size_t)b * T_ + t0) * kDim;
+  // tensors: 0 x, 1 f, 2 q, 3 k, 4 fk, 5 dO
+  const bool unit_forget = (mp.flags & seq::kUnitForget) != 0;
+  auto issue_raw = [&](int64_t ci) {     // thread 0 only: one copy per tensor
+    const Item w = split_item(ci, nc, mp.heads);
+    const int row = (int)(w.b * T_ + w.c * kC), hc = w.h * kDim;
+    const int nv = (int)((T_ - (int64_t)w.c * kC < kC) ? T_ - (int64_t)w.c * kC : kC);
     unsigned char *r = sm + oRaw;
-    acp::mbar_expect_tx(&barRaw, 6 * vb);
-    acp::bulk_g2s(r, x + base, vb, &barRaw);
-    acp::bulk_g2s(r + kRawBytes, f + base, vb, &barRaw);
-    acp::bulk_g2s(r + 2 * kRawBytes, q + base, vb, &barRaw);
-    acp::bulk_g2s(r + 3 * kRawBytes, k + base, vb, &barRaw);
-    acp::bulk_g2s(r + 4 * kRawBytes, fk + base, vb, &barRaw);
-    acp::bulk_g2s(r + 5 * kRawBytes, go + base, vb, &barRaw);
+    const uint32_t per = (mp.flags & seq::kContiguous) ? (uint32_t)nv * kDim * sizeof(T) : (uint32_t)kRawBytes;
+    const bool sigm = (mp.flags & seq::kSigmoidGate) != 0;
+    acp::mbar_expect_tx(&barRaw, ((unit_forget ? 5u : 6u) + (sigm ? 1u : 0u)) * per);
+#pragma unroll
+    for (int i = 0; i < 6; ++i)
+      if (!(i == 1 && unit_forget)) seq::fetch_block<T>(mp, i, r + i * kRawBytes, row, hc, nv, &barRaw);
+    // a second copy of the gate tensor: block 4 is turned into gate values in place, this one keeps
+    // the pre-activations for the derivative of the activation
+    if (sigm) seq::fetch_block<T>(mp, 4, r + 6 * kRawBytes, row, hc, nv, &barRaw);
   };
   // start state (16-bit, 8 KB) and end state gradient (fp32, 16 KB) of a chunk into the padded
   // landing zones: three 16-byte asynchronous copies per thread
   auto issue_state = [&](int64_t ci) {   // every thread
-    const int64_t b = ci / nc, c = ci % nc;
+    const Item w = split_item(ci, nc, mp.heads);
+    const int64_t b = w.bh, c = w.c;
     const T *s0p = (c == 0) ? state + (size_t)b * kDim * kDim : ckpt + ((size_t)b * nc + (c - 1)) * kDim * kDim;
     const float *rp = Rend + (size_t)ci * kDim * kDim;
     cp_async16(sm + oS0L + (tid >> 3) * kS0Ld + (tid & 7) * 16, s0p + (tid >> 3) * kDim + (tid & 7) * 8);
@@ -155,6 +145,7 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
     s_fail = 0;
   }
   if (warp == 0) umma::tmem_alloc(&tmem_slot, kTmemCols);
+  if (unit_forget) seq::fill_block(raw + kC * kDim, 1.f, tid, kThreadsB);   // constant d-side gate, never loaded
   sync_all();
   const uint32_t tb = __shfl_sync(0xffffffffu, tmem_slot, 0);
   const uint32_t tl = umma::tmem_addr(tb, 32 * q4, 0);
@@ -172,26 +163,28 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
   for (int i = 0; i < 4; ++i) dT[i] = desc_sw128(aT + i * kTile);
   uint32_t pz = 0, pm_par = 0;   // mbarrier phase parities
 
-#ifdef T2FW_C64_PROFILE
-  long long tprev = clock64();
-#endif
   uint32_t it = 0;
   for (int64_t ci = blockIdx.x; ci < total; ci += gridDim.x, ++it) {
-    const int64_t b = ci / nc, c = ci % nc, t0c = c * kC;
+    const Item wi = split_item(ci, nc, mp.heads);
+    const int64_t b = wi.bh, c = wi.c, t0c = c * kC;
     const int nvalid = (int)((T_ - t0c < kC) ? T_ - t0c : kC);
-    PROF(0);
-    const size_t base = ((size_t)b * T_ + t0c) * kDim;
+    const int64_t row0 = wi.b * T_ + t0c;      // first row of the chunk in the 2-D sequence arrays
+    const int hcol = wi.h * kDim;
 
     if (!acp::mbar_wait(&barRaw, it & 1u)) s_fail = 1;
     if (tid == 0) raw_pending = false;
     cp_async_wait_all();       // this thread's share of the chunk's start state and end gradient
     __syncthreads();
     if (s_fail) break;
+    if ((mp.flags & seq::kSigmoidGate) || mp.q_scale != 1.f) {      // fused layer: activations applied here
+      if (mp.flags & seq::kSigmoidGate) seq::sigmoid_gate_block(raw + 4 * kC * kDim, tid, kThreadsB);
+      if (mp.q_scale != 1.f) seq::scale_block(raw + 2 * kC * kDim, mp.q_scale, tid, kThreadsB);
+      __syncthreads();
+    }
     if (nvalid < kC) {      // partial chunk: identity steps beyond the valid ones
       pad_raw_tail<T>(raw, 6, (1u << 1) | (1u << 4), nvalid, tid, kThreadsB);
       __syncthreads();
     }
-    PROF(1);
 
 #pragma unroll 1
     for (int ph = 0; ph < 2; ++ph) {
@@ -208,7 +201,6 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
       float g[16];
       qtot[(gsw * 4 + tq) * kDim + feat] = load_gates16<T>(raw + (gsw ? blk_gw : blk_go) * kC * kDim + feat, tq, g);
       __syncthreads();
-      PROF(2);
       {
         const float *qt = qtot + gsw * 4 * kDim + feat;
         const float carry = tq == 0 ? qt[kDim] : tq == 3 ? qt[2 * kDim] : 1.f;
@@ -236,7 +228,6 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
         }
       }
       __syncthreads();
-      PROF(3);
 
       // ---- stage 2: operands ----
       {   // other side, time-major tiles in shared memory: this thread = four features, steps t and t + 32
@@ -260,7 +251,6 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
           *reinterpret_cast<float4 *>(t0p + 3 * kTile + o) = rna4(mul4(v, oc_ref));
         }
       }
-      PROF(14);
       {   // own side, feature-major A operands in tensor memory: row `own`, steps c0 .. c0 + 7
         const T *r_m = raw + blk_mw * kC * kDim + c0 * kDim + own, *r_v = raw + blk_vw * kC * kDim + c0 * kDim + own;
         const float4 p0 = *reinterpret_cast<const float4 *>(pmT + own * kPmLd + c0);
@@ -310,10 +300,8 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
         bndp[cg * kDim + own] = acc;
       }
       umma::tmem_st_wait();
-      PROF(4);
       umma::fence_async_smem();
       sync_all();       // operands complete; in the second pass the raw blocks and the state blocks are consumed
-      PROF(5);
 
       // ---- first MMA round.  A product is a chain of eight dependent instructions (one per 8
       //      contraction columns, accumulating in place); the tensor core executes instructions in
@@ -352,7 +340,6 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
       if (!umma::mbar_wait(&barZ, pz)) s_fail = 1;
       pz ^= 1u;
       umma::fence_after_sync();
-      PROF(6);
       {
         const int t = own, s0 = 32 * h + 8 * part;
         float v[8];
@@ -366,11 +353,9 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
 #pragma unroll
         for (int j = 0; j < 8; ++j) *reinterpret_cast<float *>(t1p + toff(s0 + j, t)) = v[j];
       }
-      PROF(7);
       umma::fence_async_smem();
       sync_all();
       if (s_fail) break;
-      PROF(8);
 
       // ---- second MMA round: TQ2 = Vw_mid Z^T, T2 = Mw_mid Z, four interleaved chains ----
       if (warp == 0) {
@@ -427,9 +412,7 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
           __syncwarp();
         }
       }
-      PROF(9);
       __syncthreads();      // fix_val, bndp visible
-      PROF(10);
 
       // ---- feature-major epilogue: this thread = row `own`, steps c0 .. c0 + 7 ----
       {
@@ -445,12 +428,6 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
 #pragma unroll
         for (int r = 0; r < 8; ++r) bnd += bndp[r * kDim + own];
         const unsigned m8 = (unsigned)((fix_mask[own] >> c0) & 0xffull);
-        float gr[8], ip[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          ip[j] = __fdividef(1.f, pmv[j + 1]);
-          gr[j] = pmv[j] * ip[j];                       // 1 / gate
-        }
         // own-side operand values: both lane sets hold all 64 columns, the load names one range per warp
         float mw[8], vw[8];
         {
@@ -469,7 +446,6 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
         if (!umma::mbar_wait(&barM, pm_par)) s_fail = 1;
         pm_par ^= 1u;
         umma::fence_after_sync();
-        PROF(11);
         float tq1[8], tq2[8], t2v[8], t7v[8];
         umma::tmem_ld8(tl + cTQ1 + 8 * part, tq1);
         umma::tmem_ld8(tl + cTQ2 + 8 * part, tq2);
@@ -480,7 +456,7 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           dmu[j] = pmv[j + 1] * (tq1[j] + tq2[j]);
-          ddv[j] = (t2v[j] + t7v[j]) * ip[j];
+          ddv[j] = __fdividef(t2v[j] + t7v[j], pmv[j + 1]);
           sa[j] = mw[j] * tq1[j];
           sb[j] = mw[j] * tq2[j] - vw[j] * t2v[j];
           pre[j] = vw[j] * t7v[j];
@@ -514,24 +490,36 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
               for (int e = 0; e < n_fix; ++e)
                 if (fix_code[e] == (((c0 + j) << 8) | own)) sb[j] = fix_val[e];
         }
-        // 16 consecutive features of one step are 32 contiguous bytes: the results go straight out
-        T *o_mu = (ph ? nullptr : dq) , *o_dv = ph ? dx : dk, *o_gt = ph ? df : dfk;
+        // 16 consecutive features of one step are 32 contiguous bytes: the results go straight out.
+        // Fused layer: the query was scaled on the way in, and the gate tensor holds pre-activations
+        // (gate = max(sigmoid(g), 1/8)), so the chain rule is finished here.
+        const seq::Out<T> &o_dv = ph ? dx : dk, &o_gt = ph ? df : dfk;
+        const bool sig = ph == 0 && (mp.flags & seq::kSigmoidGate);
+        const T *r_gate = raw + 6 * kC * kDim + c0 * kDim + own;     // pre-activations
+        // element pointers of step c0; one row pitch further per step
+        T *p_mu = dq.p + (size_t)(row0 + c0) * dq.ld + dq.col + hcol + own;
+        T *p_dv = o_dv.p + (size_t)(row0 + c0) * o_dv.ld + o_dv.col + hcol + own;
+        T *p_gt = o_gt.p == nullptr ? nullptr : o_gt.p + (size_t)(row0 + c0) * o_gt.ld + o_gt.col + hcol + own;
+        const int64_t ld_mu = dq.ld, ld_dv = o_dv.ld, ld_gt = o_gt.ld;
+        const float qs = mp.q_scale;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const int t = c0 + j;
           const float H = sa[j] + sb[j] + pre[j] + base_h;
-          if (t < nvalid) {
-            const size_t o = base + (size_t)t * kDim + own;
-            if (ph == 0) o_mu[o] = (T)dmu[j];
-            o_dv[o] = (T)ddv[j];
-            o_gt[o] = (T)(H * gr[j]);
+          if (c0 + j < nvalid) {
+            if (ph == 0) p_mu[j * ld_mu] = (T)(dmu[j] * qs);
+            p_dv[j * ld_dv] = (T)ddv[j];
+            float dg = H * __fdividef(pmv[j], pmv[j + 1]);      // H / gate
+            if (sig) {      // d gate / d pre-activation, from the pre-activation itself in fp32
+              const float e = __expf(-Elem<T>::ld(r_gate + j * kDim));
+              const float sg = __fdividef(1.f, 1.f + e);
+              dg *= sg > seq::kGateFloor ? sg * sg * e : 0.f;      // s (1 - s) = s^2 e^{-g}
+            }
+            if (p_gt != nullptr) p_gt[j * ld_gt] = (T)dg;
           }
         }
       }
-      PROF(12);
       sync_all();
       if (s_fail) break;
-      PROF(13);
     }
     if (s_fail) break;
   }
@@ -544,46 +532,35 @@ lfw_c64_bwd_kernel(const T *__restrict__ go, const T *__restrict__ x, const T *_
   if (warp == 0) umma::tmem_dealloc(tb, kTmemCols);
 }
 
-bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-
 }  // namespace
 
-// Returns T2FW_ERR_UNSUPPORTED (without launching) if a pointer is not 16-byte aligned.
-int lfw_c64_backward_main(const void *go, const void *x, const void *f, const void *q, const void *k,
-                          const void *fk, const void *state, const void *ckpt, const float *Rend, void *dx,
-                          void *df, void *dq, void *dk, void *dfk, int *rowflag, int64_t B, int64_t T_,
-                          int dtype, cudaStream_t st) {
-  if (!(aligned16(go) && aligned16(x) && aligned16(f) && aligned16(q) && aligned16(k) && aligned16(fk) &&
-        aligned16(state) && aligned16(ckpt) && aligned16(Rend) && aligned16(dx) && aligned16(df) &&
-        aligned16(dq) && aligned16(dk) && aligned16(dfk)))
-    return T2FW_ERR_UNSUPPORTED;
+// mp: tensor maps of x, f, q, k, fk, dO; outs: dx, df, dq, dk, dfk (pointer, row pitch, column) - df may be null.
+int lfw_c64_backward_main(const seq::Maps &mp, const void *state, const void *ckpt, const float *Rend,
+                          void *const outs[5], const int64_t out_ld[5], const int out_col[5], int *rowflag,
+                          int64_t BH, int64_t T_, int dtype, cudaStream_t st) {
   int *status = nullptr;
   int rc = lfw_chunk_status_ptr(&status);
   if (rc != T2FW_OK) return rc;
   int n_sm = 0;
   rc = lfw_chunk_sm_count(&n_sm);
   if (rc != T2FW_OK) return rc;
-  const int64_t nc = ceil_div64(T_, kC), total = B * nc;
+  const int64_t nc = ceil_div64(T_, kC), total = BH * nc;
   const unsigned grid = (unsigned)(total < n_sm ? total : n_sm);
+#define T2FW_OUT(TT, i) seq::Out<TT>{(TT *)outs[i], out_ld[i], out_col[i]}
 #define T2FW_LAUNCH(TT)                                                                               \
   do {                                                                                                \
     T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_c64_bwd_kernel<TT>,                                      \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemB));       \
     lfw_c64_bwd_kernel<TT><<<grid, kThreadsB, kSmemB, st>>>(                                          \
-        (const TT *)go, (const TT *)x, (const TT *)f, (const TT *)q, (const TT *)k, (const TT *)fk,   \
-        (const TT *)state, (const TT *)ckpt, Rend, (TT *)dx, (TT *)df, (TT *)dq, (TT *)dk, (TT *)dfk, \
-        rowflag, status, T_, nc, total);                                                              \
+        mp, (const TT *)state, (const TT *)ckpt, Rend, T2FW_OUT(TT, 0), T2FW_OUT(TT, 1), T2FW_OUT(TT, 2), \
+        T2FW_OUT(TT, 3), T2FW_OUT(TT, 4), rowflag, status, T_, nc, total);                            \
   } while (0)
   if (dtype == T2FW_F16) T2FW_LAUNCH(__half); else T2FW_LAUNCH(__nv_bfloat16);
 #undef T2FW_LAUNCH
+#undef T2FW_OUT
   T2FW_CHECK_LAUNCH(1);
   return T2FW_OK;
 }
 
 }  // namespace t2fw
 
-#ifdef T2FW_C64_PROFILE
-extern "C" int t2fw_debug_c64_prof(long long *out) {
-  return (int)cudaMemcpyFromSymbol(out, t2fw::g_c64_prof, sizeof(long long) * 32);
-}
-#endif

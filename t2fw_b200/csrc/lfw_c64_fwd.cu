@@ -21,6 +21,7 @@
 #include <type_traits>
 
 #include "lfw_c64.cuh"
+#include "seq_layout.cuh"
 
 namespace t2fw {
 
@@ -50,9 +51,8 @@ constexpr int cP = 0, cO = 32;                     // tensor-memory columns
 
 template <typename T>
 __global__ void __launch_bounds__(kThreadsF, 1)
-lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__restrict__ q,
-                   const T *__restrict__ k, const T *__restrict__ fk, const T *__restrict__ state,
-                   const T *__restrict__ ckpt, T *__restrict__ out, int *__restrict__ rowflag, int *__restrict__ status, int64_t T_,
+lfw_c64_fwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ state, const T *__restrict__ ckpt,
+                   const seq::Out<T> out, int *__restrict__ rowflag, int *__restrict__ status, int64_t T_,
                    int64_t nc, int64_t total) {
   extern __shared__ __align__(1024) unsigned char sm_raw[];
   unsigned char *sm = sm_raw + ((1024u - (umma::smem_u32(sm_raw) & 1023u)) & 1023u);   // swizzle atoms are 1024-byte aligned
@@ -73,24 +73,25 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
   float *pmA = reinterpret_cast<float *>(sm + oPmA);
   float *qtot = reinterpret_cast<float *>(sm + oQt);
 
-  auto issue_raw = [&](int64_t ci, int buf) {     // thread 0 only
-    const int64_t b = ci / nc, c = ci % nc, t0 = c * kC;
-    const int nv = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
-    const uint32_t vb = (uint32_t)nv * kDim * sizeof(T);
-    const size_t base = ((size_t)b * T_ + t0) * kDim;
+  // tensors: 0 x, 1 f, 2 q, 3 k, 4 fk
+  const bool unit_forget = (mp.flags & seq::kUnitForget) != 0;
+  auto issue_raw = [&](int64_t ci, int buf) {     // thread 0 only: one copy per tensor
+    const Item w = split_item(ci, nc, mp.heads);
+    const int row = (int)(w.b * T_ + w.c * kC), hc = w.h * kDim;
+    const int nv = (int)((T_ - (int64_t)w.c * kC < kC) ? T_ - (int64_t)w.c * kC : kC);
     unsigned char *r = sm + oRaw + buf * 5 * kRawBytes;
-    acp::mbar_expect_tx(&barRaw[buf], 5 * vb);
-    acp::bulk_g2s(r, x + base, vb, &barRaw[buf]);
-    acp::bulk_g2s(r + kRawBytes, f + base, vb, &barRaw[buf]);
-    acp::bulk_g2s(r + 2 * kRawBytes, q + base, vb, &barRaw[buf]);
-    acp::bulk_g2s(r + 3 * kRawBytes, k + base, vb, &barRaw[buf]);
-    acp::bulk_g2s(r + 4 * kRawBytes, fk + base, vb, &barRaw[buf]);
+    const uint32_t per = (mp.flags & seq::kContiguous) ? (uint32_t)nv * kDim * sizeof(T) : (uint32_t)kRawBytes;
+    acp::mbar_expect_tx(&barRaw[buf], (unit_forget ? 4u : 5u) * per);
+#pragma unroll
+    for (int i = 0; i < 5; ++i)
+      if (!(i == 1 && unit_forget)) seq::fetch_block<T>(mp, i, r + i * kRawBytes, row, hc, nv, &barRaw[buf]);
   };
 
   // start state of a chunk (the caller's state for the first chunk of a row, else the checkpoint
   // written by the carry): one 16-byte asynchronous copy per thread into the padded landing zone
   auto issue_state = [&](int64_t ci) {   // every thread
-    const int64_t b = ci / nc, c = ci % nc;
+    const Item w = split_item(ci, nc, mp.heads);
+    const int64_t b = w.bh, c = w.c;
     const T *s0p = (c == 0) ? state + (size_t)b * kDim * kDim : ckpt + ((size_t)b * nc + (c - 1)) * kDim * kDim;
     cp_async16(sm + oS0L + (tid >> 3) * kS0Ld + (tid & 7) * 16, s0p + (tid >> 3) * kDim + (tid & 7) * 8);
     cp_async_commit();
@@ -105,6 +106,10 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
     s_fail = 0;
   }
   if (warp == 0) umma::tmem_alloc(&tmem_slot, 64);
+  if (unit_forget) {      // the d-side gate block of both buffers is the constant 1 and never loaded
+    seq::fill_block(reinterpret_cast<T *>(sm + oRaw + kRawBytes), 1.f, tid, kThreadsF);
+    seq::fill_block(reinterpret_cast<T *>(sm + oRaw + 6 * kRawBytes), 1.f, tid, kThreadsF);
+  }
   sync_all();
   const uint32_t tb = __shfl_sync(0xffffffffu, tmem_slot, 0);
   const uint32_t tl = umma::tmem_addr(tb, 32 * q4, 0);
@@ -123,9 +128,11 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
   uint32_t it = 0;
   for (int64_t ci = blockIdx.x; ci < total; ci += gridDim.x, ++it) {
     const int buf = it & 1;
-    const int64_t b = ci / nc, c = ci % nc, t0c = c * kC;
+    const Item wi = split_item(ci, nc, mp.heads);
+    const int64_t b = wi.bh, c = wi.c, t0c = c * kC;      // b: problem row (batch item x head)
     const int nvalid = (int)((T_ - t0c < kC) ? T_ - t0c : kC);
     T *raw = reinterpret_cast<T *>(sm + oRaw + buf * 5 * kRawBytes);
+    T *orow = out.p + (wi.b * T_ + t0c) * out.ld + out.col + wi.h * kDim;
 
     if (tid == 0) {
       s_bad = 0;
@@ -142,6 +149,11 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
     }
     __syncthreads();
     if (s_fail) break;
+    if ((mp.flags & seq::kSigmoidGate) || mp.q_scale != 1.f) {      // fused layer: activations applied here
+      if (mp.flags & seq::kSigmoidGate) seq::sigmoid_gate_block(raw + 4 * kC * kDim, tid, kThreadsF);
+      if (mp.q_scale != 1.f) seq::scale_block(raw + 2 * kC * kDim, mp.q_scale, tid, kThreadsF);
+      __syncthreads();
+    }
     if (nvalid < kC) {      // partial chunk: identity steps beyond the valid ones
       pad_raw_tail<T>(raw, 5, (1u << 1) | (1u << 4), nvalid, tid, kThreadsF);
       __syncthreads();
@@ -284,7 +296,7 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
         __align__(16) T o[8];
         o[0] = (T)(v[0] * p0.x); o[1] = (T)(v[1] * p0.y); o[2] = (T)(v[2] * p0.z); o[3] = (T)(v[3] * p0.w);
         o[4] = (T)(v[4] * p1.x); o[5] = (T)(v[5] * p1.y); o[6] = (T)(v[6] * p1.z); o[7] = (T)(v[7] * p1.w);
-        *reinterpret_cast<uint4 *>(out + ((size_t)b * T_ + t0c + t) * kDim + d0) = *reinterpret_cast<const uint4 *>(o);
+        *reinterpret_cast<uint4 *>(orow + (size_t)t * out.ld + d0) = *reinterpret_cast<const uint4 *>(o);
       }
     }
     sync_all();       // accumulators and tiles free for the next chunk
@@ -301,33 +313,26 @@ lfw_c64_fwd_kernel(const T *__restrict__ x, const T *__restrict__ f, const T *__
   if (warp == 0) umma::tmem_dealloc(tb, 64);
 }
 
-bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-
 }  // namespace
 
-// Returns T2FW_ERR_UNSUPPORTED (without launching) if a pointer is not 16-byte aligned.
-int lfw_c64_forward_out(const void *x, const void *f, const void *q, const void *k, const void *fk,
-                        const void *state, const void *ckpt, void *out, int *rowflag, int64_t B, int64_t T_,
-                        int dtype, cudaStream_t st) {
-  if (!(aligned16(x) && aligned16(f) && aligned16(q) && aligned16(k) && aligned16(fk) && aligned16(state) &&
-        aligned16(ckpt) && aligned16(out)))
-    return T2FW_ERR_UNSUPPORTED;
+// mp: tensor maps of x, f, q, k, fk; state / ckpt [BH][.][64][64]; the outputs go to out.
+int lfw_c64_forward_out(const seq::Maps &mp, const void *state, const void *ckpt, void *out, int64_t out_ld,
+                        int out_col, int *rowflag, int64_t BH, int64_t T_, int dtype, cudaStream_t st) {
   int *status = nullptr;
   int rc = lfw_chunk_status_ptr(&status);
   if (rc != T2FW_OK) return rc;
   int n_sm = 0;
   rc = lfw_chunk_sm_count(&n_sm);
   if (rc != T2FW_OK) return rc;
-  const int64_t nc = ceil_div64(T_, kC), total = B * nc;
+  const int64_t nc = ceil_div64(T_, kC), total = BH * nc;
   const unsigned grid = (unsigned)(total < n_sm ? total : n_sm);
 #define T2FW_LAUNCH(TT)                                                                              \
   do {                                                                                               \
     T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_c64_fwd_kernel<TT>,                                     \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemF));      \
     lfw_c64_fwd_kernel<TT><<<grid, kThreadsF, kSmemF, st>>>(                                         \
-        (const TT *)x, (const TT *)f, (const TT *)q, (const TT *)k, (const TT *)fk, (const TT *)state,     \
-        (const TT *)ckpt, (TT *)out, \
-        rowflag, status, T_, nc, total);                                                             \
+        mp, (const TT *)state, (const TT *)ckpt, seq::Out<TT>{(TT *)out, out_ld, out_col}, rowflag, status, T_, \
+        nc, total);                                                                                  \
   } while (0)
   if (dtype == T2FW_F16) T2FW_LAUNCH(__half); else T2FW_LAUNCH(__nv_bfloat16);
 #undef T2FW_LAUNCH

@@ -16,18 +16,19 @@
 // rowflag[B] (int).  A flagged batch row (gate products outside the range of the factored form) is
 // recomputed by the scan kernels afterwards.
 #include "lfw_c64.cuh"
+#include "seq_layout.cuh"
 
 namespace t2fw {
 
 using namespace c64;
 
-int lfw_c64_forward_out(const void *x, const void *f, const void *q, const void *k, const void *fk,
-                        const void *state, const void *ckpt, void *out, int *rowflag, int64_t B, int64_t T_,
-                        int dtype, cudaStream_t st);
-int lfw_c64_backward_main(const void *go, const void *x, const void *f, const void *q, const void *k,
-                          const void *fk, const void *state, const void *ckpt, const float *Rend, void *dx,
-                          void *df, void *dq, void *dk, void *dfk, int *rowflag, int64_t B, int64_t T_,
-                          int dtype, cudaStream_t st);
+int lfw_chunk_local_umma(bool backward, const seq::Maps &mp, float *M, float *Ac, float *Gc, int *flags, int64_t BH,
+                         int64_t T_, int dtype, cudaStream_t st);
+int lfw_c64_forward_out(const seq::Maps &mp, const void *state, const void *ckpt, void *out, int64_t out_ld,
+                        int out_col, int *rowflag, int64_t BH, int64_t T_, int dtype, cudaStream_t st);
+int lfw_c64_backward_main(const seq::Maps &mp, const void *state, const void *ckpt, const float *Rend,
+                          void *const outs[5], const int64_t out_ld[5], const int out_col[5], int *rowflag,
+                          int64_t BH, int64_t T_, int dtype, cudaStream_t st);
 
 namespace {
 
@@ -110,33 +111,113 @@ lfw_c64_carry_kernel(const T *__restrict__ init, float *__restrict__ M, const fl
   if (d == 0 && k0 == 0) rowflag[b] = any;
 }
 
+// One sequence tensor of a call: base pointer, width of a row (elements), column of head 0.
+struct Tensor2D {
+  const void *p;
+  int64_t width;
+  int col;
+};
+
+// Tensor maps for a kernel whose inputs are `ts` (in the kernel's order); rows = batch items x T.
+int build_maps(seq::Maps &mp, const Tensor2D *ts, int n, int64_t rows, int heads, int flags, float q_scale) {
+  if (rows >= (1ll << 31) || rows * heads / kC + rows * heads >= (1ll << 31)) {
+    set_error("chunked decay rule: batch x time = %lld rows exceed the copy engine's 31-bit coordinates", (long long)rows);
+    return T2FW_ERR_UNSUPPORTED;
+  }
+  bool dense = heads == 1;
+  for (int i = 0; i < n; ++i) dense = dense && (ts[i].p == nullptr || (ts[i].width == kDim && ts[i].col == 0));
+  if (dense) flags |= seq::kContiguous;               // [rows][64] arrays: linear copies, no tensor maps needed
+  for (int i = 0; i < n; ++i) {
+    mp.col[i] = ts[i].col;
+    mp.base[i] = ts[i].p;
+    if (ts[i].p == nullptr || dense) continue;        // constant tensor (unit forget gate) / no map needed
+    bool shared = false;
+    for (int j = 0; j < i && !shared; ++j)
+      if (ts[j].p == ts[i].p && ts[j].width == ts[i].width) {
+        mp.m[i] = mp.m[j];                            // several tensors inside one array
+        shared = true;
+      }
+    if (!shared) {
+      const int rc = seq::make_map(&mp.m[i], ts[i].p, (uint64_t)rows, (uint64_t)ts[i].width, (uint64_t)ts[i].width);
+      if (rc != T2FW_OK) return rc;
+    }
+  }
+  mp.heads = heads;
+  mp.flags = flags;
+  mp.q_scale = q_scale;
+  return T2FW_OK;
+}
+
+// The tensors of a call, plain or fused: x, f, q, k, fk, dO in that order (f.p null = constant 1).
+struct Call {
+  Tensor2D x, f, q, k, fk, go;
+  int64_t B, T_;        // batch items, steps;  problem rows BH = B * heads
+  int heads, flags;
+  float q_scale;
+};
+
 template <typename T>
-int forward_typed(const void *x, const void *f, const void *q, const void *k, const void *fk, const void *state,
-                  void *out, void *ckpt, int64_t B, int64_t T_, int dtype, void *scratch, cudaStream_t st) {
-  const int64_t nc = ceil_div64(T_, kC);
-  Scratch s = carve(scratch, B, nc);
-  int rc = lfw_chunk_local_umma(false, x, f, k, fk, s.M, s.Ac, s.Gc, s.flags, B, T_, dtype, st);
+int forward_typed(const Call &c, const void *state, void *out, int64_t out_ld, int out_col, void *ckpt, int dtype,
+                  void *scratch, cudaStream_t st) {
+  const int64_t BH = c.B * c.heads, nc = ceil_div64(c.T_, kC), rows = c.B * c.T_;
+  Scratch s = carve(scratch, BH, nc);
+  seq::Maps mp;
+  const Tensor2D loc[4] = {c.x, c.f, c.k, c.fk};
+  int rc = build_maps(mp, loc, 4, rows, c.heads, c.flags, 1.f);
   if (rc != T2FW_OK) return rc;
-  const int64_t n_carry = B * kDim * (kDim / 2);
+  rc = lfw_chunk_local_umma(false, mp, s.M, s.Ac, s.Gc, s.flags, BH, c.T_, dtype, st);
+  if (rc != T2FW_OK) return rc;
+  const int64_t n_carry = BH * kDim * (kDim / 2);
   lfw_c64_carry_kernel<T, true><<<(unsigned)ceil_div64(n_carry, 256), 256, 0, st>>>(
-      (const T *)state, s.M, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ckpt, B, nc);
+      (const T *)state, s.M, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ckpt, BH, nc);
   T2FW_CHECK_LAUNCH(1);
-  return lfw_c64_forward_out(x, f, q, k, fk, state, ckpt, out, s.rowflag, B, T_, dtype, st);
+  const Tensor2D all[5] = {c.x, c.f, c.q, c.k, c.fk};
+  rc = build_maps(mp, all, 5, rows, c.heads, c.flags, c.q_scale);
+  if (rc != T2FW_OK) return rc;
+  return lfw_c64_forward_out(mp, state, ckpt, out, out_ld, out_col, s.rowflag, BH, c.T_, dtype, st);
 }
 
 template <typename T>
-int backward_typed(const void *go, const void *gs, const void *x, const void *f, const void *q, const void *k,
-                   const void *fk, const void *state, const void *ckpt, void *dx, void *df, void *dq, void *dk,
-                   void *dfk, void *ds, int64_t B, int64_t T_, int dtype, void *scratch, cudaStream_t st) {
-  const int64_t nc = ceil_div64(T_, kC);
-  Scratch s = carve(scratch, B, nc);
-  int rc = lfw_chunk_local_umma(true, go, f, q, fk, s.M, s.Ac, s.Gc, s.flags, B, T_, dtype, st);
+int backward_typed(const Call &c, const void *gs, const void *state, const void *ckpt, void *const outs[5],
+                   const int64_t out_ld[5], const int out_col[5], void *ds, int dtype, void *scratch,
+                   cudaStream_t st) {
+  const int64_t BH = c.B * c.heads, nc = ceil_div64(c.T_, kC), rows = c.B * c.T_;
+  Scratch s = carve(scratch, BH, nc);
+  seq::Maps mp;
+  const Tensor2D loc[4] = {c.go, c.f, c.q, c.fk};
+  int rc = build_maps(mp, loc, 4, rows, c.heads, c.flags, c.q_scale);
   if (rc != T2FW_OK) return rc;
-  const int64_t n_carry = B * kDim * (kDim / 2);
+  rc = lfw_chunk_local_umma(true, mp, s.M, s.Ac, s.Gc, s.flags, BH, c.T_, dtype, st);
+  if (rc != T2FW_OK) return rc;
+  const int64_t n_carry = BH * kDim * (kDim / 2);
   lfw_c64_carry_kernel<T, false><<<(unsigned)ceil_div64(n_carry, 256), 256, 0, st>>>(
-      (const T *)gs, s.M, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ds, B, nc);
+      (const T *)gs, s.M, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ds, BH, nc);
   T2FW_CHECK_LAUNCH(1);
-  return lfw_c64_backward_main(go, x, f, q, k, fk, state, ckpt, s.M, dx, df, dq, dk, dfk, s.rowflag, B, T_, dtype, st);
+  const Tensor2D all[6] = {c.x, c.f, c.q, c.k, c.fk, c.go};
+  rc = build_maps(mp, all, 6, rows, c.heads, c.flags, c.q_scale);
+  if (rc != T2FW_OK) return rc;
+  return lfw_c64_backward_main(mp, state, ckpt, s.M, outs, out_ld, out_col, s.rowflag, BH, c.T_, dtype, st);
+}
+
+Call plain_call(const void *x, const void *f, const void *q, const void *k, const void *fk, const void *go, int64_t B,
+                int64_t T_) {
+  Call c;
+  c.x = {x, kDim, 0}; c.f = {f, kDim, 0}; c.q = {q, kDim, 0}; c.k = {k, kDim, 0}; c.fk = {fk, kDim, 0};
+  c.go = {go, kDim, 0};
+  c.B = B; c.T_ = T_; c.heads = 1; c.flags = 0; c.q_scale = 1.f;
+  return c;
+}
+
+// fused layer: qkvg [B][T][4 * H * 64] = query | key | value | gate pre-activation, heads inside a row
+Call fused_call(const void *qkvg, const void *go, int64_t B, int64_t T_, int H) {
+  const int64_t C = (int64_t)H * kDim;
+  Call c;
+  c.q = {qkvg, 4 * C, 0}; c.k = {qkvg, 4 * C, (int)C}; c.x = {qkvg, 4 * C, (int)(2 * C)};
+  c.fk = {qkvg, 4 * C, (int)(3 * C)};
+  c.f = {nullptr, 0, 0};
+  c.go = {go, C, 0};
+  c.B = B; c.T_ = T_; c.heads = H; c.flags = seq::kUnitForget | seq::kSigmoidGate; c.q_scale = 0.125f;   // 1 / sqrt(64)
+  return c;
 }
 
 }  // namespace
@@ -154,13 +235,14 @@ size_t lfw_chunk_backward_scratch_bytes(int64_t B, int64_t T_) {
 }
 
 // Both calls need every pointer 16-byte aligned (the C ABI routes other callers to the scan
-// kernels) and return T2FW_ERR_UNSUPPORTED otherwise.
+// kernels).
 int lfw_chunk_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,
                       const void *state, void *out, void *ckpt, int64_t B, int64_t T_, int dtype,
                       void *scratch, cudaStream_t st, const int **rowflag_out) {
   if (rowflag_out) *rowflag_out = carve(scratch, B, ceil_div64(T_, kC)).rowflag;
-  if (dtype == T2FW_F16) return forward_typed<__half>(x, f, q, k, fk, state, out, ckpt, B, T_, dtype, scratch, st);
-  return forward_typed<__nv_bfloat16>(x, f, q, k, fk, state, out, ckpt, B, T_, dtype, scratch, st);
+  const Call c = plain_call(x, f, q, k, fk, nullptr, B, T_);
+  if (dtype == T2FW_F16) return forward_typed<__half>(c, state, out, kDim, 0, ckpt, dtype, scratch, st);
+  return forward_typed<__nv_bfloat16>(c, state, out, kDim, 0, ckpt, dtype, scratch, st);
 }
 
 int lfw_chunk_backward(const void *go, const void *gs, const void *x, const void *f, const void *q,
@@ -168,10 +250,36 @@ int lfw_chunk_backward(const void *go, const void *gs, const void *x, const void
                        void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B, int64_t T_,
                        int dtype, void *scratch, cudaStream_t st, const int **rowflag_out) {
   if (rowflag_out) *rowflag_out = carve(scratch, B, ceil_div64(T_, kC)).rowflag;
-  if (dtype == T2FW_F16)
-    return backward_typed<__half>(go, gs, x, f, q, k, fk, state, ckpt, dx, df, dq, dk, dfk, ds, B, T_, dtype, scratch, st);
-  return backward_typed<__nv_bfloat16>(go, gs, x, f, q, k, fk, state, ckpt, dx, df, dq, dk, dfk, ds, B, T_, dtype,
-                                       scratch, st);
+  const Call c = plain_call(x, f, q, k, fk, go, B, T_);
+  void *const outs[5] = {dx, df, dq, dk, dfk};
+  const int64_t ld[5] = {kDim, kDim, kDim, kDim, kDim};
+  const int col[5] = {0, 0, 0, 0, 0};
+  if (dtype == T2FW_F16) return backward_typed<__half>(c, gs, state, ckpt, outs, ld, col, ds, dtype, scratch, st);
+  return backward_typed<__nv_bfloat16>(c, gs, state, ckpt, outs, ld, col, ds, dtype, scratch, st);
+}
+
+// ---- fused layer entry points (heads read in place from the projection output) ----------------
+size_t lfw_fused_scratch_bytes(int64_t B, int64_t T_, int H) { return lfw_chunk_forward_scratch_bytes(B * H, T_); }
+
+int lfw_fused_forward(const void *qkvg, const void *state, void *out, void *ckpt, int64_t B, int64_t T_, int H,
+                      int dtype, void *scratch, cudaStream_t st) {
+  const Call c = fused_call(qkvg, nullptr, B, T_, H);
+  const int64_t C = (int64_t)H * kDim;
+  if (dtype == T2FW_F16) return forward_typed<__half>(c, state, out, C, 0, ckpt, dtype, scratch, st);
+  return forward_typed<__nv_bfloat16>(c, state, out, C, 0, ckpt, dtype, scratch, st);
+}
+
+int lfw_fused_backward(const void *go, const void *gs, const void *qkvg, const void *state, const void *ckpt,
+                       void *d_qkvg, void *ds, int64_t B, int64_t T_, int H, int dtype, void *scratch,
+                       cudaStream_t st) {
+  const Call c = fused_call(qkvg, go, B, T_, H);
+  const int64_t C = (int64_t)H * kDim;
+  // gradients land in d_qkvg [B][T][4C]: query | key | value | gate; there is no forget tensor
+  void *const outs[5] = {d_qkvg, nullptr, d_qkvg, d_qkvg, d_qkvg};
+  const int64_t ld[5] = {4 * C, 0, 4 * C, 4 * C, 4 * C};
+  const int col[5] = {(int)(2 * C), 0, 0, (int)C, (int)(3 * C)};
+  if (dtype == T2FW_F16) return backward_typed<__half>(c, gs, state, ckpt, outs, ld, col, ds, dtype, scratch, st);
+  return backward_typed<__nv_bfloat16>(c, gs, state, ckpt, outs, ld, col, ds, dtype, scratch, st);
 }
 
 }  // namespace t2fw

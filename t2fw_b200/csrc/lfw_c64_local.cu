@@ -22,24 +22,12 @@
 #include <mutex>
 
 #include "lfw_c64.cuh"
+#include "seq_layout.cuh"
 
 namespace t2fw {
 
 using namespace c64;
 
-#ifdef T2FW_C64_PROFILE
-__device__ long long g_loc_prof[16];
-#define PROF(i)                                                    \
-  do {                                                             \
-    if (threadIdx.x == 96 && blockIdx.x == 0) {                    \
-      const long long now_ = clock64();                            \
-      g_loc_prof[i] += now_ - tprev;                               \
-      tprev = now_;                                                \
-    }                                                              \
-  } while (0)
-#else
-#define PROF(i) do { } while (0)
-#endif
 
 namespace {
 
@@ -60,8 +48,7 @@ constexpr int kTmemColsL = 128;
 // kSuffix = false: value * (product of the gates up to and including the step)       [backward]
 template <typename T, bool kSuffix>
 __global__ void __launch_bounds__(kThreadsL, kCtasPerSmL)
-lfw_c64_local_kernel(const T *__restrict__ val_d, const T *__restrict__ gate_d, const T *__restrict__ val_k,
-                     const T *__restrict__ gate_k, float *__restrict__ M, float *__restrict__ Ac,
+lfw_c64_local_kernel(const __grid_constant__ seq::Maps mp, float *__restrict__ M, float *__restrict__ Ac,
                      float *__restrict__ Gc, int *__restrict__ flags, int *__restrict__ status, int64_t T_,
                      int64_t nc, int64_t total) {
   extern __shared__ __align__(1024) unsigned char sm_raw[];
@@ -80,17 +67,18 @@ lfw_c64_local_kernel(const T *__restrict__ val_d, const T *__restrict__ gate_d, 
   const int tq = dside ? 2 * h + part : (warp - 8) >> 1;
   float *qtot = reinterpret_cast<float *>(sm + oQtL);
 
-  auto issue_raw = [&](int64_t ci, int buf) {     // thread 0 only
-    const int64_t b = ci / nc, c = ci % nc, t0 = c * kC;
-    const int nv = (int)((T_ - t0 < kC) ? T_ - t0 : kC);
-    const uint32_t vb = (uint32_t)nv * kDim * sizeof(T);
-    const size_t base = ((size_t)b * T_ + t0) * kDim;
+  // tensors: 0 val_d, 1 gate_d, 2 val_k, 3 gate_k
+  const bool unit_forget = (mp.flags & seq::kUnitForget) != 0;
+  auto issue_raw = [&](int64_t ci, int buf) {     // thread 0 only: one copy per tensor
+    const Item w = split_item(ci, nc, mp.heads);
+    const int row = (int)(w.b * T_ + w.c * kC), hc = w.h * kDim;
+    const int nv = (int)((T_ - (int64_t)w.c * kC < kC) ? T_ - (int64_t)w.c * kC : kC);
     unsigned char *r = sm + oRawL + buf * 4 * kRawBytes;
-    acp::mbar_expect_tx(&barRaw[buf], 4 * vb);
-    acp::bulk_g2s(r, val_d + base, vb, &barRaw[buf]);
-    acp::bulk_g2s(r + kRawBytes, gate_d + base, vb, &barRaw[buf]);
-    acp::bulk_g2s(r + 2 * kRawBytes, val_k + base, vb, &barRaw[buf]);
-    acp::bulk_g2s(r + 3 * kRawBytes, gate_k + base, vb, &barRaw[buf]);
+    const uint32_t per = (mp.flags & seq::kContiguous) ? (uint32_t)nv * kDim * sizeof(T) : (uint32_t)kRawBytes;
+    acp::mbar_expect_tx(&barRaw[buf], (unit_forget ? 3u : 4u) * per);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (!(i == 1 && unit_forget)) seq::fetch_block<T>(mp, i, r + i * kRawBytes, row, hc, nv, &barRaw[buf]);
   };
 
   if (tid == 0) {
@@ -101,6 +89,10 @@ lfw_c64_local_kernel(const T *__restrict__ val_d, const T *__restrict__ gate_d, 
     s_fail = 0;
   }
   if (warp == 0) umma::tmem_alloc(&tmem_slot, kTmemColsL);
+  if (unit_forget) {      // the d-side gate block of both buffers is the constant 1 and never loaded
+    seq::fill_block(reinterpret_cast<T *>(sm + oRawL + kRawBytes), 1.f, tid, kThreadsL);
+    seq::fill_block(reinterpret_cast<T *>(sm + oRawL + 5 * kRawBytes), 1.f, tid, kThreadsL);
+  }
   sync_all();
   const uint32_t tb = __shfl_sync(0xffffffffu, tmem_slot, 0);
   const uint32_t tl = umma::tmem_addr(tb, 32 * q4, 0);
@@ -111,14 +103,10 @@ lfw_c64_local_kernel(const T *__restrict__ val_d, const T *__restrict__ gate_d, 
   }
   const uint64_t dTk = desc_sw128(umma::smem_u32(sm + oTk));
 
-#ifdef T2FW_C64_PROFILE
-  long long tprev = clock64();
-#endif
   uint32_t it = 0;
   for (int64_t ci = blockIdx.x; ci < total; ci += gridDim.x, ++it) {
-    PROF(0);
     const int buf = it & 1;
-    const int64_t c = ci % nc, t0c = c * kC;
+    const int64_t c = (int64_t)((uint32_t)ci % (uint32_t)nc), t0c = c * kC;
     const int nvalid = (int)((T_ - t0c < kC) ? T_ - t0c : kC);
     T *raw = reinterpret_cast<T *>(sm + oRawL + buf * 4 * kRawBytes);
     if (tid == 0) {
@@ -133,10 +121,13 @@ lfw_c64_local_kernel(const T *__restrict__ val_d, const T *__restrict__ gate_d, 
     } else {
       s_fail = 1;
     }
-    PROF(1);
     __syncthreads();
     if (s_fail) break;
-    PROF(2);
+    if ((mp.flags & seq::kSigmoidGate) || mp.q_scale != 1.f) {      // fused layer: activations applied here
+      if (mp.flags & seq::kSigmoidGate) seq::sigmoid_gate_block(raw + 3 * kC * kDim, tid, kThreadsL);
+      if (mp.q_scale != 1.f) seq::scale_block(raw + 2 * kC * kDim, mp.q_scale, tid, kThreadsL);
+      __syncthreads();
+    }
     if (nvalid < kC) {      // partial chunk: identity steps beyond the valid ones
       pad_raw_tail<T>(raw, 4, (1u << 1) | (1u << 3), nvalid, tid, kThreadsL);
       __syncthreads();
@@ -146,9 +137,7 @@ lfw_c64_local_kernel(const T *__restrict__ val_d, const T *__restrict__ gate_d, 
     const T *gcol = raw + (dside ? 1 : 3) * kC * kDim + feat, *vcol = raw + (dside ? 0 : 2) * kC * kDim + feat;
     float g[16];
     qtot[((dside ? 0 : 4) + tq) * kDim + feat] = load_gates16<T>(gcol, tq, g);
-    PROF(3);
     __syncthreads();
-    PROF(4);
 
     // ---- running products from the anchoring end, scaled values ----
     float w[16];
@@ -180,7 +169,6 @@ lfw_c64_local_kernel(const T *__restrict__ val_d, const T *__restrict__ gate_d, 
       // total decay of the chunk for this feature
       if (tq == (kSuffix ? 0 : 3)) (dside ? Ac : Gc)[(size_t)ci * kDim + feat] = s;
     }
-    PROF(5);
     if (dside) {
       // A operand [d][t] in both lane sets: the lower half warp holds quarter `part`, the upper
       // half warp quarter 2 + part of the same rows; one store names one column range per warp
@@ -200,10 +188,8 @@ lfw_c64_local_kernel(const T *__restrict__ val_d, const T *__restrict__ gate_d, 
       for (int j = 0; j < 16; j += 4)
         *reinterpret_cast<float4 *>(tk + toff(feat, 16 * tq + j)) = make_float4(w[j], w[j + 1], w[j + 2], w[j + 3]);
     }
-    PROF(6);
     umma::fence_async_smem();
     sync_all();       // operands complete, raw buffer consumed
-    PROF(7);
 
     if (warp == 0) {
       const uint32_t d0 = tb, d1 = umma::tmem_addr(tb, 16, 0);
@@ -221,10 +207,8 @@ lfw_c64_local_kernel(const T *__restrict__ val_d, const T *__restrict__ gate_d, 
       __syncwarp();
       if (tid == 0) flags[ci] = s_bad;
     }
-    PROF(8);
     if (!umma::mbar_wait(&barM, it & 1u)) s_fail = 1;
     umma::fence_after_sync();
-    PROF(9);
     {
       // thread (lane quarter, column part, lane set, row): row d, columns 32 * h + 8 * (warp >> 2) .. + 7
       const int d = 16 * q4 + fl, k0 = 32 * h + 8 * (warp >> 2);
@@ -235,9 +219,7 @@ lfw_c64_local_kernel(const T *__restrict__ val_d, const T *__restrict__ gate_d, 
       *reinterpret_cast<float4 *>(dst) = make_float4(v[0], v[1], v[2], v[3]);
       *reinterpret_cast<float4 *>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
     }
-    PROF(10);
     sync_all();       // accumulator, A operand and tile free for the next chunk
-    PROF(11);
     if (s_fail) {
       if (tid == 0) flags[ci] = 1;   // results unusable: let the scan kernels redo the row
       break;
@@ -300,16 +282,11 @@ int lfw_chunk_umma_status() {
   return v;
 }
 
-static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-
 // Forward flavour: M = L_c from (x, f) and (k, fk).  Backward flavour: M = G_c from (dO, f), (q, fk).
-// Returns T2FW_ERR_UNSUPPORTED without launching if a pointer is not 16-byte aligned.
-int lfw_chunk_local_umma(bool backward, const void *val_d, const void *gate_d, const void *val_k,
-                         const void *gate_k, float *M, float *Ac, float *Gc, int *flags, int64_t B,
+// mp describes the four tensors in that order (mp.q_scale applies to the third one).
+int lfw_chunk_local_umma(bool backward, const seq::Maps &mp, float *M, float *Ac, float *Gc, int *flags, int64_t BH,
                          int64_t T_, int dtype, cudaStream_t st) {
-  if (!(aligned16(val_d) && aligned16(gate_d) && aligned16(val_k) && aligned16(gate_k) && aligned16(M)))
-    return T2FW_ERR_UNSUPPORTED;
-  const int64_t nc = ceil_div64(T_, kC), total = B * nc;
+  const int64_t nc = ceil_div64(T_, kC), total = BH * nc;
   int *status = nullptr;
   int rc = lfw_chunk_status_ptr(&status);
   if (rc != T2FW_OK) return rc;
@@ -322,9 +299,7 @@ int lfw_chunk_local_umma(bool backward, const void *val_d, const void *gate_d, c
   do {                                                                                                \
     T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_c64_local_kernel<TT, SUF>,                               \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemL));       \
-    lfw_c64_local_kernel<TT, SUF><<<grid, kThreadsL, kSmemL, st>>>(                                   \
-        (const TT *)val_d, (const TT *)gate_d, (const TT *)val_k, (const TT *)gate_k, M, Ac, Gc, flags, \
-        status, T_, nc, total);                                                                       \
+    lfw_c64_local_kernel<TT, SUF><<<grid, kThreadsL, kSmemL, st>>>(mp, M, Ac, Gc, flags, status, T_, nc, total); \
   } while (0)
   if (dtype == T2FW_F16) {
     if (backward) T2FW_LAUNCH(__half, false); else T2FW_LAUNCH(__half, true);
@@ -338,8 +313,3 @@ int lfw_chunk_local_umma(bool backward, const void *val_d, const void *gate_d, c
 
 }  // namespace t2fw
 
-#ifdef T2FW_C64_PROFILE
-extern "C" int t2fw_debug_loc_prof(long long *out) {
-  return (int)cudaMemcpyFromSymbol(out, t2fw::g_loc_prof, sizeof(long long) * 16);
-}
-#endif

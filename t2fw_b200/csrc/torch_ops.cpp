@@ -178,6 +178,63 @@ void lfw_decode_step(at::Tensor x, at::Tensor f, at::Tensor query, at::Tensor ke
                "lfw.decode_step");
 }
 
+// Fused decay-rule layer (d_head = 64): heads are read in place from the projection output
+// qkvg [B,T,4*H*64] = query | key | value | gate; returns {outputs [B,T,H*64], ckpt_states}.
+std::vector<at::Tensor> lfw_fused_forward(at::Tensor qkvg, at::Tensor state, int64_t n_head) {
+  T2FW_CHECK_INPUT(qkvg);
+  T2FW_CHECK_INPUT(state);
+  TORCH_CHECK(qkvg.dim() == 3 && state.dim() == 3 && n_head > 0, "expected qkvg [B,T,4*H*64], state [B*H,64,64]");
+  const int64_t B = qkvg.size(0), T = qkvg.size(1), H = n_head;
+  TORCH_CHECK(qkvg.size(2) == 4 * H * 64, "qkvg must be [B,T,4*H*64]");
+  TORCH_CHECK(state.size(0) == B * H && state.size(1) == 64 && state.size(2) == 64, "state must be [B*H,64,64]");
+  check_same(state, qkvg, "state");
+  TORCH_CHECK(B > 0 && T > 0, "empty tensors are not supported");
+  const c10::cuda::CUDAGuard guard(qkvg.device());
+  const int dt = dtype_code(qkvg);
+  at::Tensor outputs = at::empty({B, T, H * 64}, qkvg.options());
+  at::Tensor ckpt = at::empty({B * H, t2fw_lfw_ckpt_slots(T, 64), 64, 64}, qkvg.options());
+  const size_t sb = t2fw_lfw_fused_scratch_bytes(B, T, H, dt);
+  at::Tensor scratch = make_scratch(sb, qkvg);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check_status(t2fw_lfw_fused_forward(qkvg.data_ptr(), state.data_ptr(), outputs.data_ptr(), ckpt.data_ptr(), B, T, H,
+                                      dt, ptr_or_null(scratch), sb, stream.stream()),
+               "lfw.fused_forward");
+  return {outputs, ckpt};
+}
+
+std::vector<at::Tensor> lfw_fused_backward(at::Tensor grad_output, at::Tensor grad_state, at::Tensor qkvg,
+                                           at::Tensor state, at::Tensor ckpt_states, int64_t n_head) {
+  T2FW_CHECK_INPUT(grad_output);
+  T2FW_CHECK_INPUT(grad_state);
+  T2FW_CHECK_INPUT(qkvg);
+  T2FW_CHECK_INPUT(state);
+  T2FW_CHECK_INPUT(ckpt_states);
+  TORCH_CHECK(qkvg.dim() == 3 && state.dim() == 3 && grad_output.dim() == 3 && ckpt_states.dim() == 4 && n_head > 0,
+              "bad ranks");
+  const int64_t B = qkvg.size(0), T = qkvg.size(1), H = n_head;
+  TORCH_CHECK(qkvg.size(2) == 4 * H * 64, "qkvg must be [B,T,4*H*64]");
+  TORCH_CHECK(grad_output.size(0) == B && grad_output.size(1) == T && grad_output.size(2) == H * 64,
+              "grad_output must be [B,T,H*64]");
+  TORCH_CHECK(state.size(0) == B * H && state.size(1) == 64 && state.size(2) == 64, "state must be [B*H,64,64]");
+  TORCH_CHECK(grad_state.sizes() == state.sizes(), "grad_state must have state's shape");
+  TORCH_CHECK(ckpt_states.size(0) == B * H && ckpt_states.size(1) == t2fw_lfw_ckpt_slots(T, 64) &&
+                  ckpt_states.size(2) == 64 && ckpt_states.size(3) == 64,
+              "ckpt_states must be the tensor lfw.fused_forward returned");
+  check_same(grad_output, qkvg, "grad_output"); check_same(grad_state, qkvg, "grad_state");
+  check_same(state, qkvg, "state"); check_same(ckpt_states, qkvg, "ckpt_states");
+  const c10::cuda::CUDAGuard guard(qkvg.device());
+  const int dt = dtype_code(qkvg);
+  at::Tensor d_qkvg = at::empty_like(qkvg), d_state = at::empty_like(state);
+  const size_t sb = t2fw_lfw_fused_scratch_bytes(B, T, H, dt);
+  at::Tensor scratch = make_scratch(sb, qkvg);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check_status(t2fw_lfw_fused_backward(grad_output.data_ptr(), grad_state.data_ptr(), qkvg.data_ptr(), state.data_ptr(),
+                                       ckpt_states.data_ptr(), d_qkvg.data_ptr(), d_state.data_ptr(), B, T, H, dt,
+                                       ptr_or_null(scratch), sb, stream.stream()),
+               "lfw.fused_backward");
+  return {d_qkvg, d_state};
+}
+
 // ---- delta rule ---------------------------------------------------------------------------
 at::ScalarType acc_type(const at::Tensor &t) {
   return t.scalar_type() == at::kDouble ? at::kDouble : at::kFloat;
@@ -257,6 +314,8 @@ TORCH_LIBRARY(lfw, m) {
   m.def("forward", lfw_forward);
   m.def("backward", lfw_backward);
   m.def("decode_step", lfw_decode_step);
+  m.def("fused_forward", lfw_fused_forward);
+  m.def("fused_backward", lfw_fused_backward);
 }
 
 TORCH_LIBRARY(dfw, m) {

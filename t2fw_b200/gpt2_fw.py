@@ -21,6 +21,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .functional_dfw import DFWFunction
+from .functional_fused import LFWFusedFunction, unfused_reference
 from .functional_lfw import LFWFunction
 
 
@@ -55,21 +56,26 @@ class FastWeightAttention(nn.Module):
 
     def forward(self, x):
         B, T, C = x.shape
+        if self.rule == "lfw":
+            # projection output = query | key | value | gate; the recurrence reads the heads in place
+            # and applies the query scale and the gate activation itself (fused entry point); other
+            # head sizes and dtypes take the same layer built from the plain operator
+            qkvg = self.qkv(x)
+            state = torch.zeros(B * self.h, self.d, self.d, dtype=x.dtype, device=x.device)
+            if self.d == 64 and x.dtype in (torch.float16, torch.bfloat16) and x.is_cuda:
+                out, _ = LFWFusedFunction.apply(qkvg, state, self.h)
+            else:
+                out, _ = unfused_reference(qkvg, state, self.h)
+            return self.proj(out)
         parts = self.qkv(x).split(C, dim=-1)
         q, k, v = (self._fold(p, B, T) for p in parts[:3])
         state = torch.zeros(B * self.h, self.d, self.d, dtype=x.dtype, device=x.device)
-        if self.rule == "dfw":
+        if True:
             beta = torch.sigmoid(self.strength(x))                       # [B, T, H]
             beta = beta.permute(0, 2, 1).reshape(B * self.h, T, 1)
             k = (torch.softmax(k.float(), dim=-1) * beta.float()).to(x.dtype)
             q = torch.softmax(q.float(), dim=-1).to(x.dtype)
             out, _ = DFWFunction.apply(q.contiguous(), k.contiguous(), v.contiguous(), state)
-        else:
-            gate = torch.sigmoid(self._fold(parts[3], B, T).float()).to(x.dtype)
-            ones = torch.ones_like(v)
-            q = q * (1.0 / math.sqrt(self.d))
-            out, _ = LFWFunction.apply(v.contiguous(), ones, q.contiguous(), k.contiguous(),
-                                       gate.contiguous(), state)
         out = out.view(B, self.h, T, self.d).permute(0, 2, 1, 3).reshape(B, T, C)
         return self.proj(out)
 

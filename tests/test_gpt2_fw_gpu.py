@@ -8,6 +8,7 @@ import torch
 
 from helpers import max_rel_err
 from oracle import torch_port
+from t2fw_b200.functional_fused import GATE_FLOOR
 
 pytestmark = pytest.mark.gpu
 
@@ -24,7 +25,8 @@ def reference_layer(layer, x):
         q = torch.softmax(q, dim=-1)
         out, _ = torch_port.dfw_loop(q, k, v, state)
     else:
-        gate = torch.sigmoid(layer._fold(parts[3], B, T))
+        # the layer's gate is max(sigmoid(.), 1/8) (t2fw_b200/functional_fused.py)
+        gate = torch.sigmoid(layer._fold(parts[3], B, T)).clamp_min(GATE_FLOOR)
         out, _ = torch_port.lfw_loop(v, torch.ones_like(v), q * layer.d ** -0.5, k, gate, state)
     out = out.view(B, layer.h, T, layer.d).permute(0, 2, 1, 3).reshape(B, T, C)
     return layer.proj(out)
