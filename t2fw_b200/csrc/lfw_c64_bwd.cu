@@ -72,7 +72,8 @@ constexpr int cS2 = 0, cR2 = 64, cVw = 128, cMw = 192;
 constexpr int cZ = 256, cTQ1 = 288, cTQ2 = 320, cT2 = 352, cT7 = 384;
 constexpr int kTmemCols = 512;
 
-template <typename T>
+// kFused = false: the plain operator (no activation flags, query scale 1), decided at compile time.
+template <typename T, bool kFused>
 __global__ void __launch_bounds__(kThreadsB, 1)
 lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ state, const T *__restrict__ ckpt,
                    const float *__restrict__ Rend, const seq::Out<T> dx, const seq::Out<T> df, const seq::Out<T> dq,
@@ -105,14 +106,16 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
   T *raw = reinterpret_cast<T *>(sm + oRaw);     // [6][64][64]: x, f, q, k, fk, dO
 
   // tensors: 0 x, 1 f, 2 q, 3 k, 4 fk, 5 dO
-  const bool unit_forget = (mp.flags & seq::kUnitForget) != 0;
+  const bool unit_forget = kFused && (mp.flags & seq::kUnitForget) != 0;
+  const bool sigmoid_gate = kFused && (mp.flags & seq::kSigmoidGate) != 0;
+  const float q_scale = kFused ? mp.q_scale : 1.f;
   auto issue_raw = [&](int64_t ci) {     // thread 0 only: one copy per tensor
     const Item w = split_item(ci, nc, mp.heads);
     const int row = (int)(w.b * T_ + w.c * kC), hc = w.h * kDim;
     const int nv = (int)((T_ - (int64_t)w.c * kC < kC) ? T_ - (int64_t)w.c * kC : kC);
     unsigned char *r = sm + oRaw;
     const uint32_t per = (mp.flags & seq::kContiguous) ? (uint32_t)nv * kDim * sizeof(T) : (uint32_t)kRawBytes;
-    const bool sigm = (mp.flags & seq::kSigmoidGate) != 0;
+    const bool sigm = sigmoid_gate;
     acp::mbar_expect_tx(&barRaw, ((unit_forget ? 5u : 6u) + (sigm ? 1u : 0u)) * per);
 #pragma unroll
     for (int i = 0; i < 6; ++i)
@@ -176,9 +179,9 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
     cp_async_wait_all();       // this thread's share of the chunk's start state and end gradient
     __syncthreads();
     if (s_fail) break;
-    if ((mp.flags & seq::kSigmoidGate) || mp.q_scale != 1.f) {      // fused layer: activations applied here
-      if (mp.flags & seq::kSigmoidGate) seq::sigmoid_gate_block(raw + 4 * kC * kDim, tid, kThreadsB);
-      if (mp.q_scale != 1.f) seq::scale_block(raw + 2 * kC * kDim, mp.q_scale, tid, kThreadsB);
+    if (kFused && (sigmoid_gate || q_scale != 1.f)) {      // fused layer: activations applied here
+      if (sigmoid_gate) seq::sigmoid_gate_block(raw + 4 * kC * kDim, tid, kThreadsB);
+      if (q_scale != 1.f) seq::scale_block(raw + 2 * kC * kDim, q_scale, tid, kThreadsB);
       __syncthreads();
     }
     if (nvalid < kC) {      // partial chunk: identity steps beyond the valid ones
@@ -494,14 +497,14 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         // Fused layer: the query was scaled on the way in, and the gate tensor holds pre-activations
         // (gate = max(sigmoid(g), 1/8)), so the chain rule is finished here.
         const seq::Out<T> &o_dv = ph ? dx : dk, &o_gt = ph ? df : dfk;
-        const bool sig = ph == 0 && (mp.flags & seq::kSigmoidGate);
+        const bool sig = ph == 0 && sigmoid_gate;
         const T *r_gate = raw + 6 * kC * kDim + c0 * kDim + own;     // pre-activations
         // element pointers of step c0; one row pitch further per step
         T *p_mu = dq.p + (size_t)(row0 + c0) * dq.ld + dq.col + hcol + own;
         T *p_dv = o_dv.p + (size_t)(row0 + c0) * o_dv.ld + o_dv.col + hcol + own;
         T *p_gt = o_gt.p == nullptr ? nullptr : o_gt.p + (size_t)(row0 + c0) * o_gt.ld + o_gt.col + hcol + own;
         const int64_t ld_mu = dq.ld, ld_dv = o_dv.ld, ld_gt = o_gt.ld;
-        const float qs = mp.q_scale;
+        const float qs = q_scale;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float H = sa[j] + sb[j] + pre[j] + base_h;
@@ -547,15 +550,20 @@ int lfw_c64_backward_main(const seq::Maps &mp, const void *state, const void *ck
   const int64_t nc = ceil_div64(T_, kC), total = BH * nc;
   const unsigned grid = (unsigned)(total < n_sm ? total : n_sm);
 #define T2FW_OUT(TT, i) seq::Out<TT>{(TT *)outs[i], out_ld[i], out_col[i]}
-#define T2FW_LAUNCH(TT)                                                                               \
+#define T2FW_LAUNCH(TT, FF)                                                                           \
   do {                                                                                                \
-    T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_c64_bwd_kernel<TT>,                                      \
+    T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_c64_bwd_kernel<TT, FF>,                                  \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemB));       \
-    lfw_c64_bwd_kernel<TT><<<grid, kThreadsB, kSmemB, st>>>(                                          \
+    lfw_c64_bwd_kernel<TT, FF><<<grid, kThreadsB, kSmemB, st>>>(                                      \
         mp, (const TT *)state, (const TT *)ckpt, Rend, T2FW_OUT(TT, 0), T2FW_OUT(TT, 1), T2FW_OUT(TT, 2), \
         T2FW_OUT(TT, 3), T2FW_OUT(TT, 4), rowflag, status, T_, nc, total);                            \
   } while (0)
-  if (dtype == T2FW_F16) T2FW_LAUNCH(__half); else T2FW_LAUNCH(__nv_bfloat16);
+  const bool fused = (mp.flags & (seq::kUnitForget | seq::kSigmoidGate)) != 0 || mp.q_scale != 1.f;
+  if (dtype == T2FW_F16) {
+    if (fused) T2FW_LAUNCH(__half, true); else T2FW_LAUNCH(__half, false);
+  } else {
+    if (fused) T2FW_LAUNCH(__nv_bfloat16, true); else T2FW_LAUNCH(__nv_bfloat16, false);
+  }
 #undef T2FW_LAUNCH
 #undef T2FW_OUT
   T2FW_CHECK_LAUNCH(1);
