@@ -51,64 +51,98 @@ inline Scratch carve(void *scratch, int64_t B, int64_t nc) {
   return s;
 }
 
-template <typename T> struct Pair2;
-template <> struct Pair2<__half> {
-  static __device__ __forceinline__ float2 ld(const __half *p) { return __half22float2(*reinterpret_cast<const __half2 *>(p)); }
-  static __device__ __forceinline__ void st(__half *p, float a, float b) { *reinterpret_cast<__half2 *>(p) = __floats2half2_rn(a, b); }
+constexpr int kBatch = 16;         // chunks whose loads are in flight together
+constexpr int kCarryThreads = 256; // one block = 16 state rows (d) of one batch row, 4 columns (k) per thread
+constexpr int kCarryRows = kCarryThreads / (kDim / 4);
+
+template <typename T> struct Quad;
+template <> struct Quad<__half> {
+  static __device__ __forceinline__ float4 ld(const __half *p) {
+    const uint2 u = *reinterpret_cast<const uint2 *>(p);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&u.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void st(__half *p, float4 v) {
+    uint2 u;
+    *reinterpret_cast<__half2 *>(&u.x) = __floats2half2_rn(v.x, v.y);
+    *reinterpret_cast<__half2 *>(&u.y) = __floats2half2_rn(v.z, v.w);
+    *reinterpret_cast<uint2 *>(p) = u;
+  }
 };
-template <> struct Pair2<__nv_bfloat16> {
-  static __device__ __forceinline__ float2 ld(const __nv_bfloat16 *p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p)); }
-  static __device__ __forceinline__ void st(__nv_bfloat16 *p, float a, float b) { *reinterpret_cast<__nv_bfloat162 *>(p) = __floats2bfloat162_rn(a, b); }
+template <> struct Quad<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 ld(const __nv_bfloat16 *p) {
+    const uint2 u = *reinterpret_cast<const uint2 *>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void st(__nv_bfloat16 *p, float4 v) {
+    uint2 u;
+    *reinterpret_cast<__nv_bfloat162 *>(&u.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162 *>(&u.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2 *>(p) = u;
+  }
 };
 
-constexpr int kBatch = 16;     // chunks whose loads are in flight together
-
-// One thread per (row, d, two consecutive k).  The recurrence over the chunks is a dependent chain,
-// so the loads of up to 16 chunks are all issued before the chain starts: one round of memory
-// latency per 16 chunks.
+// One thread per (row, d, four consecutive k); a block covers 16 state rows of one batch row.  The
+// recurrence over the chunks is a dependent chain, so the loads of up to 16 chunks are all issued
+// before the chain starts (one round of memory latency per 16 chunks); the decay vectors of those
+// chunks are shared by the block and go through shared memory.
 //   kFwd:  S_{c+1} = (Ac Gc^T) S_c + L_c from the caller's state; checkpoint slot c = S_{c+1}
 //   !kFwd: R_end(c-1) = (Ac Gc^T) R_end(c) + G_c from grad_state, last chunk first; G_c is
 //          overwritten with R_end(c); the value left after chunk 0 is d_state
 template <typename T, bool kFwd>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kCarryThreads, 3)
 lfw_c64_carry_kernel(const T *__restrict__ init, float *__restrict__ M, const float *__restrict__ Ac,
                      const float *__restrict__ Gc, const int *__restrict__ flags, int *__restrict__ rowflag,
                      T *__restrict__ out, int64_t B, int64_t nc) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= B * kDim * (kDim / 2)) return;
-  const int64_t b = idx / (kDim * (kDim / 2));
-  const int d = (int)((idx / (kDim / 2)) % kDim);
-  const int k0 = (int)(idx % (kDim / 2)) * 2;
-  const float2 s0 = Pair2<T>::ld(init + ((size_t)b * kDim + d) * kDim + k0);
-  float S0 = s0.x, S1 = s0.y;
+  __shared__ float a_s[kBatch][kCarryRows];
+  __shared__ __align__(16) float g_s[kBatch][kDim];
+  const int tid = threadIdx.x;
+  const int64_t b = blockIdx.x / (kDim / kCarryRows);
+  const int d0 = (int)(blockIdx.x % (kDim / kCarryRows)) * kCarryRows;
+  const int dl = tid / (kDim / 4), d = d0 + dl, k0 = (tid % (kDim / 4)) * 4;
+  float4 S = Quad<T>::ld(init + ((size_t)b * kDim + d) * kDim + k0);
   int any = 0;
   for (int64_t c0 = 0; c0 < nc; c0 += kBatch) {
-    float2 l[kBatch], gg[kBatch];
-    float a[kBatch];
+    float4 l[kBatch];
 #pragma unroll
     for (int j = 0; j < kBatch; ++j) {
       int64_t c = c0 + j < nc ? c0 + j : nc - 1;
       if (!kFwd) c = nc - 1 - c;
-      const size_t bc = (size_t)b * nc + c;
-      l[j] = *reinterpret_cast<const float2 *>(M + (bc * kDim + d) * kDim + k0);
-      a[j] = Ac[bc * kDim + d];
-      gg[j] = *reinterpret_cast<const float2 *>(Gc + bc * kDim + k0);
-      if (d == 0 && k0 == 0) any |= flags[bc];
+      l[j] = *reinterpret_cast<const float4 *>(M + (((size_t)b * nc + c) * kDim + d) * kDim + k0);
     }
+    __syncthreads();      // the previous batch's decay vectors are no longer read
+    for (int i = tid; i < kBatch * (kCarryRows + kDim); i += kCarryThreads) {
+      const int j = i / (kCarryRows + kDim), r = i % (kCarryRows + kDim);
+      int64_t c = c0 + j < nc ? c0 + j : nc - 1;
+      if (!kFwd) c = nc - 1 - c;
+      const size_t bc = (size_t)b * nc + c;
+      if (r < kCarryRows) a_s[j][r] = Ac[bc * kDim + d0 + r];
+      else g_s[j][r - kCarryRows] = Gc[bc * kDim + r - kCarryRows];
+    }
+    if (tid == 0 && d0 == 0)
+      for (int j = 0; j < kBatch && c0 + j < nc; ++j) any |= flags[(size_t)b * nc + c0 + j];
+    __syncthreads();
 #pragma unroll
     for (int j = 0; j < kBatch; ++j) {
       if (c0 + j < nc) {
         const int64_t c = kFwd ? c0 + j : nc - 1 - (c0 + j);
-        const size_t bc = (size_t)b * nc + c;
-        if (!kFwd) *reinterpret_cast<float2 *>(M + (bc * kDim + d) * kDim + k0) = make_float2(S0, S1);
-        S0 = a[j] * gg[j].x * S0 + l[j].x;
-        S1 = a[j] * gg[j].y * S1 + l[j].y;
-        if (kFwd) Pair2<T>::st(out + (bc * kDim + d) * kDim + k0, S0, S1);
+        const size_t off = (((size_t)b * nc + c) * kDim + d) * kDim + k0;
+        if (!kFwd) *reinterpret_cast<float4 *>(M + off) = S;
+        const float a = a_s[j][dl];
+        const float4 g = *reinterpret_cast<const float4 *>(&g_s[j][k0]);
+        S.x = a * g.x * S.x + l[j].x;
+        S.y = a * g.y * S.y + l[j].y;
+        S.z = a * g.z * S.z + l[j].z;
+        S.w = a * g.w * S.w + l[j].w;
+        if (kFwd) Quad<T>::st(out + off, S);
       }
     }
   }
-  if (!kFwd) Pair2<T>::st(out + ((size_t)b * kDim + d) * kDim + k0, S0, S1);
-  if (d == 0 && k0 == 0) rowflag[b] = any;
+  if (!kFwd) Quad<T>::st(out + ((size_t)b * kDim + d) * kDim + k0, S);
+  if (tid == 0 && d0 == 0) rowflag[b] = any;
 }
 
 // One sequence tensor of a call: base pointer, width of a row (elements), column of head 0.
@@ -167,8 +201,7 @@ int forward_typed(const Call &c, const void *state, void *out, int64_t out_ld, i
   if (rc != T2FW_OK) return rc;
   rc = lfw_chunk_local_umma(false, mp, s.M, s.Ac, s.Gc, s.flags, BH, c.T_, dtype, st);
   if (rc != T2FW_OK) return rc;
-  const int64_t n_carry = BH * kDim * (kDim / 2);
-  lfw_c64_carry_kernel<T, true><<<(unsigned)ceil_div64(n_carry, 256), 256, 0, st>>>(
+  lfw_c64_carry_kernel<T, true><<<(unsigned)(BH * (kDim / kCarryRows)), kCarryThreads, 0, st>>>(
       (const T *)state, s.M, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ckpt, BH, nc);
   T2FW_CHECK_LAUNCH(1);
   const Tensor2D all[5] = {c.x, c.f, c.q, c.k, c.fk};
@@ -189,8 +222,7 @@ int backward_typed(const Call &c, const void *gs, const void *state, const void 
   if (rc != T2FW_OK) return rc;
   rc = lfw_chunk_local_umma(true, mp, s.M, s.Ac, s.Gc, s.flags, BH, c.T_, dtype, st);
   if (rc != T2FW_OK) return rc;
-  const int64_t n_carry = BH * kDim * (kDim / 2);
-  lfw_c64_carry_kernel<T, false><<<(unsigned)ceil_div64(n_carry, 256), 256, 0, st>>>(
+  lfw_c64_carry_kernel<T, false><<<(unsigned)(BH * (kDim / kCarryRows)), kCarryThreads, 0, st>>>(
       (const T *)gs, s.M, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ds, BH, nc);
   T2FW_CHECK_LAUNCH(1);
   const Tensor2D all[6] = {c.x, c.f, c.q, c.k, c.fk, c.go};
