@@ -66,6 +66,9 @@ def parse_args():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--ckpt-every", type=int, default=0,
+                   help="checkpoint interval of the C-ABI calls (0: the library's default, 64; "
+                        "BASELINE config 4 names 128)")
     p.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                    help="weak: every GPU runs the workload's batch rows; strong: the rows are split over the GPUs")
     p.add_argument("--rule", default="dfw", choices=["dfw", "lfw"],
@@ -454,7 +457,7 @@ def run_ours(args):
     # distinct data per set without regenerating on the host: roll along the batch axis
     sets = [base] + [[t.roll(i, 0).contiguous() for t in base] for i in range(1, n_sets)]
 
-    C = cabi.ckpt_every_for(T, D, K, dtype)
+    C = args.ckpt_every if args.ckpt_every > 0 else cabi.ckpt_every_for(T, D, K, dtype)
     code = cabi.dtype_code(base[0])
     if not dfw:
         slots = int(lib.t2fw_lfw_ckpt_slots(T, C))

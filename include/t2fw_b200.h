@@ -68,7 +68,9 @@ int t2fw_device_status(void);
 /* Checkpoint interval the library recommends for a problem, and the slot count that follows
  * from an interval.  The reference stores the state of EVERY step
  * (t2fw/csrc/lfw_kernel.cu:140-144); here only every ckpt_every-th state is kept and the
- * backward pass recomputes the rest. */
+ * backward pass recomputes the rest.  Any positive interval is accepted; multiples of 64 run on
+ * the tensor-core kernels (for D, K multiples of 64 and 16-bit storage), other intervals on the
+ * sequential scan kernels. */
 int64_t t2fw_lfw_default_ckpt_every(int64_t T, int64_t D, int64_t K, int dtype);
 int64_t t2fw_lfw_ckpt_slots(int64_t T, int64_t ckpt_every);
 

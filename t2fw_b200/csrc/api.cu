@@ -67,18 +67,18 @@ static bool chunk_path_enabled() {
 size_t t2fw_lfw_forward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K, int dtype,
                                       int64_t ckpt_every) {
   if (T > 1 && chunk_path_enabled() && lfw_chunk_supported(D, K, dtype, ckpt_every))
-    return lfw_chunk_forward_scratch_bytes(B, T);
+    return lfw_chunk_forward_scratch_bytes(B, T, ckpt_every);
   if (T > 1 && chunk_path_enabled() && lfw_blocked_supported(D, K, dtype, ckpt_every))
-    return lfw_blocked_forward_scratch_bytes(B, T, D, K);
+    return lfw_blocked_forward_scratch_bytes(B, T, D, K, ckpt_every);
   return 0;
 }
 
 size_t t2fw_lfw_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K, int dtype,
                                        int64_t ckpt_every) {
   if (chunk_path_enabled() && lfw_chunk_supported(D, K, dtype, ckpt_every))
-    return lfw_chunk_backward_scratch_bytes(B, T);
+    return lfw_chunk_backward_scratch_bytes(B, T, ckpt_every);
   if (chunk_path_enabled() && lfw_blocked_supported(D, K, dtype, ckpt_every))
-    return lfw_blocked_backward_scratch_bytes(B, T, D, K);
+    return lfw_blocked_backward_scratch_bytes(B, T, D, K, ckpt_every);
   return 0;
 }
 
@@ -161,10 +161,10 @@ int t2fw_lfw_forward(const void *x, const void *f, const void *q, const void *k,
     }
     if (!lfw_chunk_supported(D, K, dtype, ckpt_every))
       return lfw_blocked_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, T, D, K, dtype,
-                                 scratch, st);
+                                 ckpt_every, scratch, st);
     const int *rowflag = nullptr;
-    rc = lfw_chunk_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, T, dtype, scratch,
-                           st, &rowflag);
+    rc = lfw_chunk_forward(x, f, q, k, f_key, state, outputs, ckpt_states, B, T, dtype, ckpt_every,
+                           scratch, st, &rowflag);
     if (rc != T2FW_OK) return rc;
     // batch rows whose gate products left the range the factored form can hold are redone by
     // the scan kernel (it exits at once for all other rows)
@@ -197,10 +197,12 @@ int t2fw_lfw_backward(const void *grad_output, const void *grad_state, const voi
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!lfw_chunk_supported(D, K, dtype, ckpt_every))
       return lfw_blocked_backward(grad_output, grad_state, x, f, q, k, f_key, state, ckpt_states,
-                                  d_x, d_f, d_q, d_k, d_f_key, d_state, B, T, D, K, dtype, scratch, st);
+                                  d_x, d_f, d_q, d_k, d_f_key, d_state, B, T, D, K, dtype, ckpt_every,
+                                  scratch, st);
     const int *rowflag = nullptr;
     rc = lfw_chunk_backward(grad_output, grad_state, x, f, q, k, f_key, state, ckpt_states, d_x,
-                            d_f, d_q, d_k, d_f_key, d_state, B, T, dtype, scratch, st, &rowflag);
+                            d_f, d_q, d_k, d_f_key, d_state, B, T, dtype, ckpt_every, scratch, st,
+                            &rowflag);
     if (rc != T2FW_OK) return rc;
     return lfw_scan_backward(grad_output, grad_state, x, f, q, k, f_key, state, ckpt_states, d_x,
                              d_f, d_q, d_k, d_f_key, d_state, B, T, D, K, dtype, ckpt_every, st,

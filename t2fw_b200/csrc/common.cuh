@@ -94,28 +94,30 @@ int lfw_scan_backward(const void *go, const void *gs, const void *x, const void 
                       void *dx, void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B,
                       int64_t T, int64_t D, int64_t K, int dtype, int64_t C, cudaStream_t st,
                       const int *rowflag = nullptr);
-// chunked tensor-core path (D = K = 64, 16-bit storage, checkpoint interval 64)
+// chunked tensor-core path (D = K = 64, 16-bit storage, checkpoint interval a multiple of 64)
 bool lfw_chunk_supported(int64_t D, int64_t K, int dtype, int64_t ckpt_every);
-size_t lfw_chunk_forward_scratch_bytes(int64_t B, int64_t T);
+size_t lfw_chunk_forward_scratch_bytes(int64_t B, int64_t T, int64_t ckpt_every);
 int lfw_chunk_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,
                       const void *state, void *out, void *ckpt, int64_t B, int64_t T, int dtype,
-                      void *scratch, cudaStream_t st, const int **rowflag_out);
-size_t lfw_chunk_backward_scratch_bytes(int64_t B, int64_t T);
+                      int64_t ckpt_every, void *scratch, cudaStream_t st, const int **rowflag_out);
+size_t lfw_chunk_backward_scratch_bytes(int64_t B, int64_t T, int64_t ckpt_every);
 int lfw_chunk_backward(const void *go, const void *gs, const void *x, const void *f, const void *q,
                        const void *k, const void *fk, const void *state, const void *ckpt, void *dx,
                        void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B, int64_t T,
-                       int dtype, void *scratch, cudaStream_t st, const int **rowflag_out);
+                       int dtype, int64_t ckpt_every, void *scratch, cudaStream_t st,
+                       const int **rowflag_out);
 // state shapes that are grids of 64 x 64 blocks (D, K multiples of 64, up to 256)
 bool lfw_blocked_supported(int64_t D, int64_t K, int dtype, int64_t ckpt_every);
-size_t lfw_blocked_forward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K);
-size_t lfw_blocked_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K);
+size_t lfw_blocked_forward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K, int64_t ckpt_every);
+size_t lfw_blocked_backward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K, int64_t ckpt_every);
 int lfw_blocked_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,
                         const void *state, void *out, void *ckpt, int64_t B, int64_t T, int64_t D,
-                        int64_t K, int dtype, void *scratch, cudaStream_t st);
+                        int64_t K, int dtype, int64_t ckpt_every, void *scratch, cudaStream_t st);
 int lfw_blocked_backward(const void *go, const void *gs, const void *x, const void *f, const void *q,
                          const void *k, const void *fk, const void *state, const void *ckpt, void *dx,
                          void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B, int64_t T,
-                         int64_t D, int64_t K, int dtype, void *scratch, cudaStream_t st);
+                         int64_t D, int64_t K, int dtype, int64_t ckpt_every, void *scratch,
+                         cudaStream_t st);
 // fused layer form of the chunked path: qkvg [B][T][4*H*64] read in place (lfw_c64_host.cu)
 size_t lfw_fused_scratch_bytes(int64_t B, int64_t T, int H);
 int lfw_fused_forward(const void *qkvg, const void *state, void *out, void *ckpt, int64_t B, int64_t T, int H,

@@ -96,18 +96,19 @@ inline unsigned grid_for(int64_t n_items) {
 }
 
 struct Layout {
-  int64_t B, T_, D, K, nd, nk, VB, slots;
+  int64_t B, T_, D, K, nd, nk, VB, slots, ckpt_every;
   size_t esz;
   size_t vec() const { return (size_t)VB * T_ * kBlk * esz; }          // one virtual-batch vector tensor
   size_t st() const { return (size_t)VB * kBlk * kBlk * esz; }         // one virtual-batch state
   size_t ck() const { return (size_t)VB * slots * kBlk * kBlk * esz; } // virtual-batch checkpoints
 };
 
-Layout make_layout(int64_t B, int64_t T_, int64_t D, int64_t K) {
+Layout make_layout(int64_t B, int64_t T_, int64_t D, int64_t K, int64_t ckpt_every) {
   Layout l;
   l.B = B; l.T_ = T_; l.D = D; l.K = K;
   l.nd = D / kBlk; l.nk = K / kBlk; l.VB = B * l.nd * l.nk;
-  l.slots = ceil_div64(T_, kC);
+  l.slots = ceil_div64(T_, ckpt_every);
+  l.ckpt_every = ckpt_every;
   l.esz = 2;
   return l;
 }
@@ -135,9 +136,9 @@ int blocked_forward_typed(const void *x, const void *f, const void *q, const voi
       (T *)const_cast<void *>(state), sq, l.B, 1, (int)l.D, (int)l.K, (int)l.nd, (int)l.nk);
   T2FW_CHECK_LAUNCH(6);
   const int *rowflag = nullptr;
-  int rc = lfw_chunk_forward(xq, fq, qq, kq, fkq, sq, oq, cq, l.VB, l.T_, dt, inner, st, &rowflag);
+  int rc = lfw_chunk_forward(xq, fq, qq, kq, fkq, sq, oq, cq, l.VB, l.T_, dt, l.ckpt_every, inner, st, &rowflag);
   if (rc != T2FW_OK) return rc;
-  rc = lfw_scan_forward(xq, fq, qq, kq, fkq, sq, oq, cq, l.VB, l.T_, kBlk, kBlk, dt, kC, st, rowflag);
+  rc = lfw_scan_forward(xq, fq, qq, kq, fkq, sq, oq, cq, l.VB, l.T_, kBlk, kBlk, dt, l.ckpt_every, st, rowflag);
   if (rc != T2FW_OK) return rc;
   combine_vec_kernel<T><<<grid_for(l.B * l.T_ * l.nd * (kBlk / 2)), 256, 0, st>>>(
       oq, (T *)out, l.B, l.T_, (int)l.D, (int)l.nd, (int)l.nk, 1);
@@ -178,10 +179,10 @@ int blocked_backward_typed(const void *go, const void *gs, const void *x, const 
   T2FW_CHECK_LAUNCH(9);
   const int *rowflag = nullptr;
   int rc = lfw_chunk_backward(goq, gsq, xq, fq, qq, kq, fkq, sq, cq, dxq, dfq, dqq, dkq, dfkq, dsq, l.VB,
-                              l.T_, dt, inner, st, &rowflag);
+                              l.T_, dt, l.ckpt_every, inner, st, &rowflag);
   if (rc != T2FW_OK) return rc;
   rc = lfw_scan_backward(goq, gsq, xq, fq, qq, kq, fkq, sq, cq, dxq, dfq, dqq, dkq, dfkq, dsq, l.VB, l.T_,
-                         kBlk, kBlk, dt, kC, st, rowflag);
+                         kBlk, kBlk, dt, l.ckpt_every, st, rowflag);
   if (rc != T2FW_OK) return rc;
   const unsigned gd = grid_for(l.B * l.T_ * l.nd * (kBlk / 2)), gk = grid_for(l.B * l.T_ * l.nk * (kBlk / 2));
   combine_vec_kernel<T><<<gd, 256, 0, st>>>(dxq, (T *)dx, l.B, l.T_, D, nd, nk, 1);
@@ -198,25 +199,25 @@ int blocked_backward_typed(const void *go, const void *gs, const void *x, const 
 
 bool lfw_blocked_supported(int64_t D, int64_t K, int dtype, int64_t ckpt_every) {
   if (dtype != T2FW_F16 && dtype != T2FW_BF16) return false;
-  if (ckpt_every != kC) return false;
+  if (ckpt_every < kC || ckpt_every % kC != 0) return false;
   if (D % kBlk != 0 || K % kBlk != 0 || D > 256 || K > 256) return false;
   return D > kBlk || K > kBlk;
 }
 
-size_t lfw_blocked_forward_scratch_bytes(int64_t B, int64_t T_, int64_t D, int64_t K) {
-  const Layout l = make_layout(B, T_, D, K);
-  return 6 * a256(l.vec()) + a256(l.st()) + a256(l.ck()) + lfw_chunk_forward_scratch_bytes(l.VB, T_);
+size_t lfw_blocked_forward_scratch_bytes(int64_t B, int64_t T_, int64_t D, int64_t K, int64_t ckpt_every) {
+  const Layout l = make_layout(B, T_, D, K, ckpt_every);
+  return 6 * a256(l.vec()) + a256(l.st()) + a256(l.ck()) + lfw_chunk_forward_scratch_bytes(l.VB, T_, ckpt_every);
 }
 
-size_t lfw_blocked_backward_scratch_bytes(int64_t B, int64_t T_, int64_t D, int64_t K) {
-  const Layout l = make_layout(B, T_, D, K);
-  return 11 * a256(l.vec()) + 3 * a256(l.st()) + a256(l.ck()) + lfw_chunk_backward_scratch_bytes(l.VB, T_);
+size_t lfw_blocked_backward_scratch_bytes(int64_t B, int64_t T_, int64_t D, int64_t K, int64_t ckpt_every) {
+  const Layout l = make_layout(B, T_, D, K, ckpt_every);
+  return 11 * a256(l.vec()) + 3 * a256(l.st()) + a256(l.ck()) + lfw_chunk_backward_scratch_bytes(l.VB, T_, ckpt_every);
 }
 
 int lfw_blocked_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,
                         const void *state, void *out, void *ckpt, int64_t B, int64_t T_, int64_t D,
-                        int64_t K, int dtype, void *scratch, cudaStream_t st) {
-  const Layout l = make_layout(B, T_, D, K);
+                        int64_t K, int dtype, int64_t ckpt_every, void *scratch, cudaStream_t st) {
+  const Layout l = make_layout(B, T_, D, K, ckpt_every);
   if (dtype == T2FW_F16)
     return blocked_forward_typed<__half>(x, f, q, k, fk, state, out, ckpt, l, scratch, st);
   return blocked_forward_typed<__nv_bfloat16>(x, f, q, k, fk, state, out, ckpt, l, scratch, st);
@@ -225,8 +226,8 @@ int lfw_blocked_forward(const void *x, const void *f, const void *q, const void 
 int lfw_blocked_backward(const void *go, const void *gs, const void *x, const void *f, const void *q,
                          const void *k, const void *fk, const void *state, const void *ckpt, void *dx,
                          void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B, int64_t T_,
-                         int64_t D, int64_t K, int dtype, void *scratch, cudaStream_t st) {
-  const Layout l = make_layout(B, T_, D, K);
+                         int64_t D, int64_t K, int dtype, int64_t ckpt_every, void *scratch, cudaStream_t st) {
+  const Layout l = make_layout(B, T_, D, K, ckpt_every);
   if (dtype == T2FW_F16)
     return blocked_backward_typed<__half>(go, gs, x, f, q, k, fk, state, ckpt, dx, df, dq, dk, dfk, ds,
                                           l, scratch, st);

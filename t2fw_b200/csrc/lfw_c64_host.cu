@@ -35,10 +35,17 @@ namespace {
 struct Scratch {
   float *M, *Ac, *Gc;
   int *flags, *rowflag;
+  void *ck_all;      // 16-bit states after every chunk [B][nc][64][64]; only for checkpoint intervals > 64
 };
 
 inline size_t scratch_floats(int64_t B, int64_t nc) {
   return (size_t)B * nc * kDim * kDim + 2 * (size_t)B * nc * kDim + (size_t)B * nc + (size_t)B;
+}
+
+inline size_t scratch_bytes(int64_t B, int64_t nc, int64_t ckpt_every) {
+  size_t n = align_up(scratch_floats(B, nc) * sizeof(float), 256);
+  if (ckpt_every != kC) n += align_up((size_t)B * nc * kDim * kDim * 2, 256);
+  return n;
 }
 
 inline Scratch carve(void *scratch, int64_t B, int64_t nc) {
@@ -48,6 +55,7 @@ inline Scratch carve(void *scratch, int64_t B, int64_t nc) {
   s.Gc = s.Ac + (size_t)B * nc * kDim;
   s.flags = reinterpret_cast<int *>(s.Gc + (size_t)B * nc * kDim);
   s.rowflag = s.flags + (size_t)B * nc;
+  s.ck_all = static_cast<unsigned char *>(scratch) + align_up(scratch_floats(B, nc) * sizeof(float), 256);
   return s;
 }
 
@@ -96,7 +104,7 @@ template <typename T, bool kFwd>
 __global__ void __launch_bounds__(kCarryThreads, 3)
 lfw_c64_carry_kernel(const T *__restrict__ init, float *__restrict__ M, const float *__restrict__ Ac,
                      const float *__restrict__ Gc, const int *__restrict__ flags, int *__restrict__ rowflag,
-                     T *__restrict__ out, int64_t B, int64_t nc) {
+                     int keep_rowflag, T *__restrict__ out, int64_t B, int64_t nc) {
   __shared__ float a_s[kBatch][kCarryRows];
   __shared__ __align__(16) float g_s[kBatch][kDim];
   const int tid = threadIdx.x;
@@ -142,7 +150,23 @@ lfw_c64_carry_kernel(const T *__restrict__ init, float *__restrict__ M, const fl
     }
   }
   if (!kFwd) Quad<T>::st(out + ((size_t)b * kDim + d) * kDim + k0, S);
-  if (tid == 0 && d0 == 0) rowflag[b] = any;
+  if (tid == 0 && d0 == 0) rowflag[b] = keep_rowflag ? (rowflag[b] | any) : any;
+}
+
+// Checkpoint interval of m chunks: slot j of the caller's checkpoints = state after chunk
+// min((j + 1) m, nc) - 1 of the per-chunk states.
+template <typename T>
+__global__ void __launch_bounds__(256)
+lfw_c64_pick_ckpt_kernel(const T *__restrict__ all, T *__restrict__ ckpt, int64_t B, int64_t nc, int64_t m,
+                         int64_t slots) {
+  constexpr int kVec = kDim * kDim / 8;      // 16-byte pieces of one state
+  const int64_t n = B * slots * kVec;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t v = i % kVec, j = (i / kVec) % slots, b = i / (kVec * slots);
+    const int64_t c = ((j + 1) * m < nc ? (j + 1) * m : nc) - 1;
+    reinterpret_cast<uint4 *>(ckpt)[(b * slots + j) * kVec + v] =
+        reinterpret_cast<const uint4 *>(all)[(b * nc + c) * kVec + v];
+  }
 }
 
 // One sequence tensor of a call: base pointer, width of a row (elements), column of head 0.
@@ -190,11 +214,10 @@ struct Call {
   float q_scale;
 };
 
+// The states after every chunk (16-bit) from the caller's state: local kernel + carry.
 template <typename T>
-int forward_typed(const Call &c, const void *state, void *out, int64_t out_ld, int out_col, void *ckpt, int dtype,
-                  void *scratch, cudaStream_t st) {
+int chunk_states(const Call &c, const Scratch &s, const void *state, T *ck_all, int dtype, cudaStream_t st) {
   const int64_t BH = c.B * c.heads, nc = ceil_div64(c.T_, kC), rows = c.B * c.T_;
-  Scratch s = carve(scratch, BH, nc);
   seq::Maps mp;
   const Tensor2D loc[4] = {c.x, c.f, c.k, c.fk};
   int rc = build_maps(mp, loc, 4, rows, c.heads, c.flags, 1.f);
@@ -202,20 +225,48 @@ int forward_typed(const Call &c, const void *state, void *out, int64_t out_ld, i
   rc = lfw_chunk_local_umma(false, mp, s.M, s.Ac, s.Gc, s.flags, BH, c.T_, dtype, st);
   if (rc != T2FW_OK) return rc;
   lfw_c64_carry_kernel<T, true><<<(unsigned)(BH * (kDim / kCarryRows)), kCarryThreads, 0, st>>>(
-      (const T *)state, s.M, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ckpt, BH, nc);
+      (const T *)state, s.M, s.Ac, s.Gc, s.flags, s.rowflag, 0, ck_all, BH, nc);
   T2FW_CHECK_LAUNCH(1);
+  return T2FW_OK;
+}
+
+// ckpt_every = m * 64.  m = 1: the carry writes the caller's checkpoints directly.  m > 1: the
+// per-chunk states go to scratch and every m-th one (and the last) is copied out.
+template <typename T>
+int forward_typed(const Call &c, const void *state, void *out, int64_t out_ld, int out_col, void *ckpt, int dtype,
+                  int64_t ckpt_every, void *scratch, cudaStream_t st) {
+  const int64_t BH = c.B * c.heads, nc = ceil_div64(c.T_, kC), rows = c.B * c.T_, m = ckpt_every / kC;
+  Scratch s = carve(scratch, BH, nc);
+  T *ck_all = m == 1 ? (T *)ckpt : (T *)s.ck_all;
+  int rc = chunk_states<T>(c, s, state, ck_all, dtype, st);
+  if (rc != T2FW_OK) return rc;
+  seq::Maps mp;
   const Tensor2D all[5] = {c.x, c.f, c.q, c.k, c.fk};
   rc = build_maps(mp, all, 5, rows, c.heads, c.flags, c.q_scale);
   if (rc != T2FW_OK) return rc;
-  return lfw_c64_forward_out(mp, state, ckpt, out, out_ld, out_col, s.rowflag, BH, c.T_, dtype, st);
+  rc = lfw_c64_forward_out(mp, state, ck_all, out, out_ld, out_col, s.rowflag, BH, c.T_, dtype, st);
+  if (rc != T2FW_OK || m == 1) return rc;
+  const int64_t slots = ceil_div64(c.T_, ckpt_every), n = BH * slots * (kDim * kDim / 8);
+  const int64_t blocks = ceil_div64(n, 256);
+  lfw_c64_pick_ckpt_kernel<T><<<(unsigned)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, st>>>(
+      ck_all, (T *)ckpt, BH, nc, m, slots);
+  T2FW_CHECK_LAUNCH(1);
+  return T2FW_OK;
 }
 
+// ckpt_every > 64: the states at the chunk starts that the caller's checkpoints do not hold are
+// rebuilt from the caller's state first, exactly as the forward call built them.
 template <typename T>
 int backward_typed(const Call &c, const void *gs, const void *state, const void *ckpt, void *const outs[5],
-                   const int64_t out_ld[5], const int out_col[5], void *ds, int dtype, void *scratch,
-                   cudaStream_t st) {
-  const int64_t BH = c.B * c.heads, nc = ceil_div64(c.T_, kC), rows = c.B * c.T_;
+                   const int64_t out_ld[5], const int out_col[5], void *ds, int dtype, int64_t ckpt_every,
+                   void *scratch, cudaStream_t st) {
+  const int64_t BH = c.B * c.heads, nc = ceil_div64(c.T_, kC), rows = c.B * c.T_, m = ckpt_every / kC;
   Scratch s = carve(scratch, BH, nc);
+  if (m > 1) {
+    const int rc0 = chunk_states<T>(c, s, state, (T *)s.ck_all, dtype, st);
+    if (rc0 != T2FW_OK) return rc0;
+    ckpt = s.ck_all;
+  }
   seq::Maps mp;
   const Tensor2D loc[4] = {c.go, c.f, c.q, c.fk};
   int rc = build_maps(mp, loc, 4, rows, c.heads, c.flags, c.q_scale);
@@ -223,7 +274,7 @@ int backward_typed(const Call &c, const void *gs, const void *state, const void 
   rc = lfw_chunk_local_umma(true, mp, s.M, s.Ac, s.Gc, s.flags, BH, c.T_, dtype, st);
   if (rc != T2FW_OK) return rc;
   lfw_c64_carry_kernel<T, false><<<(unsigned)(BH * (kDim / kCarryRows)), kCarryThreads, 0, st>>>(
-      (const T *)gs, s.M, s.Ac, s.Gc, s.flags, s.rowflag, (T *)ds, BH, nc);
+      (const T *)gs, s.M, s.Ac, s.Gc, s.flags, s.rowflag, m > 1 ? 1 : 0, (T *)ds, BH, nc);
   T2FW_CHECK_LAUNCH(1);
   const Tensor2D all[6] = {c.x, c.f, c.q, c.k, c.fk, c.go};
   rc = build_maps(mp, all, 6, rows, c.heads, c.flags, c.q_scale);
@@ -255,50 +306,52 @@ Call fused_call(const void *qkvg, const void *go, int64_t B, int64_t T_, int H) 
 }  // namespace
 
 bool lfw_chunk_supported(int64_t D, int64_t K, int dtype, int64_t ckpt_every) {
-  return D == kDim && K == kDim && ckpt_every == kC && (dtype == T2FW_F16 || dtype == T2FW_BF16);
+  return D == kDim && K == kDim && ckpt_every >= kC && ckpt_every % kC == 0 &&
+         (dtype == T2FW_F16 || dtype == T2FW_BF16);
 }
 
-size_t lfw_chunk_forward_scratch_bytes(int64_t B, int64_t T_) {
-  return align_up(scratch_floats(B, ceil_div64(T_, kC)) * sizeof(float), 256);
+size_t lfw_chunk_forward_scratch_bytes(int64_t B, int64_t T_, int64_t ckpt_every) {
+  return scratch_bytes(B, ceil_div64(T_, kC), ckpt_every);
 }
 
-size_t lfw_chunk_backward_scratch_bytes(int64_t B, int64_t T_) {
-  return align_up(scratch_floats(B, ceil_div64(T_, kC)) * sizeof(float), 256);
+size_t lfw_chunk_backward_scratch_bytes(int64_t B, int64_t T_, int64_t ckpt_every) {
+  return scratch_bytes(B, ceil_div64(T_, kC), ckpt_every);
 }
 
 // Both calls need every pointer 16-byte aligned (the C ABI routes other callers to the scan
 // kernels).
 int lfw_chunk_forward(const void *x, const void *f, const void *q, const void *k, const void *fk,
                       const void *state, void *out, void *ckpt, int64_t B, int64_t T_, int dtype,
-                      void *scratch, cudaStream_t st, const int **rowflag_out) {
+                      int64_t ckpt_every, void *scratch, cudaStream_t st, const int **rowflag_out) {
   if (rowflag_out) *rowflag_out = carve(scratch, B, ceil_div64(T_, kC)).rowflag;
   const Call c = plain_call(x, f, q, k, fk, nullptr, B, T_);
-  if (dtype == T2FW_F16) return forward_typed<__half>(c, state, out, kDim, 0, ckpt, dtype, scratch, st);
-  return forward_typed<__nv_bfloat16>(c, state, out, kDim, 0, ckpt, dtype, scratch, st);
+  if (dtype == T2FW_F16) return forward_typed<__half>(c, state, out, kDim, 0, ckpt, dtype, ckpt_every, scratch, st);
+  return forward_typed<__nv_bfloat16>(c, state, out, kDim, 0, ckpt, dtype, ckpt_every, scratch, st);
 }
 
 int lfw_chunk_backward(const void *go, const void *gs, const void *x, const void *f, const void *q,
                        const void *k, const void *fk, const void *state, const void *ckpt, void *dx,
                        void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B, int64_t T_,
-                       int dtype, void *scratch, cudaStream_t st, const int **rowflag_out) {
+                       int dtype, int64_t ckpt_every, void *scratch, cudaStream_t st, const int **rowflag_out) {
   if (rowflag_out) *rowflag_out = carve(scratch, B, ceil_div64(T_, kC)).rowflag;
   const Call c = plain_call(x, f, q, k, fk, go, B, T_);
   void *const outs[5] = {dx, df, dq, dk, dfk};
   const int64_t ld[5] = {kDim, kDim, kDim, kDim, kDim};
   const int col[5] = {0, 0, 0, 0, 0};
-  if (dtype == T2FW_F16) return backward_typed<__half>(c, gs, state, ckpt, outs, ld, col, ds, dtype, scratch, st);
-  return backward_typed<__nv_bfloat16>(c, gs, state, ckpt, outs, ld, col, ds, dtype, scratch, st);
+  if (dtype == T2FW_F16)
+    return backward_typed<__half>(c, gs, state, ckpt, outs, ld, col, ds, dtype, ckpt_every, scratch, st);
+  return backward_typed<__nv_bfloat16>(c, gs, state, ckpt, outs, ld, col, ds, dtype, ckpt_every, scratch, st);
 }
 
 // ---- fused layer entry points (heads read in place from the projection output) ----------------
-size_t lfw_fused_scratch_bytes(int64_t B, int64_t T_, int H) { return lfw_chunk_forward_scratch_bytes(B * H, T_); }
+size_t lfw_fused_scratch_bytes(int64_t B, int64_t T_, int H) { return lfw_chunk_forward_scratch_bytes(B * H, T_, kC); }
 
 int lfw_fused_forward(const void *qkvg, const void *state, void *out, void *ckpt, int64_t B, int64_t T_, int H,
                       int dtype, void *scratch, cudaStream_t st) {
   const Call c = fused_call(qkvg, nullptr, B, T_, H);
   const int64_t C = (int64_t)H * kDim;
-  if (dtype == T2FW_F16) return forward_typed<__half>(c, state, out, C, 0, ckpt, dtype, scratch, st);
-  return forward_typed<__nv_bfloat16>(c, state, out, C, 0, ckpt, dtype, scratch, st);
+  if (dtype == T2FW_F16) return forward_typed<__half>(c, state, out, C, 0, ckpt, dtype, kC, scratch, st);
+  return forward_typed<__nv_bfloat16>(c, state, out, C, 0, ckpt, dtype, kC, scratch, st);
 }
 
 int lfw_fused_backward(const void *go, const void *gs, const void *qkvg, const void *state, const void *ckpt,
@@ -310,8 +363,8 @@ int lfw_fused_backward(const void *go, const void *gs, const void *qkvg, const v
   void *const outs[5] = {d_qkvg, nullptr, d_qkvg, d_qkvg, d_qkvg};
   const int64_t ld[5] = {4 * C, 0, 4 * C, 4 * C, 4 * C};
   const int col[5] = {(int)(2 * C), 0, 0, (int)C, (int)(3 * C)};
-  if (dtype == T2FW_F16) return backward_typed<__half>(c, gs, state, ckpt, outs, ld, col, ds, dtype, scratch, st);
-  return backward_typed<__nv_bfloat16>(c, gs, state, ckpt, outs, ld, col, ds, dtype, scratch, st);
+  if (dtype == T2FW_F16) return backward_typed<__half>(c, gs, state, ckpt, outs, ld, col, ds, dtype, kC, scratch, st);
+  return backward_typed<__nv_bfloat16>(c, gs, state, ckpt, outs, ld, col, ds, dtype, kC, scratch, st);
 }
 
 }  // namespace t2fw

@@ -257,3 +257,32 @@ def test_many_tiny_gates_in_one_chunk(cuda):
     fk[2, 130, 7] = 1e-4          # a single one in row 2
     dev = to_dev((x, f, q, k, fk, s, go, gs), torch.float16, cuda)
     check_against_oracle(dev, run_cabi(*dev), torch.float16)
+
+
+@pytest.mark.parametrize("D,T,ckpt_every", [(64, 300, 128), (64, 256, 128), (64, 500, 192), (64, 70, 256), (128, 330, 128)])
+def test_checkpoint_intervals_of_several_chunks(cuda, D, T, ckpt_every):
+    """Checkpoint intervals that are multiples of 64 (BASELINE config 4 names 128) stay on the
+    tensor-core path: the per-chunk states live in scratch, the caller's checkpoints hold every
+    ckpt_every-th state and the final one, and the backward call rebuilds what it needs."""
+    from t2fw_b200 import cabi
+
+    x, f, q, k, fk, s, go, gs = lfw_inputs(3, T, D, D, "sigmoid", 0.5, 300 + T)
+    if D == 64:
+        fk[1] = 1e-3          # one batch row that the scan kernels have to redo
+    dev = to_dev((x, f, q, k, fk, s, go, gs), torch.float16, cuda)
+    from t2fw_b200 import _lib
+
+    need = _lib.load_core().t2fw_lfw_forward_scratch_bytes(3, T, D, D, 0, ckpt_every)
+    assert need > 0, "not on the tensor-core path"
+    got = run_cabi(*dev, ckpt_every=ckpt_every)
+    check_against_oracle(dev, got, torch.float16)
+    # every slot of the checkpoints against the oracle's state after that many steps
+    xd, fd, qd, kd, fkd, sd = dev[:6]
+    _, ckpt = cabi.lfw_forward(xd, fd, qd, kd, fkd, sd, ckpt_every=ckpt_every)
+    torch.cuda.synchronize()
+    slots = math.ceil(T / ckpt_every)
+    assert ckpt.shape[1] == slots
+    for j in range(slots):
+        t_end = min((j + 1) * ckpt_every, T)
+        _, r_state = fw_oracle.lfw_forward(xd[:, :t_end], fd[:, :t_end], qd[:, :t_end], kd[:, :t_end], fkd[:, :t_end], sd)
+        assert max_rel_err(ckpt[:, j], r_state) <= OUT_TOL[torch.float16], j
