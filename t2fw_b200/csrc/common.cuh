@@ -106,6 +106,18 @@ int lfw_chunk_backward(const void *go, const void *gs, const void *x, const void
                        void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B, int64_t T,
                        int dtype, int64_t ckpt_every, void *scratch, cudaStream_t st,
                        const int **rowflag_out);
+// the same for a batch of D x K states cut into (D/64) x (K/64) blocks: sequence inputs dense
+// [B*T][D] / [B*T][K] read in place; states, checkpoints and all results per block
+// ([B * nd * nk][..][64][64] and [B * nd * nk][T][64], block (i, j) of item b at b * nd * nk + i * nk + j)
+int lfw_chunk_forward_grid(const void *x, const void *f, const void *q, const void *k, const void *fk,
+                           const void *state_blocks, void *out_blocks, void *ckpt_blocks, int64_t B, int64_t T,
+                           int nd, int nk, int dtype, int64_t ckpt_every, void *scratch, cudaStream_t st,
+                           const int **rowflag_out);
+int lfw_chunk_backward_grid(const void *go, const void *gs_blocks, const void *x, const void *f, const void *q,
+                            const void *k, const void *fk, const void *state_blocks, const void *ckpt_blocks,
+                            void *dx, void *df, void *dq, void *dk, void *dfk, void *ds_blocks, int64_t B, int64_t T,
+                            int nd, int nk, int dtype, int64_t ckpt_every, void *scratch, cudaStream_t st,
+                            const int **rowflag_out);
 // state shapes that are grids of 64 x 64 blocks (D, K multiples of 64, up to 256)
 bool lfw_blocked_supported(int64_t D, int64_t K, int dtype, int64_t ckpt_every);
 size_t lfw_blocked_forward_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K, int64_t ckpt_every);

@@ -6,11 +6,13 @@
 // to slice j.  Everything that leaves the state is a sum over the other axis' blocks:
 //   outputs, d_x, d_f  [.., slice i] = sum over j of block (i, j)'s result
 //   d_q, d_k, d_f_key  [.., slice j] = sum over i of block (i, j)'s result
-// while checkpoints, next state and d_state are block-local.  The blocks are laid out as a
-// virtual batch of B * (D/64) * (K/64) rows with 64-wide contiguous vectors, run through the
-// chunked 64 x 64 kernels (and, for rows they flag, the scan kernels), and the per-block
-// results are summed in fp32.  This is what makes the long-sequence configuration (D = K = 128, T = 16384)
-// run on the tensor-core path.
+// while checkpoints, next state and d_state are block-local.  The blocks form a virtual batch of
+// B * (D/64) * (K/64) problem rows for the chunked 64 x 64 kernels, which read each block's
+// 64-column window of the caller's [B*T][D] / [B*T][K] arrays in place (tensor-map copies) and write
+// per-block result arrays; those are summed in fp32 over the other axis' blocks.  Only the states and
+// checkpoints are re-laid out per block.  For blocks the chunk kernels flag, contiguous copies of
+// the windows are gathered and the scan kernels redo them.  This is what makes the long-sequence
+// configuration (D = K = 128, T = 16384) run on the tensor-core path.
 #include <type_traits>
 
 #include "lfw_chunk.cuh"
@@ -23,22 +25,28 @@ namespace {
 
 constexpr int kBlk = 64;
 
-// dst[((b*nd + i)*nk + j)][t][0..63] = src[b][t][sel*64 ..], sel = i (d side) or j (k side)
+// dst[((b*nd + i)*nk + j)][t][0..63] = src[b][t][sel*64 ..], sel = i (d side) or j (k side), for the
+// blocks whose flag is set (the ones the scan kernels have to redo; the chunk kernels read the
+// windows in place).  A CTA takes (block, slice of the steps) items, so that in the usual case
+// (no flag set) every CTA leaves after a few flag reads.
+constexpr int kGatherSlices = 16;
 template <typename T>
 __global__ void __launch_bounds__(256)
 gather_vec_kernel(const T *__restrict__ src, T *__restrict__ dst, int64_t B, int64_t T_, int W, int nd,
-                  int nk, int dside) {
-  const int64_t n = B * nd * nk * T_ * (kBlk / 8);
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    const int ch = (int)(idx % (kBlk / 8));
-    const int64_t t = (idx / (kBlk / 8)) % T_;
-    const int64_t vb = idx / ((kBlk / 8) * T_);
+                  int nk, int dside, const int *__restrict__ rowflag) {
+  const int64_t VB = B * nd * nk, per = (T_ + kGatherSlices - 1) / kGatherSlices;
+  for (int64_t item = blockIdx.x; item < VB * kGatherSlices; item += gridDim.x) {
+    const int64_t vb = item / kGatherSlices, t0 = (item % kGatherSlices) * per;
+    if (rowflag[vb] == 0) continue;
     const int j = (int)(vb % nk), i = (int)((vb / nk) % nd);
-    const int64_t b = vb / ((int64_t)nk * nd);
+    const int64_t b = vb / ((int64_t)nk * nd), t1 = t0 + per < T_ ? t0 + per : T_;
     const int sel = dside ? i : j;
-    const uint4 v = *reinterpret_cast<const uint4 *>(src + (b * T_ + t) * W + sel * kBlk + ch * 8);
-    *reinterpret_cast<uint4 *>(dst + (vb * T_ + t) * kBlk + ch * 8) = v;
+    for (int64_t e = threadIdx.x; e < (t1 - t0) * (kBlk / 8); e += blockDim.x) {
+      const int64_t t = t0 + e / (kBlk / 8);
+      const int ch = (int)(e % (kBlk / 8));
+      *reinterpret_cast<uint4 *>(dst + (vb * T_ + t) * kBlk + ch * 8) =
+          *reinterpret_cast<const uint4 *>(src + (b * T_ + t) * W + sel * kBlk + ch * 8);
+    }
   }
 }
 
@@ -65,28 +73,38 @@ state_blocks_kernel(T *__restrict__ dense, T *__restrict__ blocks, int64_t B, in
   }
 }
 
-// dst[b][t][sel*64 + e] = sum over the other block index of src[((b*nd + i)*nk + j)][t][e]
+// dst[b][t][sel*64 + e] = sum over the other block index of src[((b*nd + i)*nk + j)][t][e];
+// eight elements (16 bytes) per thread
 template <typename T>
 __global__ void __launch_bounds__(256)
 combine_vec_kernel(const T *__restrict__ src, T *__restrict__ dst, int64_t B, int64_t T_, int W, int nd,
                    int nk, int dside) {
   const int nsel = dside ? nd : nk, nother = dside ? nk : nd;
-  const int64_t n = B * T_ * nsel * (kBlk / 2);
+  const int64_t n = B * T_ * nsel * (kBlk / 8);
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
        idx += (int64_t)gridDim.x * blockDim.x) {
-    const int e2 = (int)(idx % (kBlk / 2));
-    const int sel = (int)((idx / (kBlk / 2)) % nsel);
-    const int64_t t = (idx / ((int64_t)(kBlk / 2) * nsel)) % T_;
-    const int64_t b = idx / ((int64_t)(kBlk / 2) * nsel * T_);
-    float a0 = 0.f, a1 = 0.f;
+    const int e8 = (int)(idx % (kBlk / 8));
+    const int sel = (int)((idx / (kBlk / 8)) % nsel);
+    const int64_t t = (idx / ((int64_t)(kBlk / 8) * nsel)) % T_;
+    const int64_t b = idx / ((int64_t)(kBlk / 8) * nsel * T_);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int o = 0; o < nother; ++o) {
       const int i = dside ? sel : o, j = dside ? o : sel;
       const int64_t vb = (b * nd + i) * nk + j;
-      const float2 v = Pair<T>::ld(src + (vb * T_ + t) * kBlk + 2 * e2);
-      a0 += v.x;
-      a1 += v.y;
+      const uint4 u = *reinterpret_cast<const uint4 *>(src + (vb * T_ + t) * kBlk + 8 * e8);
+      const T *e = reinterpret_cast<const T *>(&u);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float2 v = Pair<T>::ld(e + 2 * r);
+        acc[2 * r] += v.x;
+        acc[2 * r + 1] += v.y;
+      }
     }
-    Pair<T>::st(dst + (b * T_ + t) * W + sel * kBlk + 2 * e2, a0, a1);
+    uint4 o4;
+    T *oe = reinterpret_cast<T *>(&o4);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) Pair<T>::st(oe + 2 * r, acc[2 * r], acc[2 * r + 1]);
+    *reinterpret_cast<uint4 *>(dst + (b * T_ + t) * W + sel * kBlk + 8 * e8) = o4;
   }
 }
 
@@ -115,6 +133,14 @@ Layout make_layout(int64_t B, int64_t T_, int64_t D, int64_t K, int64_t ckpt_eve
 
 size_t a256(size_t v) { return align_up(v, 256); }
 
+// Copies of the flagged blocks' input windows for the scan kernels.
+template <typename T>
+void gather_flagged(const void *src, T *dst, const Layout &l, int W, int dside, const int *rowflag, cudaStream_t st) {
+  const int64_t items = l.VB * kGatherSlices;
+  gather_vec_kernel<T><<<(unsigned)(items < 148 * 8 ? items : 148 * 8), 256, 0, st>>>(
+      (const T *)src, dst, l.B, l.T_, W, (int)l.nd, (int)l.nk, dside, rowflag);
+}
+
 template <typename T>
 int blocked_forward_typed(const void *x, const void *f, const void *q, const void *k, const void *fk,
                           const void *state, void *out, void *ckpt, const Layout &l, void *scratch,
@@ -126,24 +152,25 @@ int blocked_forward_typed(const void *x, const void *f, const void *q, const voi
   T *sq = (T *)take(l.st()), *cq = (T *)take(l.ck());
   void *inner = p;
   const int dt = std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16;
-  const int64_t nvec = l.VB * l.T_ * (kBlk / 8);
-  gather_vec_kernel<T><<<grid_for(nvec), 256, 0, st>>>((const T *)x, xq, l.B, l.T_, (int)l.D, (int)l.nd, (int)l.nk, 1);
-  gather_vec_kernel<T><<<grid_for(nvec), 256, 0, st>>>((const T *)f, fq, l.B, l.T_, (int)l.D, (int)l.nd, (int)l.nk, 1);
-  gather_vec_kernel<T><<<grid_for(nvec), 256, 0, st>>>((const T *)q, qq, l.B, l.T_, (int)l.K, (int)l.nd, (int)l.nk, 0);
-  gather_vec_kernel<T><<<grid_for(nvec), 256, 0, st>>>((const T *)k, kq, l.B, l.T_, (int)l.K, (int)l.nd, (int)l.nk, 0);
-  gather_vec_kernel<T><<<grid_for(nvec), 256, 0, st>>>((const T *)fk, fkq, l.B, l.T_, (int)l.K, (int)l.nd, (int)l.nk, 0);
+  const int nd = (int)l.nd, nk = (int)l.nk, D = (int)l.D, K = (int)l.K;
   state_blocks_kernel<T, true><<<grid_for(l.VB * kBlk * 8), 256, 0, st>>>(
-      (T *)const_cast<void *>(state), sq, l.B, 1, (int)l.D, (int)l.K, (int)l.nd, (int)l.nk);
-  T2FW_CHECK_LAUNCH(6);
+      (T *)const_cast<void *>(state), sq, l.B, 1, D, K, nd, nk);
+  T2FW_CHECK_LAUNCH(1);
   const int *rowflag = nullptr;
-  int rc = lfw_chunk_forward(xq, fq, qq, kq, fkq, sq, oq, cq, l.VB, l.T_, dt, l.ckpt_every, inner, st, &rowflag);
+  int rc = lfw_chunk_forward_grid(x, f, q, k, fk, sq, oq, cq, l.B, l.T_, nd, nk, dt, l.ckpt_every, inner, st, &rowflag);
   if (rc != T2FW_OK) return rc;
+  gather_flagged<T>(x, xq, l, D, 1, rowflag, st);
+  gather_flagged<T>(f, fq, l, D, 1, rowflag, st);
+  gather_flagged<T>(q, qq, l, K, 0, rowflag, st);
+  gather_flagged<T>(k, kq, l, K, 0, rowflag, st);
+  gather_flagged<T>(fk, fkq, l, K, 0, rowflag, st);
+  T2FW_CHECK_LAUNCH(5);
   rc = lfw_scan_forward(xq, fq, qq, kq, fkq, sq, oq, cq, l.VB, l.T_, kBlk, kBlk, dt, l.ckpt_every, st, rowflag);
   if (rc != T2FW_OK) return rc;
-  combine_vec_kernel<T><<<grid_for(l.B * l.T_ * l.nd * (kBlk / 2)), 256, 0, st>>>(
-      oq, (T *)out, l.B, l.T_, (int)l.D, (int)l.nd, (int)l.nk, 1);
+  combine_vec_kernel<T><<<grid_for(l.B * l.T_ * l.nd * (kBlk / 8)), 256, 0, st>>>(
+      oq, (T *)out, l.B, l.T_, D, nd, nk, 1);
   state_blocks_kernel<T, false><<<grid_for(l.VB * l.slots * kBlk * 8), 256, 0, st>>>(
-      (T *)ckpt, cq, l.B, l.slots, (int)l.D, (int)l.K, (int)l.nd, (int)l.nk);
+      (T *)ckpt, cq, l.B, l.slots, D, K, nd, nk);
   T2FW_CHECK_LAUNCH(2);
   return T2FW_OK;
 }
@@ -162,29 +189,29 @@ int blocked_backward_typed(const void *go, const void *gs, const void *x, const 
   T *sq = (T *)take(l.st()), *gsq = (T *)take(l.st()), *dsq = (T *)take(l.st()), *cq = (T *)take(l.ck());
   void *inner = p;
   const int dt = std::is_same<T, __half>::value ? T2FW_F16 : T2FW_BF16;
-  const int64_t nvec = l.VB * l.T_ * (kBlk / 8);
   const int nd = (int)l.nd, nk = (int)l.nk, D = (int)l.D, K = (int)l.K;
-  gather_vec_kernel<T><<<grid_for(nvec), 256, 0, st>>>((const T *)x, xq, l.B, l.T_, D, nd, nk, 1);
-  gather_vec_kernel<T><<<grid_for(nvec), 256, 0, st>>>((const T *)f, fq, l.B, l.T_, D, nd, nk, 1);
-  gather_vec_kernel<T><<<grid_for(nvec), 256, 0, st>>>((const T *)go, goq, l.B, l.T_, D, nd, nk, 1);
-  gather_vec_kernel<T><<<grid_for(nvec), 256, 0, st>>>((const T *)q, qq, l.B, l.T_, K, nd, nk, 0);
-  gather_vec_kernel<T><<<grid_for(nvec), 256, 0, st>>>((const T *)k, kq, l.B, l.T_, K, nd, nk, 0);
-  gather_vec_kernel<T><<<grid_for(nvec), 256, 0, st>>>((const T *)fk, fkq, l.B, l.T_, K, nd, nk, 0);
   state_blocks_kernel<T, true><<<grid_for(l.VB * kBlk * 8), 256, 0, st>>>(
       (T *)const_cast<void *>(state), sq, l.B, 1, D, K, nd, nk);
   state_blocks_kernel<T, true><<<grid_for(l.VB * kBlk * 8), 256, 0, st>>>(
       (T *)const_cast<void *>(gs), gsq, l.B, 1, D, K, nd, nk);
   state_blocks_kernel<T, true><<<grid_for(l.VB * l.slots * kBlk * 8), 256, 0, st>>>(
       (T *)const_cast<void *>(ckpt), cq, l.B, l.slots, D, K, nd, nk);
-  T2FW_CHECK_LAUNCH(9);
+  T2FW_CHECK_LAUNCH(3);
   const int *rowflag = nullptr;
-  int rc = lfw_chunk_backward(goq, gsq, xq, fq, qq, kq, fkq, sq, cq, dxq, dfq, dqq, dkq, dfkq, dsq, l.VB,
-                              l.T_, dt, l.ckpt_every, inner, st, &rowflag);
+  int rc = lfw_chunk_backward_grid(go, gsq, x, f, q, k, fk, sq, cq, dxq, dfq, dqq, dkq, dfkq, dsq, l.B, l.T_, nd, nk,
+                                   dt, l.ckpt_every, inner, st, &rowflag);
   if (rc != T2FW_OK) return rc;
+  gather_flagged<T>(x, xq, l, D, 1, rowflag, st);
+  gather_flagged<T>(f, fq, l, D, 1, rowflag, st);
+  gather_flagged<T>(go, goq, l, D, 1, rowflag, st);
+  gather_flagged<T>(q, qq, l, K, 0, rowflag, st);
+  gather_flagged<T>(k, kq, l, K, 0, rowflag, st);
+  gather_flagged<T>(fk, fkq, l, K, 0, rowflag, st);
+  T2FW_CHECK_LAUNCH(6);
   rc = lfw_scan_backward(goq, gsq, xq, fq, qq, kq, fkq, sq, cq, dxq, dfq, dqq, dkq, dfkq, dsq, l.VB, l.T_,
                          kBlk, kBlk, dt, l.ckpt_every, st, rowflag);
   if (rc != T2FW_OK) return rc;
-  const unsigned gd = grid_for(l.B * l.T_ * l.nd * (kBlk / 2)), gk = grid_for(l.B * l.T_ * l.nk * (kBlk / 2));
+  const unsigned gd = grid_for(l.B * l.T_ * l.nd * (kBlk / 8)), gk = grid_for(l.B * l.T_ * l.nk * (kBlk / 8));
   combine_vec_kernel<T><<<gd, 256, 0, st>>>(dxq, (T *)dx, l.B, l.T_, D, nd, nk, 1);
   combine_vec_kernel<T><<<gd, 256, 0, st>>>(dfq, (T *)df, l.B, l.T_, D, nd, nk, 1);
   combine_vec_kernel<T><<<gk, 256, 0, st>>>(dqq, (T *)dq, l.B, l.T_, K, nd, nk, 0);

@@ -111,7 +111,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
   const float q_scale = kFused ? mp.q_scale : 1.f;
   auto issue_raw = [&](int64_t ci) {     // thread 0 only: one copy per tensor
     const Item w = split_item(ci, nc, mp.heads);
-    const int row = (int)(w.b * T_ + w.c * kC), hc = w.h * kDim;
+    const int row = (int)(w.b * T_ + w.c * kC), hc = w.h;
     const int nv = (int)((T_ - (int64_t)w.c * kC < kC) ? T_ - (int64_t)w.c * kC : kC);
     unsigned char *r = sm + oRaw;
     const uint32_t per = (mp.flags & seq::kContiguous) ? (uint32_t)nv * kDim * sizeof(T) : (uint32_t)kRawBytes;
@@ -171,8 +171,10 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
     const Item wi = split_item(ci, nc, mp.heads);
     const int64_t b = wi.bh, c = wi.c, t0c = c * kC;
     const int nvalid = (int)((T_ - t0c < kC) ? T_ - t0c : kC);
-    const int64_t row0 = wi.b * T_ + t0c;      // first row of the chunk in the 2-D sequence arrays
-    const int hcol = wi.h * kDim;
+    // first row and column window of the chunk in the output arrays
+    const bool by_row = (mp.flags & seq::kOutByRow) != 0;
+    const int64_t row0 = (by_row ? wi.bh : wi.b) * T_ + t0c;
+    const int hcol = by_row ? 0 : wi.h * kDim;
 
     if (!acp::mbar_wait(&barRaw, it & 1u)) s_fail = 1;
     if (tid == 0) raw_pending = false;

@@ -77,7 +77,7 @@ lfw_c64_fwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
   const bool unit_forget = (mp.flags & seq::kUnitForget) != 0;
   auto issue_raw = [&](int64_t ci, int buf) {     // thread 0 only: one copy per tensor
     const Item w = split_item(ci, nc, mp.heads);
-    const int row = (int)(w.b * T_ + w.c * kC), hc = w.h * kDim;
+    const int row = (int)(w.b * T_ + w.c * kC), hc = w.h;
     const int nv = (int)((T_ - (int64_t)w.c * kC < kC) ? T_ - (int64_t)w.c * kC : kC);
     unsigned char *r = sm + oRaw + buf * 5 * kRawBytes;
     const uint32_t per = (mp.flags & seq::kContiguous) ? (uint32_t)nv * kDim * sizeof(T) : (uint32_t)kRawBytes;
@@ -132,7 +132,8 @@ lfw_c64_fwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
     const int64_t b = wi.bh, c = wi.c, t0c = c * kC;      // b: problem row (batch item x head)
     const int nvalid = (int)((T_ - t0c < kC) ? T_ - t0c : kC);
     T *raw = reinterpret_cast<T *>(sm + oRaw + buf * 5 * kRawBytes);
-    T *orow = out.p + (wi.b * T_ + t0c) * out.ld + out.col + wi.h * kDim;
+    const bool by_row = (mp.flags & seq::kOutByRow) != 0;
+    T *orow = out.p + ((by_row ? wi.bh : wi.b) * T_ + t0c) * out.ld + out.col + (by_row ? 0 : wi.h * kDim);
 
     if (tid == 0) {
       s_bad = 0;

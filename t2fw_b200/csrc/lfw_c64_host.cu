@@ -169,11 +169,13 @@ lfw_c64_pick_ckpt_kernel(const T *__restrict__ all, T *__restrict__ ckpt, int64_
   }
 }
 
-// One sequence tensor of a call: base pointer, width of a row (elements), column of head 0.
+// One sequence tensor of a call: base pointer, width of a row (elements), column of sub-item 0,
+// and which 64-column window sub-item h reads: (h / hdiv) % hmod (0, 0 = head h of `heads`).
 struct Tensor2D {
   const void *p;
   int64_t width;
   int col;
+  int hdiv = 0, hmod = 0;
 };
 
 // Tensor maps for a kernel whose inputs are `ts` (in the kernel's order); rows = batch items x T.
@@ -188,6 +190,8 @@ int build_maps(seq::Maps &mp, const Tensor2D *ts, int n, int64_t rows, int heads
   for (int i = 0; i < n; ++i) {
     mp.col[i] = ts[i].col;
     mp.base[i] = ts[i].p;
+    mp.hdiv[i] = ts[i].hdiv > 0 ? ts[i].hdiv : 1;
+    mp.hmod[i] = ts[i].hmod > 0 ? ts[i].hmod : heads;
     if (ts[i].p == nullptr || dense) continue;        // constant tensor (unit forget gate) / no map needed
     bool shared = false;
     for (int j = 0; j < i && !shared; ++j)
@@ -291,6 +295,19 @@ Call plain_call(const void *x, const void *f, const void *q, const void *k, cons
   return c;
 }
 
+// A D x K state cut into (D/64) x (K/64) blocks: sub-item h = i * nk + j of a batch item is block
+// (i, j); the d-side tensors [B*T][D] are read at window i, the k-side tensors [B*T][K] at window j,
+// and every sub-item writes its own [T][64] result arrays (summed over the other index afterwards).
+Call grid_call(const void *x, const void *f, const void *q, const void *k, const void *fk, const void *go, int64_t B,
+               int64_t T_, int nd, int nk) {
+  const int64_t D = (int64_t)nd * kDim, K = (int64_t)nk * kDim;
+  Call c;
+  c.x = {x, D, 0, nk, nd}; c.f = {f, D, 0, nk, nd}; c.go = {go, D, 0, nk, nd};
+  c.q = {q, K, 0, 1, nk}; c.k = {k, K, 0, 1, nk}; c.fk = {fk, K, 0, 1, nk};
+  c.B = B; c.T_ = T_; c.heads = nd * nk; c.flags = seq::kOutByRow; c.q_scale = 1.f;
+  return c;
+}
+
 // fused layer: qkvg [B][T][4 * H * 64] = query | key | value | gate pre-activation, heads inside a row
 Call fused_call(const void *qkvg, const void *go, int64_t B, int64_t T_, int H) {
   const int64_t C = (int64_t)H * kDim;
@@ -341,6 +358,37 @@ int lfw_chunk_backward(const void *go, const void *gs, const void *x, const void
   if (dtype == T2FW_F16)
     return backward_typed<__half>(c, gs, state, ckpt, outs, ld, col, ds, dtype, ckpt_every, scratch, st);
   return backward_typed<__nv_bfloat16>(c, gs, state, ckpt, outs, ld, col, ds, dtype, ckpt_every, scratch, st);
+}
+
+// ---- block-grid form: inputs dense [B*T][D] / [B*T][K], states, checkpoints and results per block ----
+int lfw_chunk_forward_grid(const void *x, const void *f, const void *q, const void *k, const void *fk,
+                           const void *state_blocks, void *out_blocks, void *ckpt_blocks, int64_t B, int64_t T_,
+                           int nd, int nk, int dtype, int64_t ckpt_every, void *scratch, cudaStream_t st,
+                           const int **rowflag_out) {
+  const int64_t VB = B * nd * nk;
+  if (rowflag_out) *rowflag_out = carve(scratch, VB, ceil_div64(T_, kC)).rowflag;
+  const Call c = grid_call(x, f, q, k, fk, nullptr, B, T_, nd, nk);
+  if (dtype == T2FW_F16)
+    return forward_typed<__half>(c, state_blocks, out_blocks, kDim, 0, ckpt_blocks, dtype, ckpt_every, scratch, st);
+  return forward_typed<__nv_bfloat16>(c, state_blocks, out_blocks, kDim, 0, ckpt_blocks, dtype, ckpt_every, scratch, st);
+}
+
+int lfw_chunk_backward_grid(const void *go, const void *gs_blocks, const void *x, const void *f, const void *q,
+                            const void *k, const void *fk, const void *state_blocks, const void *ckpt_blocks,
+                            void *dx, void *df, void *dq, void *dk, void *dfk, void *ds_blocks, int64_t B, int64_t T_,
+                            int nd, int nk, int dtype, int64_t ckpt_every, void *scratch, cudaStream_t st,
+                            const int **rowflag_out) {
+  const int64_t VB = B * nd * nk;
+  if (rowflag_out) *rowflag_out = carve(scratch, VB, ceil_div64(T_, kC)).rowflag;
+  const Call c = grid_call(x, f, q, k, fk, go, B, T_, nd, nk);
+  void *const outs[5] = {dx, df, dq, dk, dfk};
+  const int64_t ld[5] = {kDim, kDim, kDim, kDim, kDim};
+  const int col[5] = {0, 0, 0, 0, 0};
+  if (dtype == T2FW_F16)
+    return backward_typed<__half>(c, gs_blocks, state_blocks, ckpt_blocks, outs, ld, col, ds_blocks, dtype, ckpt_every,
+                                  scratch, st);
+  return backward_typed<__nv_bfloat16>(c, gs_blocks, state_blocks, ckpt_blocks, outs, ld, col, ds_blocks, dtype,
+                                       ckpt_every, scratch, st);
 }
 
 // ---- fused layer entry points (heads read in place from the projection output) ----------------

@@ -71,7 +71,7 @@ lfw_c64_local_kernel(const __grid_constant__ seq::Maps mp, float *__restrict__ M
   const bool unit_forget = (mp.flags & seq::kUnitForget) != 0;
   auto issue_raw = [&](int64_t ci, int buf) {     // thread 0 only: one copy per tensor
     const Item w = split_item(ci, nc, mp.heads);
-    const int row = (int)(w.b * T_ + w.c * kC), hc = w.h * kDim;
+    const int row = (int)(w.b * T_ + w.c * kC), hc = w.h;
     const int nv = (int)((T_ - (int64_t)w.c * kC < kC) ? T_ - (int64_t)w.c * kC : kC);
     unsigned char *r = sm + oRawL + buf * 4 * kRawBytes;
     const uint32_t per = (mp.flags & seq::kContiguous) ? (uint32_t)nv * kDim * sizeof(T) : (uint32_t)kRawBytes;

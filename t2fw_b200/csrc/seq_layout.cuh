@@ -24,14 +24,19 @@ enum : int {
   kUnitForget = 1,     // the d-side gate is the constant 1: nothing is read for it
   kSigmoidGate = 2,    // the k-side gate tensor holds pre-activations: gate = max(sigmoid(g), 1/8)
   kContiguous = 4,     // every tensor is a dense [rows][64] array: a chunk's block is one linear 8 KB copy
+  kOutByRow = 8,       // outputs are [problem row][T][64] arrays (one per sub-item), not windows of a batch item's row
 };
 constexpr float kGateFloor = 0.125f;   // with gates >= 1/8 no 32-step product leaves the safe range
 
 struct Maps {
   CUtensorMap m[kMaxTensors];    // one per input tensor of the kernel
   const void *base[kMaxTensors]; // the arrays themselves (used for the linear copies of dense [rows][64] arrays)
-  int col[kMaxTensors];          // column of head 0 in a row of that tensor (elements)
-  int heads;                     // problem row bh = b * heads + h; head h adds 64 * h to the column
+  int col[kMaxTensors];          // column of sub-item 0 in a row of that tensor (elements)
+  int hdiv[kMaxTensors];         // sub-item h of a batch item reads the 64-column window number
+  int hmod[kMaxTensors];         //   (h / hdiv) % hmod of that tensor
+  int heads;                     // sub-items per batch item: problem row bh = b * heads + h.  Heads of a
+                                 // layer: hdiv = 1, hmod = heads.  A D x K state cut into 64 x 64 blocks:
+                                 // h = i * (K/64) + j, d-side tensors hdiv = K/64, hmod = D/64, k-side 1, K/64
   int flags;
   float q_scale;                 // factor on the query tensor (1 for the plain operators)
 };
@@ -73,17 +78,17 @@ __device__ __forceinline__ void scale_block(T *blk, float s, int tid, int nthrea
   for (int i = tid; i < 64 * 64; i += nthreads) blk[i] = (T)(Elem<T>::ld(blk + i) * s);
 }
 
-// The block of tensor i for the chunk whose first row is `row` (nv valid rows), head column hc.
+// The block of tensor i for the chunk whose first row is `row` (nv valid rows), sub-item h.
 // Dense [rows][64] arrays: one linear bulk copy of the valid rows; otherwise the tiled copy of the
 // whole box.  Returns the bytes that will arrive on the barrier.
 template <typename T>
-__device__ __forceinline__ uint32_t fetch_block(const Maps &mp, int i, void *dst, int row, int hc, int nv, uint64_t *bar) {
+__device__ __forceinline__ uint32_t fetch_block(const Maps &mp, int i, void *dst, int row, int h, int nv, uint64_t *bar) {
   if (mp.flags & kContiguous) {
     const uint32_t bytes = (uint32_t)nv * 64u * sizeof(T);
     acp::bulk_g2s(dst, static_cast<const T *>(mp.base[i]) + (size_t)row * 64, bytes, bar);
     return bytes;
   }
-  load_block(dst, &mp.m[i], mp.col[i] + hc, row, bar);
+  load_block(dst, &mp.m[i], mp.col[i] + ((h / mp.hdiv[i]) % mp.hmod[i]) * 64, row, bar);
   return 64u * 64u * sizeof(T);
 }
 

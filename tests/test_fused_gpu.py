@@ -74,3 +74,34 @@ def test_fused_against_the_oracle(cuda):
     want_g = torch.as_tensor(r[4]) * torch.where(sig > GATE_FLOOR, sig * (1 - sig), torch.zeros_like(sig))
     assert max_rel_err(d_g, want_g) <= GRAD_TOL[torch.float16]
     assert max_rel_err(d_state, r[5]) <= GRAD_TOL[torch.float16]
+
+
+def test_fused_layer_under_graph_capture(cuda):
+    """Forward + backward of the fused entry points captured in a CUDA graph (the tensor maps are
+    built on the host inside the capture, on the caller's thread and on autograd's worker thread)
+    and replayed twice: bitwise equal to the eager result."""
+    from t2fw_b200.functional_fused import LFWFusedFunction
+
+    qkvg, state, go, gs = _inputs(2, 256, 3, torch.float16, cuda, 77)
+
+    def run():
+        leaves = [qkvg.detach().requires_grad_(True), state.detach().requires_grad_(True)]
+        out, nxt = LFWFusedFunction.apply(leaves[0], leaves[1], 3)
+        return [out, nxt] + list(torch.autograd.grad([out, nxt], leaves, [go, gs]))
+
+    eager = [t.clone() for t in run()]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        run()
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        static = run()
+    for _ in range(2):
+        for t in static:
+            t.detach().fill_(float("nan"))
+        g.replay()
+        torch.cuda.synchronize()
+        for a, b in zip(static, eager):
+            assert torch.equal(a, b)
