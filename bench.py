@@ -435,7 +435,11 @@ def run_ours(args):
     from t2fw_b200.decode import LFWDecodeLoop
     from t2fw_b200.functional_dfw import DFWFunction
     from t2fw_b200.functional_lfw import LFWFunction
-    from t2fw_b200.parallel import max_over_ranks, row_shard
+    from t2fw_b200.parallel import bind_host_to_gpu_node, max_over_ranks, row_shard
+
+    # several ranks on one box: each rank's pinned host buffers and copy threads on its GPU's own
+    # NUMA node (matters for the end-to-end leg only; a no-op where the topology is not visible)
+    host_binding = bind_host_to_gpu_node(local) if world > 1 else None
 
     lib = _lib.load_core()
     B, T, D, K = WORKLOADS[args.workload]
@@ -871,7 +875,7 @@ def run_ours(args):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": args.scaling,
         "vs_baseline": None, "dtype": "f32 state arithmetic, f16 I/O", "data": "synthetic",
-        "config": dict(workload_config(args, B, T, D, K),
+        "config": dict(workload_config(args, B, T, D, K), host_binding=host_binding,
                        l2="inputs larger than L2: %d rotating input/output sets" % n_sets,
                        ckpt_every=C, cuda_graph=graph is not None, flagged_rows=flagged),
         "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),

@@ -23,6 +23,14 @@ void set_error(const char *fmt, ...) {
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+bool dependent_launch_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("T2FW_DISABLE_PDL");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
+
 }  // namespace t2fw
 
 using namespace t2fw;

@@ -41,6 +41,36 @@ void count_launch(int n = 1);
     T2FW_CHECK_CUDA(cudaGetLastError());                                             \
   } while (0)
 
+// ---- programmatic dependent launch -------------------------------------------------------
+// A kernel launched with launch_dependent() may be scheduled while the kernel before it in the
+// stream is still running: its prologue (barrier initialisation, tensor-memory allocation) and its
+// launch latency then overlap that kernel's tail.  dependency_wait() blocks until the earlier
+// kernel has completed and its writes are visible; every such kernel calls it before its first
+// access to global memory (so completion is transitive along the stream), then lets the next
+// kernel in.  T2FW_DISABLE_PDL=1 turns the launch attribute off (the device calls are then no-ops).
+#ifdef __CUDACC__
+__device__ __forceinline__ void dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+#endif
+bool dependent_launch_enabled();      // api.cu
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                    Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---- element types ----------------------------------------------------------------------
 // Acc<T> is the type the recurrences are carried in: float for 16/32-bit storage, double for
 // double.  (The reference accumulates in the storage type, t2fw/csrc/lfw_kernel.cu:49.)

@@ -150,6 +150,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
   if (warp == 0) umma::tmem_alloc(&tmem_slot, kTmemCols);
   if (unit_forget) seq::fill_block(raw + kC * kDim, 1.f, tid, kThreadsB);   // constant d-side gate, never loaded
   sync_all();
+  dependency_wait();
   const uint32_t tb = __shfl_sync(0xffffffffu, tmem_slot, 0);
   const uint32_t tl = umma::tmem_addr(tb, 32 * q4, 0);
   bool raw_pending = false;      // thread 0
@@ -556,9 +557,10 @@ int lfw_c64_backward_main(const seq::Maps &mp, const void *state, const void *ck
   do {                                                                                                \
     T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_c64_bwd_kernel<TT, FF>,                                  \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemB));       \
-    lfw_c64_bwd_kernel<TT, FF><<<grid, kThreadsB, kSmemB, st>>>(                                      \
-        mp, (const TT *)state, (const TT *)ckpt, Rend, T2FW_OUT(TT, 0), T2FW_OUT(TT, 1), T2FW_OUT(TT, 2), \
-        T2FW_OUT(TT, 3), T2FW_OUT(TT, 4), rowflag, status, T_, nc, total);                            \
+    T2FW_CHECK_CUDA(launch_dependent(lfw_c64_bwd_kernel<TT, FF>, dim3(grid), dim3(kThreadsB), kSmemB, st, mp,   \
+                                     (const TT *)state, (const TT *)ckpt, Rend, T2FW_OUT(TT, 0), T2FW_OUT(TT, 1), \
+                                     T2FW_OUT(TT, 2), T2FW_OUT(TT, 3), T2FW_OUT(TT, 4), rowflag, status, T_, nc,  \
+                                     total));                                                         \
   } while (0)
   const bool fused = (mp.flags & (seq::kUnitForget | seq::kSigmoidGate)) != 0 || mp.q_scale != 1.f;
   if (dtype == T2FW_F16) {

@@ -111,6 +111,7 @@ lfw_c64_fwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
     seq::fill_block(reinterpret_cast<T *>(sm + oRaw + 6 * kRawBytes), 1.f, tid, kThreadsF);
   }
   sync_all();
+  dependency_wait();
   const uint32_t tb = __shfl_sync(0xffffffffu, tmem_slot, 0);
   const uint32_t tl = umma::tmem_addr(tb, 32 * q4, 0);
   uint32_t n_issued[2] = {0u, 0u}, n_landed[2] = {0u, 0u};      // thread 0: bulk-copy rounds per buffer
@@ -331,9 +332,9 @@ int lfw_c64_forward_out(const seq::Maps &mp, const void *state, const void *ckpt
   do {                                                                                               \
     T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_c64_fwd_kernel<TT>,                                     \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemF));      \
-    lfw_c64_fwd_kernel<TT><<<grid, kThreadsF, kSmemF, st>>>(                                         \
-        mp, (const TT *)state, (const TT *)ckpt, seq::Out<TT>{(TT *)out, out_ld, out_col}, rowflag, status, T_, \
-        nc, total);                                                                                  \
+    T2FW_CHECK_CUDA(launch_dependent(lfw_c64_fwd_kernel<TT>, dim3(grid), dim3(kThreadsF), kSmemF, st, mp,       \
+                                     (const TT *)state, (const TT *)ckpt, seq::Out<TT>{(TT *)out, out_ld, out_col}, \
+                                     rowflag, status, T_, nc, total));                               \
   } while (0)
   if (dtype == T2FW_F16) T2FW_LAUNCH(__half); else T2FW_LAUNCH(__nv_bfloat16);
 #undef T2FW_LAUNCH

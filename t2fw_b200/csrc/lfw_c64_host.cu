@@ -108,6 +108,7 @@ lfw_c64_carry_kernel(const T *__restrict__ init, float *__restrict__ M, const fl
   __shared__ float a_s[kBatch][kCarryRows];
   __shared__ __align__(16) float g_s[kBatch][kDim];
   const int tid = threadIdx.x;
+  dependency_wait();
   const int64_t b = blockIdx.x / (kDim / kCarryRows);
   const int d0 = (int)(blockIdx.x % (kDim / kCarryRows)) * kCarryRows;
   const int dl = tid / (kDim / 4), d = d0 + dl, k0 = (tid % (kDim / 4)) * 4;
@@ -228,8 +229,9 @@ int chunk_states(const Call &c, const Scratch &s, const void *state, T *ck_all, 
   if (rc != T2FW_OK) return rc;
   rc = lfw_chunk_local_umma(false, mp, s.M, s.Ac, s.Gc, s.flags, BH, c.T_, dtype, st);
   if (rc != T2FW_OK) return rc;
-  lfw_c64_carry_kernel<T, true><<<(unsigned)(BH * (kDim / kCarryRows)), kCarryThreads, 0, st>>>(
-      (const T *)state, s.M, s.Ac, s.Gc, s.flags, s.rowflag, 0, ck_all, BH, nc);
+  T2FW_CHECK_CUDA(launch_dependent(lfw_c64_carry_kernel<T, true>, dim3((unsigned)(BH * (kDim / kCarryRows))),
+                                   dim3(kCarryThreads), 0, st, (const T *)state, s.M, (const float *)s.Ac,
+                                   (const float *)s.Gc, (const int *)s.flags, s.rowflag, 0, ck_all, BH, nc));
   T2FW_CHECK_LAUNCH(1);
   return T2FW_OK;
 }
@@ -277,8 +279,10 @@ int backward_typed(const Call &c, const void *gs, const void *state, const void 
   if (rc != T2FW_OK) return rc;
   rc = lfw_chunk_local_umma(true, mp, s.M, s.Ac, s.Gc, s.flags, BH, c.T_, dtype, st);
   if (rc != T2FW_OK) return rc;
-  lfw_c64_carry_kernel<T, false><<<(unsigned)(BH * (kDim / kCarryRows)), kCarryThreads, 0, st>>>(
-      (const T *)gs, s.M, s.Ac, s.Gc, s.flags, s.rowflag, m > 1 ? 1 : 0, (T *)ds, BH, nc);
+  T2FW_CHECK_CUDA(launch_dependent(lfw_c64_carry_kernel<T, false>, dim3((unsigned)(BH * (kDim / kCarryRows))),
+                                   dim3(kCarryThreads), 0, st, (const T *)gs, s.M, (const float *)s.Ac,
+                                   (const float *)s.Gc, (const int *)s.flags, s.rowflag, m > 1 ? 1 : 0, (T *)ds, BH,
+                                   nc));
   T2FW_CHECK_LAUNCH(1);
   const Tensor2D all[6] = {c.x, c.f, c.q, c.k, c.fk, c.go};
   rc = build_maps(mp, all, 6, rows, c.heads, c.flags, c.q_scale);

@@ -94,6 +94,7 @@ lfw_c64_local_kernel(const __grid_constant__ seq::Maps mp, float *__restrict__ M
     seq::fill_block(reinterpret_cast<T *>(sm + oRawL + 5 * kRawBytes), 1.f, tid, kThreadsL);
   }
   sync_all();
+  dependency_wait();
   const uint32_t tb = __shfl_sync(0xffffffffu, tmem_slot, 0);
   const uint32_t tl = umma::tmem_addr(tb, 32 * q4, 0);
   uint32_t n_issued[2] = {0u, 0u}, n_landed[2] = {0u, 0u};      // thread 0: bulk-copy rounds per buffer
@@ -299,7 +300,8 @@ int lfw_chunk_local_umma(bool backward, const seq::Maps &mp, float *M, float *Ac
   do {                                                                                                \
     T2FW_CHECK_CUDA(cudaFuncSetAttribute(lfw_c64_local_kernel<TT, SUF>,                               \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemL));       \
-    lfw_c64_local_kernel<TT, SUF><<<grid, kThreadsL, kSmemL, st>>>(mp, M, Ac, Gc, flags, status, T_, nc, total); \
+    T2FW_CHECK_CUDA(launch_dependent(lfw_c64_local_kernel<TT, SUF>, dim3(grid), dim3(kThreadsL), kSmemL, st, mp, M, \
+                                     Ac, Gc, flags, status, T_, nc, total));                         \
   } while (0)
   if (dtype == T2FW_F16) {
     if (backward) T2FW_LAUNCH(__half, false); else T2FW_LAUNCH(__half, true);

@@ -54,3 +54,26 @@ def test_dfw_contract():
         DFWFunction.apply(q, k, v.double(), s)
     with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
         DFWFunction.apply(q, k, v, s)
+
+
+def test_numa_binding_reads_the_topology(tmp_path):
+    """bind_host_to_gpu_node's sysfs logic on a fake tree: node lookup, CPU list parsing, the
+    intersection with the allowed set, and the reasons it gives when it cannot bind."""
+    from t2fw_b200.parallel import _bind_to_pci_node, _parse_cpulist
+
+    assert _parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    dev = tmp_path / "bus/pci/devices/0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices/system/node/node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text("16-31\n")
+    ok = _bind_to_pci_node("0000:1b:00.0", str(tmp_path), set(range(0, 24)), False, {"bound": False})
+    assert ok["bound"] and ok["numa_node"] == 1 and ok["cpus"] == 8
+    none = _bind_to_pci_node("0000:1b:00.0", str(tmp_path), set(range(0, 16)), False, {"bound": False})
+    assert not none["bound"] and "available" in none["reason"]
+    missing = _bind_to_pci_node("0000:ff:00.0", str(tmp_path), {0}, False, {"bound": False})
+    assert not missing["bound"] and "not readable" in missing["reason"]
+    (dev / "numa_node").write_text("-1\n")
+    flat = _bind_to_pci_node("0000:1b:00.0", str(tmp_path), {0}, False, {"bound": False})
+    assert not flat["bound"] and "no NUMA node" in flat["reason"]
