@@ -153,13 +153,24 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
   dependency_wait();
   const uint32_t tb = __shfl_sync(0xffffffffu, tmem_slot, 0);
   const uint32_t tl = umma::tmem_addr(tb, 32 * q4, 0);
+  // Work items of this CTA.  Chunk ci = blockIdx + r * grid for the full rounds r.  The chunks that
+  // are left over when the count is not a multiple of the grid would make some CTAs run one whole
+  // chunk longer than the others; if there are at most grid / 2 of them, each is split into its two
+  // passes (which are independent) over two CTAs instead.
+  const int64_t n_full = total / gridDim.x, rem = total - n_full * gridDim.x;
+  const bool split_tail = rem > 0 && 2 * rem <= (int64_t)gridDim.x;
+  const int64_t n_items =
+      n_full + ((split_tail ? (int64_t)blockIdx.x < 2 * rem : (int64_t)blockIdx.x < rem) ? 1 : 0);
+  auto item_chunk = [&](int64_t r) -> int64_t {
+    return (split_tail && r == n_full) ? n_full * gridDim.x + (blockIdx.x >> 1) : (int64_t)blockIdx.x + r * gridDim.x;
+  };
   bool raw_pending = false;      // thread 0
-  if ((int64_t)blockIdx.x < total) {
+  if (n_items > 0) {
     if (tid == 0) {
-      issue_raw(blockIdx.x);
+      issue_raw(item_chunk(0));
       raw_pending = true;
     }
-    issue_state(blockIdx.x);
+    issue_state(item_chunk(0));
   }
   const uint32_t aT = umma::smem_u32(sm + oT);
   uint64_t dT[4];      // descriptors of the four tiles
@@ -168,7 +179,10 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
   uint32_t pz = 0, pm_par = 0;   // mbarrier phase parities
 
   uint32_t it = 0;
-  for (int64_t ci = blockIdx.x; ci < total; ci += gridDim.x, ++it) {
+  for (int64_t r = 0; r < n_items; ++r, ++it) {
+    const int64_t ci = item_chunk(r);
+    const bool half_item = split_tail && r == n_full;
+    const int ph_lo = half_item ? (int)(blockIdx.x & 1u) : 0, ph_hi = half_item ? ph_lo + 1 : 2;
     const Item wi = split_item(ci, nc, mp.heads);
     const int64_t b = wi.bh, c = wi.c, t0c = c * kC;
     const int nvalid = (int)((T_ - t0c < kC) ? T_ - t0c : kC);
@@ -193,7 +207,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
     }
 
 #pragma unroll 1
-    for (int ph = 0; ph < 2; ++ph) {
+    for (int ph = ph_lo; ph < ph_hi; ++ph) {
       // pass 0: own = k side (other = d side);  pass 1: own = d side
       const int blk_go = ph ? 4 : 1, blk_mo = ph ? 2 : 5, blk_vo = ph ? 3 : 0;   // other: gate, mul, div
       const int blk_gw = ph ? 1 : 4, blk_mw = ph ? 5 : 2, blk_vw = ph ? 0 : 3;   // own
@@ -333,12 +347,12 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         }
         __syncwarp();
       }
-      if (ph == 1 && ci + gridDim.x < total) {      // the next chunk's inputs and state blocks
+      if (ph == ph_hi - 1 && r + 1 < n_items) {      // the next item's inputs and state blocks
         if (tid == 0) {
-          issue_raw(ci + gridDim.x);
+          issue_raw(item_chunk(r + 1));
           raw_pending = true;
         }
-        issue_state(ci + gridDim.x);
+        issue_state(item_chunk(r + 1));
       }
       if (tid == 0 && s_bad) atomicExch(rowflag + b, 1);      // the scan kernels redo this batch row
 
