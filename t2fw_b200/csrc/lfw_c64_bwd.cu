@@ -332,17 +332,23 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         constexpr uint32_t idesc = umma::make_idesc_tf32(64, 32, false, false);
         constexpr uint64_t n1 = (uint64_t)(32 * 128 >> 4);     // B rows 32..63
         if (elect_one()) {
+          // Z first and on its own barrier: the CTA rounds and stores it while the other four
+          // chains of this round are still in the pipe
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
             umma::mma_tf32(d0 + cZ, dT[0] + o, dT[1] + o, idesc, ks > 0);                 // Z = Mo_mid Vo_mid^T
             umma::mma_tf32(d1 + cZ, dT[0] + o, dT[1] + n1 + o, idesc, ks > 0);
+          }
+          umma::mma_commit(&barZ);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
             mma_tf32_ts(d0 + cTQ1, d0 + cS2 + 8 * ks, dT[2] + o, idesc, ks > 0);          // TQ1 = S2 Mo_start^T
             mma_tf32_ts(d1 + cTQ1, d1 + cS2 + 8 * ks, dT[2] + n1 + o, idesc, ks > 0);
             mma_tf32_ts(d0 + cT7, d0 + cR2 + 8 * ks, dT[3] + o, idesc, ks > 0);           // T7 = R2 Vo_end^T
             mma_tf32_ts(d1 + cT7, d1 + cR2 + 8 * ks, dT[3] + n1 + o, idesc, ks > 0);
           }
-          umma::mma_commit(&barZ);
           umma::mma_commit(&barM);
         }
         __syncwarp();
