@@ -143,7 +143,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
   if (tid == 0) {
     umma::mbar_init(&barRaw, 1);
     umma::mbar_init(&barZ, 1);
-    umma::mbar_init(&barM, 2);
+    umma::mbar_init(&barM, 4);      // TQ1, T7, TQ2, T2: one commit each
     umma::mbar_fence_init();
     s_fail = 0;
   }
@@ -327,29 +327,39 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       //      contraction columns, accumulating in place); the tensor core executes instructions in
       //      issue order, so the six independent chains of this round are issued interleaved by ONE
       //      lane and overlap in the pipeline instead of running one after the other. ----
-      if (warp == 0) {
+      // Issuing one instruction costs the issuing thread about 30 cycles, so the three products of
+      // this round are issued by lanes of three different warps at the same time; each product is
+      // two interleaved chains (the two 32-column halves).
+      if (warp == 0 || warp == 4 || warp == 8) {
         const uint32_t d0 = tb, d1 = umma::tmem_addr(tb, 16, 0);
         constexpr uint32_t idesc = umma::make_idesc_tf32(64, 32, false, false);
         constexpr uint64_t n1 = (uint64_t)(32 * 128 >> 4);     // B rows 32..63
         if (elect_one()) {
-          // Z first and on its own barrier: the CTA rounds and stores it while the other four
-          // chains of this round are still in the pipe
+          if (warp == 0) {
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
-            umma::mma_tf32(d0 + cZ, dT[0] + o, dT[1] + o, idesc, ks > 0);                 // Z = Mo_mid Vo_mid^T
-            umma::mma_tf32(d1 + cZ, dT[0] + o, dT[1] + n1 + o, idesc, ks > 0);
-          }
-          umma::mma_commit(&barZ);
+            for (int ks = 0; ks < 8; ++ks) {
+              const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
+              umma::mma_tf32(d0 + cZ, dT[0] + o, dT[1] + o, idesc, ks > 0);                 // Z = Mo_mid Vo_mid^T
+              umma::mma_tf32(d1 + cZ, dT[0] + o, dT[1] + n1 + o, idesc, ks > 0);
+            }
+            umma::mma_commit(&barZ);
+          } else if (warp == 4) {
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
-            mma_tf32_ts(d0 + cTQ1, d0 + cS2 + 8 * ks, dT[2] + o, idesc, ks > 0);          // TQ1 = S2 Mo_start^T
-            mma_tf32_ts(d1 + cTQ1, d1 + cS2 + 8 * ks, dT[2] + n1 + o, idesc, ks > 0);
-            mma_tf32_ts(d0 + cT7, d0 + cR2 + 8 * ks, dT[3] + o, idesc, ks > 0);           // T7 = R2 Vo_end^T
-            mma_tf32_ts(d1 + cT7, d1 + cR2 + 8 * ks, dT[3] + n1 + o, idesc, ks > 0);
+            for (int ks = 0; ks < 8; ++ks) {
+              const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
+              mma_tf32_ts(d0 + cTQ1, d0 + cS2 + 8 * ks, dT[2] + o, idesc, ks > 0);          // TQ1 = S2 Mo_start^T
+              mma_tf32_ts(d1 + cTQ1, d1 + cS2 + 8 * ks, dT[2] + n1 + o, idesc, ks > 0);
+            }
+            umma::mma_commit(&barM);
+          } else {
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+              const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
+              mma_tf32_ts(d0 + cT7, d0 + cR2 + 8 * ks, dT[3] + o, idesc, ks > 0);           // T7 = R2 Vo_end^T
+              mma_tf32_ts(d1 + cT7, d1 + cR2 + 8 * ks, dT[3] + n1 + o, idesc, ks > 0);
+            }
+            umma::mma_commit(&barM);
           }
-          umma::mma_commit(&barM);
         }
         __syncwarp();
       }
@@ -384,18 +394,25 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       if (s_fail) break;
 
       // ---- second MMA round: TQ2 = Vw_mid Z^T, T2 = Mw_mid Z, four interleaved chains ----
-      if (warp == 0) {
+      if (warp == 0 || warp == 4) {
         const uint32_t d0 = tb, d1 = umma::tmem_addr(tb, 16, 0);
         constexpr uint32_t idesc = umma::make_idesc_tf32(64, 32, false, false);
         constexpr uint64_t n1 = (uint64_t)(32 * 128 >> 4);
         if (elect_one()) {
+          if (warp == 0) {
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
-            mma_tf32_ts(d0 + cTQ2, d0 + cVw + 8 * ks, dT[0] + o, idesc, ks > 0);
-            mma_tf32_ts(d1 + cTQ2, d1 + cVw + 8 * ks, dT[0] + n1 + o, idesc, ks > 0);
-            mma_tf32_ts(d0 + cT2, d0 + cMw + 8 * ks, dT[1] + o, idesc, ks > 0);
-            mma_tf32_ts(d1 + cT2, d1 + cMw + 8 * ks, dT[1] + n1 + o, idesc, ks > 0);
+            for (int ks = 0; ks < 8; ++ks) {
+              const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
+              mma_tf32_ts(d0 + cTQ2, d0 + cVw + 8 * ks, dT[0] + o, idesc, ks > 0);
+              mma_tf32_ts(d1 + cTQ2, d1 + cVw + 8 * ks, dT[0] + n1 + o, idesc, ks > 0);
+            }
+          } else {
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+              const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
+              mma_tf32_ts(d0 + cT2, d0 + cMw + 8 * ks, dT[1] + o, idesc, ks > 0);
+              mma_tf32_ts(d1 + cT2, d1 + cMw + 8 * ks, dT[1] + n1 + o, idesc, ks > 0);
+            }
           }
           umma::mma_commit(&barM);
         }
