@@ -45,10 +45,11 @@ __device__ __forceinline__ int toff(int r, int c) {
   return (c >> 5) * kColBlock + r * 128 + ((((c >> 2) & 7) ^ (r & 7)) << 4) + ((c & 3) << 2);
 }
 
+// Round to TF32 (10 mantissa bits), nearest with ties away from zero - what cvt.rna.tf32.f32 does -
+// as two integer instructions: the conversion instruction runs on the quarter-rate pipe and there
+// are hundreds of them per thread and chunk.  (Infinity becomes NaN; such rows are flagged anyway.)
 __device__ __forceinline__ float rna_tf32(float v) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
-  return __uint_as_float(r);
+  return __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xffffe000u);
 }
 
 __device__ __forceinline__ float sanitize_gate(float g) {
@@ -177,13 +178,21 @@ __device__ __forceinline__ void sync_all() {
 // Thread (feature, 16-step quarter tq).  g[j] = sanitized gate of step 16 * tq + j (the raw gate
 // blocks hold 1 beyond the valid steps); returns the product of the quarter.
 template <typename T>
-__device__ __forceinline__ float load_gates16(const T *gate_col, int tq, float (&g)[16]) {
-  float p = 1.f;
+__device__ __forceinline__ float load_gates16(const T *gate_col, int tq, float (&g)[16], float *min_abs = nullptr) {
+  float mn = kRangeHi;
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
-    g[j] = sanitize_gate(Elem<T>::ld(gate_col + (16 * tq + j) * kDim));
-    p *= g[j];
+    g[j] = Elem<T>::ld(gate_col + (16 * tq + j) * kDim);
+    mn = fminf(mn, fabsf(g[j]));
   }
+  if (!(mn >= kTinyState)) {      // rare (also NaN): some gate needs the clamp
+#pragma unroll
+    for (int j = 0; j < 16; ++j) g[j] = sanitize_gate(g[j]);
+  }
+  float p = 1.f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) p *= g[j];
+  if (min_abs != nullptr) *min_abs = mn;
   return p;
 }
 

@@ -218,8 +218,9 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         fix_n = 0;
       }
       if (tid < kDim) fix_mask[tid] = 0ull;
-      float g[16];
-      qtot[(gsw * 4 + tq) * kDim + feat] = load_gates16<T>(raw + (gsw ? blk_gw : blk_go) * kC * kDim + feat, tq, g);
+      float g[16], g_min;
+      qtot[(gsw * 4 + tq) * kDim + feat] =
+          load_gates16<T>(raw + (gsw ? blk_gw : blk_go) * kC * kDim + feat, tq, g, &g_min);
       __syncthreads();
       {
         const float *qt = qtot + gsw * 4 * kDim + feat;
@@ -233,6 +234,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
 #pragma unroll
           for (int j = 0; j < 16; j += 4)
             *reinterpret_cast<float4 *>(pmT + feat * kPmLd + 16 * tq + j) = make_float4(pm[j], pm[j + 1], pm[j + 2], pm[j + 3]);
+          if (g_min < kTinyGate)      // rare: some gate of this quarter is tiny
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (fabsf(g[j]) < kTinyGate && 16 * tq + j < nvalid) {   // exact pair sum for this (step, feature) later
@@ -543,7 +545,8 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         T *p_mu = dq.p + (size_t)(row0 + c0) * dq.ld + dq.col + hcol + own;
         T *p_dv = o_dv.p + (size_t)(row0 + c0) * o_dv.ld + o_dv.col + hcol + own;
         T *p_gt = o_gt.p == nullptr ? nullptr : o_gt.p + (size_t)(row0 + c0) * o_gt.ld + o_gt.col + hcol + own;
-        const int64_t ld_mu = dq.ld, ld_dv = o_dv.ld, ld_gt = o_gt.ld;
+        // the plain operator and the block-grid form write dense [rows][64] arrays
+        const int64_t ld_mu = kFused ? dq.ld : kDim, ld_dv = kFused ? o_dv.ld : kDim, ld_gt = kFused ? o_gt.ld : kDim;
         const float qs = q_scale;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
