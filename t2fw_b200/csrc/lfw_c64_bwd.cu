@@ -497,11 +497,13 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         umma::tmem_ld8(tl + cT2 + 8 * part, t2v);
         umma::tmem_ld8(tl + cT7 + 8 * part, t7v);
         umma::tmem_ld_wait();
-        float dmu[8], ddv[8], sa[8], sb[8], pre[8];
+        float dmu[8], ddv[8], sa[8], sb[8], pre[8], igate[8];      // igate = 1 / gate of the step
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
+          const float ip = __fdividef(1.f, pmv[j + 1]);
           dmu[j] = pmv[j + 1] * (tq1[j] + tq2[j]);
-          ddv[j] = __fdividef(t2v[j] + t7v[j], pmv[j + 1]);
+          ddv[j] = (t2v[j] + t7v[j]) * ip;
+          igate[j] = pmv[j] * ip;
           sa[j] = mw[j] * tq1[j];
           sb[j] = mw[j] * tq2[j] - vw[j] * t2v[j];
           pre[j] = vw[j] * t7v[j];
@@ -554,7 +556,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
           if (c0 + j < nvalid) {
             if (ph == 0) p_mu[j * ld_mu] = (T)(dmu[j] * qs);
             p_dv[j * ld_dv] = (T)ddv[j];
-            float dg = H * __fdividef(pmv[j], pmv[j + 1]);      // H / gate
+            float dg = H * igate[j];      // H / gate
             if (sig) {      // d gate / d pre-activation, from the pre-activation itself in fp32
               const float e = __expf(-Elem<T>::ld(r_gate + j * kDim));
               const float sg = __fdividef(1.f, 1.f + e);
