@@ -59,8 +59,10 @@ constexpr int oBnd = oXc + 3 * 8 * kDim * 4;        // boundary-term partials [8
 constexpr int oFixCode = oBnd + 8 * kDim * 4;       // [kFixCap] int
 constexpr int oFixVal = oFixCode + kFixCap * 4;     // [kFixCap] float
 constexpr int oFixMask = oFixVal + kFixCap * 4;     // [64] one bit per step
-constexpr int oFixRow = oFixMask + kDim * 8;        // [16 warps][2][64] floats: operand rows of a tiny-gate entry
-constexpr int oS0L = oFixRow + 16 * 2 * kDim * 4;   // start state of the chunk, [64][kS0Ld]
+constexpr int kFixRows = 16;                        // features with tiny gates per pass whose operand rows are kept
+constexpr int oFixSlot = oFixMask + kDim * 8;       // [64] int: row slot of a feature, -1 = none
+constexpr int oFixRow = oFixSlot + kDim * 4;        // [kFixRows][2][64] floats: own-side operand rows Mw, Vw
+constexpr int oS0L = oFixRow + kFixRows * 2 * kDim * 4;   // start state of the chunk, [64][kS0Ld]
 constexpr int oRL = oS0L + kDim * kS0Ld;            // end state gradient of the chunk, [64][kRLd]
 constexpr int oRaw = oRL + kDim * kRLd;             // x, f, q, k, fk, dO, and (fused layer) the gate pre-activations
 constexpr int kSmemB = oRaw + 7 * kRawBytes + 1024; // + slack for the 1024-byte alignment
@@ -83,7 +85,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
   unsigned char *sm = sm_raw + ((1024u - (umma::smem_u32(sm_raw) & 1023u)) & 1023u);
   __shared__ __align__(8) uint64_t barRaw, barZ, barM;
   __shared__ uint32_t tmem_slot;
-  __shared__ int s_fail, s_bad, fix_n;
+  __shared__ int s_fail, s_bad, fix_n, fix_rows_n;
 
   const int tid = threadIdx.x, warp = uniform_warp_idx(), lane = tid & 31;
   // stage 1: 0 = other side, 1 = own side; 16-step quarter; feature
@@ -102,7 +104,8 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
   int *fix_code = reinterpret_cast<int *>(sm + oFixCode);
   float *fix_val = reinterpret_cast<float *>(sm + oFixVal);
   unsigned long long *fix_mask = reinterpret_cast<unsigned long long *>(sm + oFixMask);
-  float *fix_row = reinterpret_cast<float *>(sm + oFixRow) + warp * 2 * kDim;
+  int *fix_slot = reinterpret_cast<int *>(sm + oFixSlot);
+  float *fix_rows = reinterpret_cast<float *>(sm + oFixRow);
   T *raw = reinterpret_cast<T *>(sm + oRaw);     // [6][64][64]: x, f, q, k, fk, dO
 
   // tensors: 0 x, 1 f, 2 q, 3 k, 4 fk, 5 dO
@@ -216,6 +219,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       if (tid == 0) {
         s_bad = 0;
         fix_n = 0;
+        fix_rows_n = 0;
       }
       if (tid < kDim) fix_mask[tid] = 0ull;
       float g[16], g_min;
@@ -241,7 +245,11 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
               const int slot = atomicAdd(&fix_n, 1);
               if (slot < kFixCap) {
                 fix_code[slot] = ((16 * tq + j) << 8) | feat;
-                atomicOr(&fix_mask[feat], 1ull << (16 * tq + j));
+                if (atomicOr(&fix_mask[feat], 1ull << (16 * tq + j)) == 0ull) {      // first entry of this feature
+                  const int rs = atomicAdd(&fix_rows_n, 1);
+                  fix_slot[feat] = rs < kFixRows ? rs : -1;
+                  if (rs >= kFixRows) s_bad = 1;
+                }
               } else {
                 s_bad = 1;
               }
@@ -286,6 +294,17 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         }
         tmem_put_dup(tl + cMw, part, h, mw);
         tmem_put_dup(tl + cVw, part, h, vw);
+        if (fix_mask[own] != 0ull) {      // rare: the direct pair sums of this feature read its operand rows
+          const int rs = fix_slot[own];
+          if (rs >= 0) {
+            float *row = fix_rows + rs * 2 * kDim + c0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              row[j] = mw[j];
+              row[kDim + j] = vw[j];
+            }
+          }
+        }
       }
       // ---- state blocks S2 = W_REF .* S0, R2 = W_63/W_REF .* R as A operands, boundary partial sums ----
       {
@@ -420,41 +439,25 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         }
         __syncwarp();
       }
-      // ---- tiny gates: pair terms i < t <= s summed directly (runs under the MMAs).  The operand
-      //      rows of the entry's feature are in the tensor-memory lanes of one lane quarter, so a
-      //      warp of that quarter copies them to shared memory first. ----
+      // ---- tiny gates: pair terms i < t <= s summed directly (runs under the MMAs), one warp per
+      //      entry, from the operand rows that the feature's threads left in shared memory ----
       {
         const int n_fix = fix_n < kFixCap ? fix_n : kFixCap;
         const unsigned char *zt = sm + oT;
-        for (int e = 0; e < n_fix; ++e) {
-          const int code = fix_code[e], t = code >> 8, fo = code & 0xff;
-          if (warp != (fo >> 4) + 4 * (e & 3)) continue;      // warp-uniform
-#pragma unroll
-          for (int cc = 0; cc < kDim; cc += 16) {
-            float a[16], bq[16];
-            umma::tmem_ld16(tl + cMw + cc, a);
-            umma::tmem_ld16(tl + cVw + cc, bq);
-            umma::tmem_ld_wait();
-            if (lane == (fo & 15)) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                fix_row[cc + j] = a[j];
-                fix_row[kDim + cc + j] = bq[j];
-              }
-            }
-          }
-          __syncwarp();
+        for (int e = warp; e < n_fix; e += kThreadsB / 32) {
+          const int code = fix_code[e], t = code >> 8, rs = fix_slot[code & 0xff];
+          if (rs < 0) continue;      // no row slot: the batch row is flagged
+          const float *row = fix_rows + rs * 2 * kDim;
           // sum_{s >= t} Mw[s] sum_{i < t} Z[s][i] Vw[i]: lanes over i, independent loads over s
           float acc = 0.f;
           for (int i = lane; i < t; i += 32) {
             float a = 0.f;
 #pragma unroll 8
-            for (int s = t; s < kC; ++s) a = fmaf(fix_row[s], *reinterpret_cast<const float *>(zt + toff(s, i)), a);
-            acc = fmaf(a, fix_row[kDim + i], acc);
+            for (int s = t; s < kC; ++s) a = fmaf(row[s], *reinterpret_cast<const float *>(zt + toff(s, i)), a);
+            acc = fmaf(a, row[kDim + i], acc);
           }
           acc = warp_sum(acc);
           if (lane == 0) fix_val[e] = acc;
-          __syncwarp();
         }
       }
       __syncthreads();      // fix_val, bndp visible
