@@ -460,7 +460,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
           if (lane == 0) fix_val[e] = acc;
         }
       }
-      __syncthreads();      // fix_val, bndp visible
+      if (fix_n > 0) __syncthreads();      // the direct sums are visible (fix_n is final since the ratio stage)
 
       // ---- feature-major epilogue: this thread = row `own`, steps c0 .. c0 + 7 ----
       {
