@@ -53,14 +53,14 @@ constexpr int kRLd = 272;              // row stride (bytes) of the end-gradient
 constexpr int oT = 0;
 constexpr int oPm = oT + 4 * kTile;                 // pm_w[own][t]   (ratios of the own side)
 constexpr int oPmo = oPm + kDim * kPmLd * 4;        // pm_o[t][other] (ratios of the other side)
-constexpr int oQt = oPmo + kC * kDim * 4;           // quarter products [other, own][4][64]
-constexpr int oXc = oQt + 2 * 4 * kDim * 4;         // partial sums [3][8 ranges][64]
+constexpr int oQt = oPmo + kC * kDim * 4;           // quarter products [pass][other, own][4][64]
+constexpr int oXc = oQt + 2 * 2 * 4 * kDim * 4;     // partial sums [3][8 ranges][64]
 constexpr int oBnd = oXc + 3 * 8 * kDim * 4;        // boundary-term partials [8][64]
 constexpr int oFixCode = oBnd + 8 * kDim * 4;       // [kFixCap] int
 constexpr int oFixVal = oFixCode + kFixCap * 4;     // [kFixCap] float
-constexpr int oFixMask = oFixVal + kFixCap * 4;     // [64] one bit per step
+constexpr int oFixMask = oFixVal + kFixCap * 4;     // [pass][64] one bit per step
 constexpr int kFixRows = 16;                        // features with tiny gates per pass whose operand rows are kept
-constexpr int oFixSlot = oFixMask + kDim * 8;       // [64] int: row slot of a feature, -1 = none
+constexpr int oFixSlot = oFixMask + 2 * kDim * 8;   // [64] int: row slot of a feature, -1 = none
 constexpr int oFixRow = oFixSlot + kDim * 4;        // [kFixRows][2][64] floats: own-side operand rows Mw, Vw
 constexpr int oS0L = oFixRow + kFixRows * 2 * kDim * 4;   // start state of the chunk, [64][kS0Ld]
 constexpr int oRL = oS0L + kDim * kS0Ld;            // end state gradient of the chunk, [64][kRLd]
@@ -85,7 +85,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
   unsigned char *sm = sm_raw + ((1024u - (umma::smem_u32(sm_raw) & 1023u)) & 1023u);
   __shared__ __align__(8) uint64_t barRaw, barZ, barM;
   __shared__ uint32_t tmem_slot;
-  __shared__ int s_fail, s_bad, fix_n, fix_rows_n;
+  __shared__ int s_fail, s_bad, fix_n2[2], fix_rows_n;
 
   const int tid = threadIdx.x, warp = uniform_warp_idx(), lane = tid & 31;
   // stage 1: 0 = other side, 1 = own side; 16-step quarter; feature
@@ -98,12 +98,12 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
 
   float *pmT = reinterpret_cast<float *>(sm + oPm);
   float *pmo = reinterpret_cast<float *>(sm + oPmo);
-  float *qtot = reinterpret_cast<float *>(sm + oQt);
+  float *qtot2 = reinterpret_cast<float *>(sm + oQt);
   float *xc = reinterpret_cast<float *>(sm + oXc);
   float *bndp = reinterpret_cast<float *>(sm + oBnd);
   int *fix_code = reinterpret_cast<int *>(sm + oFixCode);
   float *fix_val = reinterpret_cast<float *>(sm + oFixVal);
-  unsigned long long *fix_mask = reinterpret_cast<unsigned long long *>(sm + oFixMask);
+  unsigned long long *fix_mask2 = reinterpret_cast<unsigned long long *>(sm + oFixMask);
   int *fix_slot = reinterpret_cast<int *>(sm + oFixSlot);
   float *fix_rows = reinterpret_cast<float *>(sm + oFixRow);
   T *raw = reinterpret_cast<T *>(sm + oRaw);     // [6][64][64]: x, f, q, k, fk, dO
@@ -214,6 +214,12 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       // pass 0: own = k side (other = d side);  pass 1: own = d side
       const int blk_go = ph ? 4 : 1, blk_mo = ph ? 2 : 5, blk_vo = ph ? 3 : 0;   // other: gate, mul, div
       const int blk_gw = ph ? 1 : 4, blk_mw = ph ? 5 : 2, blk_vw = ph ? 0 : 3;   // own
+      // What a pass writes before its first barrier - the quarter products and the tiny-gate
+      // bookkeeping - the epilogue of the pass before may still be reading: one copy per pass, and no
+      // barrier between the passes of an item.
+      float *qtot = qtot2 + ph * 8 * kDim;
+      unsigned long long *fix_mask = fix_mask2 + ph * kDim;
+      int &fix_n = fix_n2[ph];
 
       // ---- stage 1: gate products of the four quarters, then the ratios to the anchor ----
       if (tid == 0) {
@@ -226,6 +232,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       qtot[(gsw * 4 + tq) * kDim + feat] =
           load_gates16<T>(raw + (gsw ? blk_gw : blk_go) * kC * kDim + feat, tq, g, &g_min);
       __syncthreads();
+      if (s_fail) break;      // a wait of the pass before gave up (seen by all after the barrier)
       {
         const float *qt = qtot + gsw * 4 * kDim + feat;
         const float carry = tq == 0 ? qt[kDim] : tq == 3 ? qt[2 * kDim] : 1.f;
@@ -569,10 +576,8 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
           }
         }
       }
-      sync_all();
-      if (s_fail) break;
+      umma::fence_before_sync();      // this pass's accumulator reads are ordered before the next barrier
     }
-    if (s_fail) break;
   }
   cp_async_wait_all();
   if (tid == 0 && s_fail) {
