@@ -580,6 +580,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
     }
   }
   cp_async_wait_all();
+  __syncthreads();      // s_fail of the last pass is visible
   if (tid == 0 && s_fail) {
     atomicExch(status, 1);
     if (raw_pending) acp::mbar_wait(&barRaw, it & 1u);   // bounded: let the copies in flight land

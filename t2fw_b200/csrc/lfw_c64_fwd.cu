@@ -301,10 +301,12 @@ lfw_c64_fwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         *reinterpret_cast<uint4 *>(orow + (size_t)t * out.ld + d0) = *reinterpret_cast<const uint4 *>(o);
       }
     }
-    sync_all();       // accumulators and tiles free for the next chunk
-    if (s_fail) break;
+    // No barrier here: the next chunk writes nothing before the barrier at its start (which every
+    // thread reaches only after this read-out), and that barrier also spreads s_fail.
+    umma::fence_before_sync();
   }
   cp_async_wait_all();
+  __syncthreads();      // s_fail of the last chunk is visible
   if (tid == 0) {
     if (s_fail) atomicExch(status, 1);
     // bounded: let copies that are still in flight land before the CTA leaves

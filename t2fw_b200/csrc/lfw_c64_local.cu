@@ -208,7 +208,10 @@ lfw_c64_local_kernel(const __grid_constant__ seq::Maps mp, float *__restrict__ M
       __syncwarp();
       if (tid == 0) flags[ci] = s_bad;
     }
-    if (!umma::mbar_wait(&barM, it & 1u)) s_fail = 1;
+    if (!umma::mbar_wait(&barM, it & 1u)) {
+      s_fail = 1;
+      flags[ci] = 1;      // results unusable: let the scan kernels redo the row
+    }
     umma::fence_after_sync();
     {
       // thread (lane quarter, column part, lane set, row): row d, columns 32 * h + 8 * (warp >> 2) .. + 7
@@ -220,12 +223,11 @@ lfw_c64_local_kernel(const __grid_constant__ seq::Maps mp, float *__restrict__ M
       *reinterpret_cast<float4 *>(dst) = make_float4(v[0], v[1], v[2], v[3]);
       *reinterpret_cast<float4 *>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
     }
-    sync_all();       // accumulator, A operand and tile free for the next chunk
-    if (s_fail) {
-      if (tid == 0) flags[ci] = 1;   // results unusable: let the scan kernels redo the row
-      break;
-    }
+    // No barrier here: the next chunk writes nothing before the barrier at its start, which every
+    // thread reaches only after this read-out; that barrier also spreads s_fail.
+    umma::fence_before_sync();
   }
+  __syncthreads();      // s_fail of the last chunk is visible
   if (tid == 0) {
     if (s_fail) atomicExch(status, 1);
     for (int bb = 0; bb < 2; ++bb)     // bounded: let copies that are still in flight land
