@@ -240,15 +240,20 @@ lfw_c64_fwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       constexpr uint32_t idesc = umma::make_idesc_tf32(64, 32, false, false);
       constexpr uint64_t n1 = (uint64_t)(32 * 128 >> 4);     // B rows 32..63
       if (elect_one()) {
+        // P first and on its own barrier: the state term runs while P is masked and stored
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
           umma::mma_tf32(d0 + cP, dT0 + o, dT1 + o, idesc, ks > 0);             // P = Qmid Kmid^T
           umma::mma_tf32(d1 + cP, dT0 + o, dT1 + n1 + o, idesc, ks > 0);
+        }
+        umma::mma_commit(&barP);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t o = (uint64_t)(((ks >> 2) * kColBlock + (ks & 3) * 32) >> 4);
           umma::mma_tf32(d0 + cO, dT2 + o, dT4 + o, idesc, ks > 0);             // O^ = Qstart S0'^T
           umma::mma_tf32(d1 + cO, dT2 + o, dT4 + n1 + o, idesc, ks > 0);
         }
-        umma::mma_commit(&barP);
       }
       __syncwarp();
       if (tid == 0 && s_bad) atomicExch(rowflag + b, 1);      // the scan kernel redoes this batch row
