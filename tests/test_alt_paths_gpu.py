@@ -46,7 +46,7 @@ print("ok")
 """
 
 
-@pytest.mark.parametrize("switch", ["T2FW_DISABLE_DFW_UMMA", "T2FW_DISABLE_DFW_CHUNK", "T2FW_DISABLE_CHUNK"])
+@pytest.mark.parametrize("switch", ["T2FW_DISABLE_DFW_UMMA", "T2FW_DISABLE_DFW_CHUNK", "T2FW_DISABLE_CHUNK", "T2FW_DISABLE_PDL"])
 def test_switched_path_matches_oracle(cuda, switch):
     env = dict(os.environ)
     env[switch] = "1"
