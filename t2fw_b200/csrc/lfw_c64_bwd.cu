@@ -18,7 +18,7 @@
 //                 + G_63 .* sum_d A_63 S0 R                              (d_f_key = that / g_t)
 // The suffix sum cancels the pair terms (i, s >= t) of its two parts; both parts come from the same
 // TF32-rounded Z and operands, so the cancellation is exact up to fp32 accumulation.  Where a gate
-// is below 2^-10 even that is not enough (the result is divided by the gate), and the pair terms
+// is below 2^-13 even that is not enough (the result is divided by the gate), and the pair terms
 // i < t <= s are summed directly for that (t, feature).
 // Results are feature-major ([own feature][step], rows = tensor-memory lanes): after tcgen05.ld a
 // thread owns one feature over eight steps, so the sums over time are register-local plus one

@@ -249,12 +249,16 @@ def test_blocked_extreme_gates(cuda):
 
 
 def test_many_tiny_gates_in_one_chunk(cuda):
-    """More gates below 2^-10 in a chunk than the exact-sum list holds, and rows full of small
-    (but in-range) gates: results stay right whichever path serves the row."""
-    x, f, q, k, fk, s, go, gs = lfw_inputs(3, 192, 64, 64, "sigmoid", 0.5, 41)
-    fk[0, 70:74, :] = 5e-4        # 256 tiny gates in one chunk of row 0 (list capacity 128)
-    f[1, 10, ::2] = 3e-4          # 32 tiny d-side gates at one step of row 1
-    fk[2, 130, 7] = 1e-4          # a single one in row 2
+    """More gates below 2^-13 in a chunk than the direct-sum list holds, rows with a few of them (the
+    direct pair sums), and rows full of small gates that stay on the factored form: results stay
+    right whichever path serves the row."""
+    x, f, q, k, fk, s, go, gs = lfw_inputs(4, 192, 64, 64, "sigmoid", 0.5, 41)
+    fk[0, 70:74, :] = 5e-5        # 256 tiny gates in one chunk of row 0 (list capacity 128)
+    f[1, 10, ::2] = 3e-5          # 32 tiny d-side gates at one step of row 1
+    fk[2, 130, 7] = 1e-5          # a single one in row 2
+    fk[2, 20, 9] = -6e-5          # and a negative one
+    fk[3, 100:104, ::3] = 4e-4    # 2^-11.3: small, but above the threshold
+    f[3, 30, :] = 2e-4            # 2^-12.3
     dev = to_dev((x, f, q, k, fk, s, go, gs), torch.float16, cuda)
     check_against_oracle(dev, run_cabi(*dev), torch.float16)
 
