@@ -451,17 +451,28 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       {
         const int n_fix = fix_n < kFixCap ? fix_n : kFixCap;
         const unsigned char *zt = sm + oT;
-        for (int e = warp; e < n_fix; e += kThreadsB / 32) {
+        // entries go to warps 8 .. 15: warps 0 and 4 are still issuing the second round
+        for (int e = warp - 8; e >= 0 && e < n_fix; e += 8) {
           const int code = fix_code[e], t = code >> 8, rs = fix_slot[code & 0xff];
           if (rs < 0) continue;      // no row slot: the batch row is flagged
           const float *row = fix_rows + rs * 2 * kDim;
           // sum_{s >= t} Mw[s] sum_{i < t} Z[s][i] Vw[i]: lanes over i, independent loads over s
           float acc = 0.f;
           for (int i = lane; i < t; i += 32) {
-            float a = 0.f;
-#pragma unroll 8
-            for (int s = t; s < kC; ++s) a = fmaf(row[s], *reinterpret_cast<const float *>(zt + toff(s, i)), a);
-            acc = fmaf(a, row[kDim + i], acc);
+            const unsigned char *zcol = zt + (i >> 5) * kColBlock + ((i & 3) << 2);      // toff(s, i) without the s terms
+            const int ic = (i >> 2) & 7;
+            float a0 = 0.f, a1 = 0.f;      // two chains: the sums are latency-bound
+            int s = t;
+            if ((kC - t) & 1) {
+              a0 = row[s] * *reinterpret_cast<const float *>(zcol + s * 128 + ((ic ^ (s & 7)) << 4));
+              ++s;
+            }
+#pragma unroll 4
+            for (; s < kC; s += 2) {
+              a0 = fmaf(row[s], *reinterpret_cast<const float *>(zcol + s * 128 + ((ic ^ (s & 7)) << 4)), a0);
+              a1 = fmaf(row[s + 1], *reinterpret_cast<const float *>(zcol + (s + 1) * 128 + ((ic ^ ((s + 1) & 7)) << 4)), a1);
+            }
+            acc = fmaf(a0 + a1, row[kDim + i], acc);
           }
           acc = warp_sum(acc);
           if (lane == 0) fix_val[e] = acc;
