@@ -301,7 +301,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         }
         tmem_put_dup(tl + cMw, part, h, mw);
         tmem_put_dup(tl + cVw, part, h, vw);
-        if (fix_mask[own] != 0ull) {      // rare: the direct pair sums of this feature read its operand rows
+        if (fix_n > 0 && fix_mask[own] != 0ull) {      // rare: the direct pair sums of this feature read its operand rows
           const int rs = fix_slot[own];
           if (rs >= 0) {
             float *row = fix_rows + rs * 2 * kDim + c0;
@@ -493,7 +493,6 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         float bnd = 0.f;
 #pragma unroll
         for (int r = 0; r < 8; ++r) bnd += bndp[r * kDim + own];
-        const unsigned m8 = (unsigned)((fix_mask[own] >> c0) & 0xffull);
         // own-side operand values: both lane sets hold all 64 columns, the load names one range per warp
         float mw[8], vw[8];
         {
@@ -550,13 +549,16 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         const float base_h = addA + addP + bnd;
 #pragma unroll
         for (int j = 0; j < 8; ++j) sb[j] += addB;
-        if (m8) {        // some gate of this range is tiny: its pair terms were summed directly
+        if (fix_n > 0) {      // (uniform) tiny gates in this chunk: their pair terms were summed directly
           const int n_fix = fix_n < kFixCap ? fix_n : kFixCap;
+          for (int e = 0; e < n_fix; ++e) {
+            const int code = fix_code[e], jj = (code >> 8) - c0;
+            if ((code & 0xff) == own && (unsigned)jj < 8u) {
+              const float v = fix_val[e];
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if ((m8 >> j) & 1u)
-              for (int e = 0; e < n_fix; ++e)
-                if (fix_code[e] == (((c0 + j) << 8) | own)) sb[j] = fix_val[e];
+              for (int j = 0; j < 8; ++j) sb[j] = (jj == j) ? v : sb[j];
+            }
+          }
         }
         // 16 consecutive features of one step are 32 contiguous bytes: the results go straight out.
         // Fused layer: the query was scaled on the way in, and the gate tensor holds pre-activations
