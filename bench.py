@@ -51,6 +51,8 @@ WORKLOADS = {
     "dfw": (96, 1024, 64, 64),       # delta rule (DFWFunction), GPT-2-small shape, fwd + bwd
     "gpt2": (96, 1024, 64, 64),      # GPT-2-small, every attention replaced by a fast-weight layer:
                                      # batch 8 x 12 heads per GPU, whole training step (run_gpt2)
+    "seqsplit": (16, 65536, 64, 64), # one long sequence per row, its TIME axis split over the GPUs
+                                     # (t2fw_b200/seq_parallel.py; strong scaling, run_seqsplit)
 }
 CPU_SAMPLE_ROWS = {"train": 16, "decode": 4096, "long": 1, "dfw": 16}
 
@@ -369,9 +371,104 @@ def run_gpt2(args):
         dist.destroy_process_group()
 
 
+def run_seqsplit(args):
+    """B*H = 16 rows of 65 536 steps (D = K = 64, fp16), forward + backward through
+    LFWSeqParallelFunction: every GPU holds T / N steps of every row and the ranks exchange one segment
+    summary per direction (two all-gathers of 16 x 4 224 floats per rank and one all-reduce).  Strong
+    scaling: the job is the same at every N; at N = 1 the exchange degenerates to the rank itself."""
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the kernels have no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world == 1:      # the function needs a process group even for one rank
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from t2fw_b200 import _lib
+    from t2fw_b200.parallel import max_over_ranks
+    from t2fw_b200.seq_parallel import LFWSeqParallelFunction
+
+    lib = _lib.load_core()
+    B, T, D, K = WORKLOADS["seqsplit"]
+    Tr = T // world
+    g = torch.Generator().manual_seed(args.seed + 7 * rank)
+    def rnd(*shape):
+        return torch.randn(*shape, generator=g)
+    # two input sets (each rank's segment: 5 x 16 x T/N x 64 x 2 bytes), sigmoid gates on both sides
+    sets = []
+    for _ in range(2):
+        x, q, k = rnd(B, Tr, D), rnd(B, Tr, K) / 8, rnd(B, Tr, K) / 8
+        f, fk = torch.sigmoid(rnd(B, Tr, D) + 2), torch.sigmoid(rnd(B, Tr, K) + 2)
+        go = rnd(B, Tr, D)
+        sets.append([t.half().to(dev) for t in (x, f, q, k, fk, go)])
+    state = torch.zeros(B, D, K, dtype=torch.float16, device=dev)
+    gfin = (torch.randn(B, D, K, generator=g) / world).half().to(dev)
+
+    def step(i):
+        x, f, q, k, fk, go = sets[i & 1]
+        leaves = [t.requires_grad_(True) for t in (x, f, q, k, fk)] + [state.clone().requires_grad_(True)]
+        out, fin = LFWSeqParallelFunction.apply(*leaves)
+        return torch.autograd.grad([out, fin], leaves, [go, gfin])
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    barrier()
+    clk = ClockSampler(local)
+    clk.start()
+    l0 = lib.t2fw_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    launches = lib.t2fw_launch_count() - l0
+    clocks = clk.stop()
+    ms = max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
+    if rank == 0:
+        esz = 2
+        algo = esz * (B * T * (2 * D + 3 * K) + B * T * D + 2 * B * D * K) + esz * (B * T * D + 2 * B * T * (2 * D + 3 * K) + 3 * B * D * K)
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+                peak, peak_kind = float(json.load(fh)["hbm_gbs"]), "measured copy bandwidth"
+        except Exception:
+            peak, peak_kind = 6650.0, "fallback copy bandwidth"
+        achieved = algo / world / (ms * 1e-3) / 1e9        # per GPU
+        print(json.dumps({
+            "metric": "lfw_fwd_bwd_tokens_per_s", "value": B * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32 state arithmetic, f16 I/O", "data": "synthetic",
+            "config": {"workload": "seqsplit: LFW forward+backward, B*H=%d rows of T=%d steps, D=K=64, fp16; the time axis "
+                                   "split over the GPUs (%d steps per GPU), sigmoid gates on both sides" % (B, T, Tr),
+                       "api": "t2fw_b200.seq_parallel.LFWSeqParallelFunction.apply + torch.autograd.grad (eager)",
+                       "exchange": "per step and rank: 2 all-gathers of %d bytes, 1 all-reduce of %d bytes (NCCL)"
+                                   % (B * (D * K + D + K) * 4, B * D * K * 4),
+                       "l2": "two alternating input sets; one segment set is %.0f MB" % (6 * B * Tr * 64 * 2 / 1e6)},
+            "clocks": clocks, "e2e": None, "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "whole step per GPU (summaries, exchange, forward and backward kernels)"},
+            "cpu_baseline": None}))
+    dist.destroy_process_group()
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
+        return
+    if args.workload == "seqsplit":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference has no multi-device code; the "
+                          "time-split workload is measured against the unsplit run of the same library"}))
         return
     if args.workload == "gpt2":
         print(json.dumps({"impl": "reference", "unavailable": "the reference ships no model: the end-to-end "
@@ -896,6 +993,8 @@ def main():
         run_reference(args)
     elif args.workload == "gpt2":
         run_gpt2(args)
+    elif args.workload == "seqsplit":
+        run_seqsplit(args)
     else:
         run_ours(args)
 

@@ -138,6 +138,25 @@ int t2fw_lfw_fused_backward(const void *grad_output, const void *grad_state, con
                             int64_t B, int64_t T, int64_t H, int dtype,
                             void *scratch, size_t scratch_bytes, void *stream);
 
+/* Summary of a sequence segment of the decay rule, for splitting the TIME axis over devices
+ * (D = K = 64, 16-bit storage).  The recurrence is linear in the state, so a segment acts on the
+ * state as  S_end = (decay_d decay_k^T) .* S_start + L  with the segment's total decays and the
+ * state L that a zero state becomes; the state gradient runs backwards through the same map.
+ *   backward = 0: (val_d, gate_d, val_k, gate_k) = (x, f, key, f_key) [B,T,64]; end_state = L
+ *   backward = 1: (grad_output, f, query, f_key);  end_state = the state gradient at the segment
+ *                 start for a zero gradient at its end
+ * decay_d, decay_k: fp32 [B,64], products of f / f_key over the segment (NaN for a batch row whose
+ * gate products leave the supported range).  Each device computes the summary of its own segment,
+ * the devices exchange them ([B,64,64] + 2 x [B,64] each), combine the ones before (after) their own
+ * into their incoming state (state gradient) and then call the ordinary forward (backward) entry
+ * point: t2fw_b200/seq_parallel.py.  No counterpart in the reference, which has no multi-device
+ * code; the recurrence it restates is t2fw/torch.py:21-28. */
+size_t t2fw_lfw_segment_summary_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K, int dtype);
+int t2fw_lfw_segment_summary(int backward, const void *val_d, const void *gate_d, const void *val_k,
+                             const void *gate_k, void *end_state, float *decay_d, float *decay_k, int64_t B,
+                             int64_t T, int64_t D, int64_t K, int dtype, void *scratch, size_t scratch_bytes,
+                             void *stream);
+
 /*
  * Delta rule forward:  o_t = S_{t-1} q_t ,  delta_t = v_t - S_{t-1} k_t ,
  *                      S_t = S_{t-1} + delta_t k_t^T.

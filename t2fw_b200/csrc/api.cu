@@ -221,6 +221,37 @@ int t2fw_lfw_backward(const void *grad_output, const void *grad_state, const voi
                            static_cast<cudaStream_t>(stream));
 }
 
+// ---- summary of a sequence segment (time axis split over devices) -------------------------------
+size_t t2fw_lfw_segment_summary_scratch_bytes(int64_t B, int64_t T, int64_t D, int64_t K, int dtype) {
+  if (B <= 0 || T <= 0 || !lfw_chunk_supported(D, K, dtype, 64)) return 0;
+  return lfw_segment_summary_scratch_bytes(B, T);
+}
+
+int t2fw_lfw_segment_summary(int backward, const void *val_d, const void *gate_d, const void *val_k,
+                             const void *gate_k, void *end_state, float *decay_d, float *decay_k, int64_t B,
+                             int64_t T, int64_t D, int64_t K, int dtype, void *scratch, size_t scratch_bytes,
+                             void *stream) {
+  int rc = check_common(B, T, D, K, dtype);
+  if (rc != T2FW_OK) return rc;
+  T2FW_CHECK_ARG(val_d && gate_d && val_k && gate_k && end_state && decay_d && decay_k, "null pointer argument");
+  if (!lfw_chunk_supported(D, K, dtype, 64)) {
+    set_error("segment summary: D = K = 64 and 16-bit storage only (D=%lld K=%lld dtype %d)", (long long)D, (long long)K,
+              dtype);
+    return T2FW_ERR_UNSUPPORTED;
+  }
+  const size_t need = lfw_segment_summary_scratch_bytes(B, T);
+  if (scratch == nullptr || scratch_bytes < need) {
+    set_error("segment summary needs %zu bytes of scratch, got %zu", need, scratch_bytes);
+    return T2FW_ERR_SCRATCH;
+  }
+  if (!aligned16({val_d, gate_d, val_k, gate_k, end_state, decay_d, decay_k, scratch})) {
+    set_error("segment summary: all pointers must be 16-byte aligned");
+    return T2FW_ERR_UNSUPPORTED;
+  }
+  return lfw_segment_summary(backward != 0, val_d, gate_d, val_k, gate_k, end_state, decay_d, decay_k, B, T, dtype,
+                             scratch, static_cast<cudaStream_t>(stream));
+}
+
 // ---- fused decay-rule layer (heads read in place from the projection output) -------------------
 static int check_fused(int64_t B, int64_t T, int64_t H, int dtype) {
   T2FW_CHECK_ARG(B > 0 && T > 0 && H > 0, "sizes must be positive (B=%lld T=%lld H=%lld)", (long long)B,

@@ -160,6 +160,11 @@ int lfw_blocked_backward(const void *go, const void *gs, const void *x, const vo
                          void *df, void *dq, void *dk, void *dfk, void *ds, int64_t B, int64_t T,
                          int64_t D, int64_t K, int dtype, int64_t ckpt_every, void *scratch,
                          cudaStream_t st);
+// what a sequence segment does to the state / state gradient (D = K = 64, 16-bit): see lfw_c64_host.cu
+size_t lfw_segment_summary_scratch_bytes(int64_t B, int64_t T);
+int lfw_segment_summary(bool backward, const void *val_d, const void *gate_d, const void *val_k, const void *gate_k,
+                        void *end_state, float *A_out, float *G_out, int64_t B, int64_t T, int dtype, void *scratch,
+                        cudaStream_t st);
 // fused layer form of the chunked path: qkvg [B][T][4*H*64] read in place (lfw_c64_host.cu)
 size_t lfw_fused_scratch_bytes(int64_t B, int64_t T, int H);
 int lfw_fused_forward(const void *qkvg, const void *state, void *out, void *ckpt, int64_t B, int64_t T, int H,

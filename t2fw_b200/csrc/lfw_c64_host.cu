@@ -112,7 +112,8 @@ lfw_c64_carry_kernel(const T *__restrict__ init, float *__restrict__ M, const fl
   const int64_t b = blockIdx.x / (kDim / kCarryRows);
   const int d0 = (int)(blockIdx.x % (kDim / kCarryRows)) * kCarryRows;
   const int dl = tid / (kDim / 4), d = d0 + dl, k0 = (tid % (kDim / 4)) * 4;
-  float4 S = Quad<T>::ld(init + ((size_t)b * kDim + d) * kDim + k0);
+  // init may be null: the carry then starts from zero (the summary of a sequence segment)
+  float4 S = init != nullptr ? Quad<T>::ld(init + ((size_t)b * kDim + d) * kDim + k0) : make_float4(0.f, 0.f, 0.f, 0.f);
   int any = 0;
   for (int64_t c0 = 0; c0 < nc; c0 += kBatch) {
     float4 l[kBatch];
@@ -393,6 +394,68 @@ int lfw_chunk_backward_grid(const void *go, const void *gs_blocks, const void *x
                                   scratch, st);
   return backward_typed<__nv_bfloat16>(c, gs_blocks, state_blocks, ckpt_blocks, outs, ld, col, ds_blocks, dtype,
                                        ckpt_every, scratch, st);
+}
+
+// ---- summary of a sequence segment (for splitting the time axis over devices) ------------------
+// Total decay of a segment per feature: the product of the chunks' decay vectors.  A row with a
+// flagged chunk (gate products beyond 2^100) gets NaN decays, so that whatever is built on the
+// summary shows the problem instead of hiding it.
+__global__ void __launch_bounds__(128)
+lfw_c64_decay_totals_kernel(const float *__restrict__ Ac, const float *__restrict__ Gc, const int *__restrict__ rowflag,
+                            float *__restrict__ A_out, float *__restrict__ G_out, int64_t B, int64_t nc) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= B * 2 * kDim) return;
+  const int64_t b = i / (2 * kDim);
+  const int side = (int)((i / kDim) & 1), feat = (int)(i % kDim);
+  const float *src = side ? Gc : Ac;
+  float p = 1.f;
+  for (int64_t c = 0; c < nc; ++c) p *= src[((size_t)b * nc + c) * kDim + feat];
+  if (rowflag[b] != 0) p = __int_as_float(0x7fc00000);
+  (side ? G_out : A_out)[b * kDim + feat] = p;
+}
+
+template <typename T>
+int summary_typed(bool backward, const void *val_d, const void *gate_d, const void *val_k, const void *gate_k,
+                  void *end_state, float *A_out, float *G_out, int64_t B, int64_t T_, int dtype, void *scratch,
+                  cudaStream_t st) {
+  const int64_t nc = ceil_div64(T_, kC), rows = B * T_;
+  Scratch s = carve(scratch, B, nc);
+  seq::Maps mp;
+  const Tensor2D loc[4] = {{val_d, kDim, 0}, {gate_d, kDim, 0}, {val_k, kDim, 0}, {gate_k, kDim, 0}};
+  int rc = build_maps(mp, loc, 4, rows, 1, 0, 1.f);
+  if (rc != T2FW_OK) return rc;
+  rc = lfw_chunk_local_umma(backward, mp, s.M, s.Ac, s.Gc, s.flags, B, T_, dtype, st);
+  if (rc != T2FW_OK) return rc;
+  const dim3 grid((unsigned)(B * (kDim / kCarryRows)));
+  if (backward) {      // the state gradient at the segment start that the segment's own output gradients cause
+    T2FW_CHECK_CUDA(launch_dependent(lfw_c64_carry_kernel<T, false>, grid, dim3(kCarryThreads), 0, st, (const T *)nullptr,
+                                     s.M, (const float *)s.Ac, (const float *)s.Gc, (const int *)s.flags, s.rowflag, 0,
+                                     (T *)end_state, B, nc));
+  } else {             // the state at the segment end that the segment's own inputs cause
+    T2FW_CHECK_CUDA(launch_dependent(lfw_c64_carry_kernel<T, true>, grid, dim3(kCarryThreads), 0, st, (const T *)nullptr,
+                                     s.M, (const float *)s.Ac, (const float *)s.Gc, (const int *)s.flags, s.rowflag, 0,
+                                     (T *)s.ck_all, B, nc));
+    lfw_c64_pick_ckpt_kernel<T><<<(unsigned)ceil_div64(B * (kDim * kDim / 8), 256), 256, 0, st>>>(
+        (const T *)s.ck_all, (T *)end_state, B, nc, nc, 1);
+  }
+  lfw_c64_decay_totals_kernel<<<(unsigned)ceil_div64(B * 2 * kDim, 128), 128, 0, st>>>(s.Ac, s.Gc, s.rowflag, A_out,
+                                                                                     G_out, B, nc);
+  T2FW_CHECK_LAUNCH(backward ? 2 : 3);
+  return T2FW_OK;
+}
+
+size_t lfw_segment_summary_scratch_bytes(int64_t B, int64_t T_) { return scratch_bytes(B, ceil_div64(T_, kC), 2 * kC); }
+
+// forward flavour: (val_d, gate_d, val_k, gate_k) = (x, f, k, f_key), end_state = the state a zero state becomes over
+// the segment; backward flavour: (dO, f, q, f_key), end_state = the state gradient at the segment start for a zero
+// gradient at its end.  A_out, G_out [B][64] fp32: the segment's total decays.
+int lfw_segment_summary(bool backward, const void *val_d, const void *gate_d, const void *val_k, const void *gate_k,
+                        void *end_state, float *A_out, float *G_out, int64_t B, int64_t T_, int dtype, void *scratch,
+                        cudaStream_t st) {
+  if (dtype == T2FW_F16)
+    return summary_typed<__half>(backward, val_d, gate_d, val_k, gate_k, end_state, A_out, G_out, B, T_, dtype, scratch, st);
+  return summary_typed<__nv_bfloat16>(backward, val_d, gate_d, val_k, gate_k, end_state, A_out, G_out, B, T_, dtype,
+                                      scratch, st);
 }
 
 // ---- fused layer entry points (heads read in place from the projection output) ----------------

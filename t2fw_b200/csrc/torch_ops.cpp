@@ -308,6 +308,41 @@ std::vector<at::Tensor> dfw_backward(at::Tensor grad_output, at::Tensor grad_sta
   return {d_q, d_k, d_v, d_s};
 }
 
+// What a sequence segment does to the state (backward = false: inputs value, forget, key, f_key) or
+// to the state gradient (backward = true: grad_output, forget, query, f_key), D = K = 64, 16-bit:
+// {end_state [B,64,64], decay_d [B,64] fp32, decay_k [B,64] fp32}.  See t2fw_lfw_segment_summary.
+std::vector<at::Tensor> lfw_segment_summary(at::Tensor val_d, at::Tensor gate_d, at::Tensor val_k, at::Tensor gate_k,
+                                            bool backward) {
+  T2FW_CHECK_INPUT(val_d);
+  T2FW_CHECK_INPUT(gate_d);
+  T2FW_CHECK_INPUT(val_k);
+  T2FW_CHECK_INPUT(gate_k);
+  TORCH_CHECK(val_d.dim() == 3 && val_k.dim() == 3, "expected [B,T,D] and [B,T,K] tensors");
+  const int64_t B = val_d.size(0), T = val_d.size(1), D = val_d.size(2), K = val_k.size(2);
+  TORCH_CHECK(gate_d.sizes() == val_d.sizes() && gate_k.sizes() == val_k.sizes() && val_k.size(0) == B &&
+                  val_k.size(1) == T,
+              "segment_summary: tensor shapes do not agree");
+  check_same(gate_d, val_d, "gate_d");
+  check_same(val_k, val_d, "val_k");
+  check_same(gate_k, val_d, "gate_k");
+  TORCH_CHECK(B > 0 && T > 0, "empty tensors are not supported");
+  const c10::cuda::CUDAGuard guard(val_d.device());
+  const int dt = dtype_code(val_d);
+  at::Tensor end_state = at::empty({B, D, K}, val_d.options());
+  at::Tensor decay_d = at::empty({B, D}, val_d.options().dtype(at::kFloat));
+  at::Tensor decay_k = at::empty({B, K}, val_d.options().dtype(at::kFloat));
+  const size_t sb = t2fw_lfw_segment_summary_scratch_bytes(B, T, D, K, dt);
+  TORCH_CHECK(sb != 0, "lfw.segment_summary: D = K = 64 and fp16 / bf16 only");
+  at::Tensor scratch = make_scratch(sb, val_d);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check_status(t2fw_lfw_segment_summary(backward ? 1 : 0, val_d.data_ptr(), gate_d.data_ptr(), val_k.data_ptr(),
+                                        gate_k.data_ptr(), end_state.data_ptr(), decay_d.data_ptr<float>(),
+                                        decay_k.data_ptr<float>(), B, T, D, K, dt, ptr_or_null(scratch), sb,
+                                        stream.stream()),
+               "lfw.segment_summary");
+  return {end_state, decay_d, decay_k};
+}
+
 }  // namespace
 
 TORCH_LIBRARY(lfw, m) {
@@ -316,6 +351,7 @@ TORCH_LIBRARY(lfw, m) {
   m.def("decode_step", lfw_decode_step);
   m.def("fused_forward", lfw_fused_forward);
   m.def("fused_backward", lfw_fused_backward);
+  m.def("segment_summary", lfw_segment_summary);
 }
 
 TORCH_LIBRARY(dfw, m) {
