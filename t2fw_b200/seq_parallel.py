@@ -102,9 +102,11 @@ class LFWSeqParallelFunction(torch.autograd.Function):
         x, f, q, k, fk = (t.contiguous() for t in (value, forget, query, key, f_key))
         L, A, G = ops.summary(x, f, k, fk, False)
         summaries = all_gather_summaries(pack_summary(L, A, G), group)
-        s_in = fold_forward(state, summaries, rank, D, K).to(state.dtype).contiguous()
+        s_in32 = fold_forward(state, summaries, rank, D, K)
+        s_in = s_in32.to(state.dtype).contiguous()
         outputs, ckpt = ops.forward(x, f, q, k, fk, s_in)
-        final = fold_forward(state, summaries, world, D, K).to(state.dtype)
+        # the state after the whole sequence: carry on from this rank's incoming state
+        final = fold_forward(s_in32, summaries[rank:], world - rank, D, K).to(state.dtype)
         ctx.save_for_backward(x, f, q, k, fk, outputs, s_in, ckpt, *summaries)
         ctx.group, ctx.ops, ctx.dims = group, ops, (D, K)
         return outputs, final
