@@ -7,7 +7,10 @@ the rest of the reference (whose package imports JIT-compile CUDA sources).  ora
 git-ignored: nothing of the reference is committed; the folder travels to the GPU machine like the
 other build outputs.  Test infrastructure only.
 
-    python -m oracle.make_ref [/path/to/reference]      (default: /root/reference)
+    python -m oracle.make_ref [/path/to/reference]
+
+Without an argument the reference is looked for in $T2FW_REFERENCE_ROOT, then in a folder named
+`reference` beside this repository.
 """
 import os
 import shutil
@@ -17,9 +20,13 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 REF_DIR = os.path.join(HERE, "_ref")
 
 
-def build(reference_root: str = "/root/reference") -> str:
+def default_reference_root() -> str:
+    return os.environ.get("T2FW_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(reference_root: str = "") -> str:
     """Returns the path of oracle/_ref/t2fw/torch.py, or "" if the reference is not present."""
-    src = os.path.join(reference_root, "t2fw", "torch.py")
+    src = os.path.join(reference_root or default_reference_root(), "t2fw", "torch.py")
     if not os.path.exists(src):
         return ""
     dst_dir = os.path.join(REF_DIR, "t2fw")
