@@ -1,8 +1,12 @@
 #!/usr/bin/env python
 """Benchmark of the decay-rule (LFW) hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload train|decode|long]
-                    [--gates raw_f1|raw|sigmoid] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload train|decode|long|dfw|gpt2|seqsplit]
+                    [--gates raw_f1|raw|sigmoid] [--impl ours|reference] [--ckpt-every C]
+
+Workloads: train (default, below), decode (T=1, B*H=4096), long (B*H=16, T=16384, D=K=128), dfw (the delta
+rule at the default shape), gpt2 (GPT-2-small with every attention replaced, whole training step),
+seqsplit (16 rows of 65 536 steps with the TIME axis split over the GPUs; strong scaling).
 
 Default workload ("train"): one LFW layer at GPT-2-small shape, fp16, B*H=96, T=1024,
 D=K=64, x,q,k,f_key ~ N(0,1) with q,k scaled by 1/8, forget gate f = 1, zero initial state;
