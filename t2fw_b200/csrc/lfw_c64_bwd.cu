@@ -54,7 +54,8 @@ constexpr int oT = 0;
 constexpr int oPm = oT + 4 * kTile;                 // pm_w[own][t]   (ratios of the own side)
 constexpr int oPmo = oPm + kDim * kPmLd * 4;        // pm_o[t][other] (ratios of the other side)
 constexpr int oQt = oPmo + kC * kDim * 4;           // quarter products [pass][other, own][4][64]
-constexpr int oXc = oQt + 2 * 2 * 4 * kDim * 4;     // partial sums [3][8 ranges][64]
+constexpr int oPrd = oQt + 2 * 2 * 4 * kDim * 4;    // products of the quarter products [pass][6][64], see the ratio stage
+constexpr int oXc = oPrd + 2 * 6 * kDim * 4;        // partial sums [3][8 ranges][64]
 constexpr int oBnd = oXc + 3 * 8 * kDim * 4;        // boundary-term partials [8][64]
 constexpr int oFixCode = oBnd + 8 * kDim * 4;       // [kFixCap] int
 constexpr int oFixVal = oFixCode + kFixCap * 4;     // [kFixCap] float
@@ -99,6 +100,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
   float *pmT = reinterpret_cast<float *>(sm + oPm);
   float *pmo = reinterpret_cast<float *>(sm + oPmo);
   float *qtot2 = reinterpret_cast<float *>(sm + oQt);
+  float *prd2 = reinterpret_cast<float *>(sm + oPrd);
   float *xc = reinterpret_cast<float *>(sm + oXc);
   float *bndp = reinterpret_cast<float *>(sm + oBnd);
   int *fix_code = reinterpret_cast<int *>(sm + oFixCode);
@@ -218,6 +220,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       // bookkeeping - the epilogue of the pass before may still be reading: one copy per pass, and no
       // barrier between the passes of an item.
       float *qtot = qtot2 + ph * 8 * kDim;
+      float *prd = prd2 + ph * 6 * kDim;
       unsigned long long *fix_mask = fix_mask2 + ph * kDim;
       int &fix_n = fix_n2[ph];
 
@@ -238,6 +241,14 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         const float carry = tq == 0 ? qt[kDim] : tq == 3 ? qt[2 * kDim] : 1.f;
         float pm[16];
         if (!ratios16(tq, g, carry, pm)) s_bad = 1;
+        if (tq == 1) {
+          // Products over the half chunks, once per feature instead of once per use.  Other side:
+          // [0] up to the anchor, [1] after it, [2] the whole chunk; own side: [3], [4], [5] = 1 / [3].
+          const float up = qt[0] * qt[kDim], after = qt[2 * kDim] * qt[3 * kDim];
+          prd[(3 * gsw) * kDim + feat] = up;
+          prd[(3 * gsw + 1) * kDim + feat] = after;
+          prd[(3 * gsw + 2) * kDim + feat] = gsw ? __fdividef(1.f, up) : up * after;
+        }
         if (gsw == 0) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) pmo[(16 * tq + j) * kDim + feat] = pm[j];
@@ -269,10 +280,8 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       // ---- stage 2: operands ----
       {   // other side, time-major tiles in shared memory: this thread = four features, steps t and t + 32
         const int f4 = (tid & 15) * 4;
-        const float4 o_ref = mul4(*reinterpret_cast<const float4 *>(qtot + f4),
-                                  *reinterpret_cast<const float4 *>(qtot + kDim + f4));
-        const float4 oc_ref = mul4(*reinterpret_cast<const float4 *>(qtot + 2 * kDim + f4),
-                                   *reinterpret_cast<const float4 *>(qtot + 3 * kDim + f4));
+        const float4 o_ref = *reinterpret_cast<const float4 *>(prd + f4);
+        const float4 oc_ref = *reinterpret_cast<const float4 *>(prd + kDim + f4);
         const T *r_m = raw + blk_mo * kC * kDim + f4, *r_v = raw + blk_vo * kC * kDim + f4;
         unsigned char *t0p = sm + oT;
 #pragma unroll
@@ -288,12 +297,12 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
           *reinterpret_cast<float4 *>(t0p + 3 * kTile + o) = rna4(mul4(v, oc_ref));
         }
       }
+      float mw[8], vw[8];      // own-side operand values of this thread, used again by the epilogue
       {   // own side, feature-major A operands in tensor memory: row `own`, steps c0 .. c0 + 7
         const T *r_m = raw + blk_mw * kC * kDim + c0 * kDim + own, *r_v = raw + blk_vw * kC * kDim + c0 * kDim + own;
         const float4 p0 = *reinterpret_cast<const float4 *>(pmT + own * kPmLd + c0);
         const float4 p1 = *reinterpret_cast<const float4 *>(pmT + own * kPmLd + c0 + 4);
         const float pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-        float mw[8], vw[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           mw[j] = rna_tf32(Elem<T>::ld(r_m + j * kDim) * pv[j]);
@@ -315,8 +324,10 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       }
       // ---- state blocks S2 = W_REF .* S0, R2 = W_63/W_REF .* R as A operands, boundary partial sums ----
       {
-        const float w_ref = qtot[4 * kDim + own] * qtot[5 * kDim + own];
-        const float wc_ref = qtot[6 * kDim + own] * qtot[7 * kDim + own];
+        const float w_ref = prd[3 * kDim + own], wc_ref = prd[4 * kDim + own];
+        const float4 oc0 = *reinterpret_cast<const float4 *>(prd + 2 * kDim + c0);
+        const float4 oc1 = *reinterpret_cast<const float4 *>(prd + 2 * kDim + c0 + 4);
+        const float ocv[8] = {oc0.x, oc0.y, oc0.z, oc0.w, oc1.x, oc1.y, oc1.z, oc1.w};
         float sv[8], rv[8];
         if (ph == 0) {        // S(own = k, other = d = c0 + j): a column of the stored blocks
 #pragma unroll
@@ -337,11 +348,9 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         float s2[8], r2[8], acc = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const int o = c0 + j;
-          const float oc = (qtot[o] * qtot[kDim + o]) * (qtot[2 * kDim + o] * qtot[3 * kDim + o]);
           s2[j] = rna_tf32(sv[j] * w_ref);
           r2[j] = rna_tf32(rv[j] * wc_ref);
-          acc = fmaf(oc * s2[j], r2[j], acc);
+          acc = fmaf(ocv[j] * s2[j], r2[j], acc);
         }
         tmem_put_dup(tl + cS2, part, h, s2);
         tmem_put_dup(tl + cR2, part, h, r2);
@@ -488,26 +497,11 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
           const float4 p1 = *reinterpret_cast<const float4 *>(pmT + own * kPmLd + c0 + 4);
           pmv[1] = p0.x; pmv[2] = p0.y; pmv[3] = p0.z; pmv[4] = p0.w; pmv[5] = p1.x; pmv[6] = p1.y; pmv[7] = p1.z; pmv[8] = p1.w;
           // ratio of the step before this range; before step 0 it is 1 / W_REF
-          pmv[0] = c0 ? pmT[own * kPmLd + c0 - 1] : __fdividef(1.f, qtot[4 * kDim + own] * qtot[5 * kDim + own]);
+          pmv[0] = c0 ? pmT[own * kPmLd + c0 - 1] : prd[5 * kDim + own];
         }
         float bnd = 0.f;
 #pragma unroll
         for (int r = 0; r < 8; ++r) bnd += bndp[r * kDim + own];
-        // own-side operand values: both lane sets hold all 64 columns, the load names one range per warp
-        float mw[8], vw[8];
-        {
-          float m0[8], m1[8], v0[8], v1[8];
-          umma::tmem_ld8(tl + cMw + 8 * part, m0);
-          umma::tmem_ld8(tl + cMw + 32 + 8 * part, m1);
-          umma::tmem_ld8(tl + cVw + 8 * part, v0);
-          umma::tmem_ld8(tl + cVw + 32 + 8 * part, v1);
-          umma::tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            mw[j] = h ? m1[j] : m0[j];
-            vw[j] = h ? v1[j] : v0[j];
-          }
-        }
         if (!umma::mbar_wait(&barM, pm_par)) s_fail = 1;
         pm_par ^= 1u;
         umma::fence_after_sync();
