@@ -57,6 +57,11 @@ __device__ __forceinline__ float rna_tf32(float v) {
   return __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xffffe000u);
 }
 
+// The same rounding for a value that is ONLY stored as a tensor-core operand: the tensor core ignores
+// the low 13 bits of an fp32 operand (shared memory and tensor memory alike; tests/test_umma_gpu.py checks it),
+// so adding half a unit of the last kept place is enough and the mask can be left out.
+__device__ __forceinline__ float bias_tf32(float v) { return __uint_as_float(__float_as_uint(v) + 0x1000u); }
+
 __device__ __forceinline__ float sanitize_gate(float g) {
   return fabsf(g) < kTinyState ? copysignf(kTinyState, g) : g;
 }
@@ -256,8 +261,8 @@ template <> struct Vec2<__nv_bfloat16> {
     return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p));
   }
 };
-__device__ __forceinline__ float4 rna4(float4 v) {
-  return make_float4(rna_tf32(v.x), rna_tf32(v.y), rna_tf32(v.z), rna_tf32(v.w));
+__device__ __forceinline__ float4 bias4(float4 v) {
+  return make_float4(bias_tf32(v.x), bias_tf32(v.y), bias_tf32(v.z), bias_tf32(v.w));
 }
 __device__ __forceinline__ float4 mul4(float4 a, float4 b) {
   return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w);

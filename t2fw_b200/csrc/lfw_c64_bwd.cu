@@ -291,10 +291,10 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
           const float4 m = mul4(Vec4<T>::ld(r_m + t * kDim), pv);
           const float4 v = mul4(Vec4<T>::ld(r_v + t * kDim), rcp4(pv));
           const int o = toff(t, f4);
-          *reinterpret_cast<float4 *>(t0p + o) = rna4(m);
-          *reinterpret_cast<float4 *>(t0p + kTile + o) = rna4(v);
-          *reinterpret_cast<float4 *>(t0p + 2 * kTile + o) = rna4(mul4(m, o_ref));
-          *reinterpret_cast<float4 *>(t0p + 3 * kTile + o) = rna4(mul4(v, oc_ref));
+          *reinterpret_cast<float4 *>(t0p + o) = bias4(m);
+          *reinterpret_cast<float4 *>(t0p + kTile + o) = bias4(v);
+          *reinterpret_cast<float4 *>(t0p + 2 * kTile + o) = bias4(mul4(m, o_ref));
+          *reinterpret_cast<float4 *>(t0p + 3 * kTile + o) = bias4(mul4(v, oc_ref));
         }
       }
       float mw[8], vw[8];      // own-side operand values of this thread, used again by the epilogue
@@ -419,7 +419,7 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         umma::tmem_ld8(tl + cZ + 8 * part, v);
         umma::tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = (s0 + j <= t) ? rna_tf32(v[j]) : 0.f;
+        for (int j = 0; j < 8; ++j) v[j] = (s0 + j <= t) ? bias_tf32(v[j]) : 0.f;
         unsigned char *t0p = sm + oT, *t1p = t0p + kTile;
         *reinterpret_cast<float4 *>(t0p + toff(t, s0)) = make_float4(v[0], v[1], v[2], v[3]);
         *reinterpret_cast<float4 *>(t0p + toff(t, s0 + 4)) = make_float4(v[4], v[5], v[6], v[7]);
@@ -460,6 +460,10 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       {
         const int n_fix = fix_n < kFixCap ? fix_n : kFixCap;
         const unsigned char *zt = sm + oT;
+        // the tile holds Z with the rounding increment but unmasked: the value the tensor core uses
+        auto zval = [](const unsigned char *p) {
+          return __uint_as_float(*reinterpret_cast<const uint32_t *>(p) & 0xffffe000u);
+        };
         // entries go to warps 8 .. 15: warps 0 and 4 are still issuing the second round
         for (int e = warp - 8; e >= 0 && e < n_fix; e += 8) {
           const int code = fix_code[e], t = code >> 8, rs = fix_slot[code & 0xff];
@@ -473,13 +477,13 @@ lfw_c64_bwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
             float a0 = 0.f, a1 = 0.f;      // two chains: the sums are latency-bound
             int s = t;
             if ((kC - t) & 1) {
-              a0 = row[s] * *reinterpret_cast<const float *>(zcol + s * 128 + ((ic ^ (s & 7)) << 4));
+              a0 = row[s] * zval(zcol + s * 128 + ((ic ^ (s & 7)) << 4));
               ++s;
             }
 #pragma unroll 4
             for (; s < kC; s += 2) {
-              a0 = fmaf(row[s], *reinterpret_cast<const float *>(zcol + s * 128 + ((ic ^ (s & 7)) << 4)), a0);
-              a1 = fmaf(row[s + 1], *reinterpret_cast<const float *>(zcol + (s + 1) * 128 + ((ic ^ ((s + 1) & 7)) << 4)), a1);
+              a0 = fmaf(row[s], zval(zcol + s * 128 + ((ic ^ (s & 7)) << 4)), a0);
+              a1 = fmaf(row[s + 1], zval(zcol + (s + 1) * 128 + ((ic ^ ((s + 1) & 7)) << 4)), a1);
             }
             acc = fmaf(a0 + a1, row[kDim + i], acc);
           }

@@ -197,9 +197,9 @@ lfw_c64_fwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
         const float4 qm = mul4(Vec4<T>::ld(r_q + t * kDim), pv);
         const float4 km = mul4(Vec4<T>::ld(r_k + t * kDim), rcp4(pv));
         const int o = toff(t, f4);
-        *reinterpret_cast<float4 *>(t0p + o) = rna4(qm);
-        *reinterpret_cast<float4 *>(t0p + kTile + o) = rna4(km);
-        *reinterpret_cast<float4 *>(t0p + 2 * kTile + o) = rna4(mul4(qm, g_ref));
+        *reinterpret_cast<float4 *>(t0p + o) = bias4(qm);
+        *reinterpret_cast<float4 *>(t0p + kTile + o) = bias4(km);
+        *reinterpret_cast<float4 *>(t0p + 2 * kTile + o) = bias4(mul4(qm, g_ref));
       }
     }
     {   // d side, feature-major: this thread = features 2 * lane, 2 * lane + 1, steps 4 * warp .. + 3
@@ -211,8 +211,8 @@ lfw_c64_fwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       const float4 i0 = rcp4(*reinterpret_cast<const float4 *>(pmF + f0 * kPmLd + t));
       const float4 i1 = rcp4(*reinterpret_cast<const float4 *>(pmF + (f0 + 1) * kPmLd + t));
       unsigned char *tX = sm + oT + 3 * kTile;
-      *reinterpret_cast<float4 *>(tX + toff(f0, t)) = rna4(mul4(make_float4(x2[0].x, x2[1].x, x2[2].x, x2[3].x), i0));
-      *reinterpret_cast<float4 *>(tX + toff(f0 + 1, t)) = rna4(mul4(make_float4(x2[0].y, x2[1].y, x2[2].y, x2[3].y), i1));
+      *reinterpret_cast<float4 *>(tX + toff(f0, t)) = bias4(mul4(make_float4(x2[0].x, x2[1].x, x2[2].x, x2[3].x), i0));
+      *reinterpret_cast<float4 *>(tX + toff(f0 + 1, t)) = bias4(mul4(make_float4(x2[0].y, x2[1].y, x2[2].y, x2[3].y), i1));
     }
     // ---- state tile S0' = A_REF .* S0 ----
     {
@@ -223,11 +223,11 @@ lfw_c64_fwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       const float4 s_hi = make_float4(Elem<T>::ld(e + 4), Elem<T>::ld(e + 5), Elem<T>::ld(e + 6), Elem<T>::ld(e + 7));
       unsigned char *tS = sm + oT + 4 * kTile;
       *reinterpret_cast<float4 *>(tS + toff(sr, sc0)) =
-          make_float4(rna_tf32(s_lo.x * a_ref), rna_tf32(s_lo.y * a_ref), rna_tf32(s_lo.z * a_ref),
-                      rna_tf32(s_lo.w * a_ref));
+          make_float4(bias_tf32(s_lo.x * a_ref), bias_tf32(s_lo.y * a_ref), bias_tf32(s_lo.z * a_ref),
+                      bias_tf32(s_lo.w * a_ref));
       *reinterpret_cast<float4 *>(tS + toff(sr, sc0 + 4)) =
-          make_float4(rna_tf32(s_hi.x * a_ref), rna_tf32(s_hi.y * a_ref), rna_tf32(s_hi.z * a_ref),
-                      rna_tf32(s_hi.w * a_ref));
+          make_float4(bias_tf32(s_hi.x * a_ref), bias_tf32(s_hi.y * a_ref), bias_tf32(s_hi.z * a_ref),
+                      bias_tf32(s_hi.w * a_ref));
     }
     umma::fence_async_smem();
     sync_all();       // tiles complete, raw buffer and start state consumed
@@ -267,7 +267,7 @@ lfw_c64_fwd_kernel(const __grid_constant__ seq::Maps mp, const T *__restrict__ s
       umma::tmem_ld8(tl + cP + 8 * part, v);
       umma::tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = (s0 + j <= t) ? rna_tf32(v[j]) : 0.f;
+      for (int j = 0; j < 8; ++j) v[j] = (s0 + j <= t) ? bias_tf32(v[j]) : 0.f;
       unsigned char *tP = sm + oT;
       *reinterpret_cast<float4 *>(tP + toff(t, s0)) = make_float4(v[0], v[1], v[2], v[3]);
       *reinterpret_cast<float4 *>(tP + toff(t, s0 + 4)) = make_float4(v[4], v[5], v[6], v[7]);

@@ -151,7 +151,7 @@ lfw_c64_local_kernel(const __grid_constant__ seq::Maps mp, float *__restrict__ M
           if (i > tq) s *= qt[i * kDim];
 #pragma unroll
         for (int j = 15; j >= 0; --j) {
-          w[j] = rna_tf32(Elem<T>::ld(vcol + (16 * tq + j) * kDim) * s);
+          w[j] = bias_tf32(Elem<T>::ld(vcol + (16 * tq + j) * kDim) * s);
           s *= g[j];
           hi = fmaxf(hi, fabsf(s));
         }
@@ -163,7 +163,7 @@ lfw_c64_local_kernel(const __grid_constant__ seq::Maps mp, float *__restrict__ M
         for (int j = 0; j < 16; ++j) {
           s *= g[j];
           hi = fmaxf(hi, fabsf(s));
-          w[j] = rna_tf32(Elem<T>::ld(vcol + (16 * tq + j) * kDim) * s);
+          w[j] = bias_tf32(Elem<T>::ld(vcol + (16 * tq + j) * kDim) * s);
         }
       }
       if (!(hi <= kRangeHi)) s_bad = 1;     // also catches NaN

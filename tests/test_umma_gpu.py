@@ -106,3 +106,47 @@ def test_umma_a_operand_from_tensor_memory(cuda):
     assert int(status.item()) == 0, "a bounded wait expired"
     ref = A.double() @ B.double().T
     assert (D.double() - ref).abs().max().item() <= 1e-4 * max(1.0, ref.abs().max().item())
+
+
+def _trunc(t):
+    """Drop the 13 low mantissa bits: what the tensor core keeps of an fp32 operand."""
+    i = t.contiguous().view(torch.int32)
+    return (i & ~0x1FFF).view(torch.float32)
+
+
+@pytest.mark.gpu
+def test_tf32_operands_are_truncated_not_rounded(cuda):
+    """The chunk kernels store operands with the rounding increment added but the low 13 bits left
+    in place, relying on the tensor core to ignore those bits - for operands in shared memory and in
+    tensor memory.  Unrounded inputs must therefore give the product of the truncated inputs."""
+    from t2fw_b200 import _lib
+
+    lib = _lib.load_core()
+    g = torch.Generator().manual_seed(23)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    fn = lib.t2fw_selftest_umma
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 4 + [ctypes.c_void_p, ctypes.c_void_p]
+    A1, A2, B1, B2 = (torch.randn(64, 64, generator=g).to(cuda) for _ in range(4))
+    D1 = torch.full((64, 64), float("nan"), device=cuda)
+    D2 = torch.full((64, 64), float("nan"), device=cuda)
+    rc = fn(A1.data_ptr(), B1.data_ptr(), A2.data_ptr(), B2.data_ptr(), D1.data_ptr(), D2.data_ptr(),
+            64, 64, 0, 0, status.data_ptr(), stream)
+    assert rc == 0, lib.t2fw_last_error().decode()
+
+    fn_ts = lib.t2fw_selftest_umma_ts
+    fn_ts.restype = ctypes.c_int
+    fn_ts.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_void_p, ctypes.c_void_p]
+    A3, B3 = (torch.randn(64, 64, generator=g).to(cuda) for _ in range(2))
+    D3 = torch.full((64, 64), float("nan"), device=cuda)
+    rc = fn_ts(A3.data_ptr(), B3.data_ptr(), D3.data_ptr(), status.data_ptr(), stream)
+    assert rc == 0, lib.t2fw_last_error().decode()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded wait expired"
+    for D, A, B in ((D1, A1, B1), (D2, A2, B2), (D3, A3, B3)):
+        kept = _trunc(A).double() @ _trunc(B).double().T
+        full = A.double() @ B.double().T
+        assert (D.double() - kept).abs().max().item() <= 1e-4       # fp32 accumulation only
+        assert (D.double() - full).abs().max().item() >= 1e-3       # the dropped bits do matter
