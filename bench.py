@@ -400,7 +400,9 @@ def run_seqsplit(args):
     if world == 1:      # the function needs a process group even for one rank
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29533")
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import datetime
+    # a short collective timeout: a rank that fails leaves the others with an error, not a long wait
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=180))
     from t2fw_b200 import _lib
     from t2fw_b200.parallel import max_over_ranks
     from t2fw_b200.seq_parallel import LFWSeqParallelFunction
