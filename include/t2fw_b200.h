@@ -157,6 +157,19 @@ int t2fw_lfw_segment_summary(int backward, const void *val_d, const void *gate_d
                              int64_t T, int64_t D, int64_t K, int dtype, void *scratch, size_t scratch_bytes,
                              void *stream);
 
+/* Fold of the exchanged segment summaries (one launch).  gathered: fp32 [n_segments][B][D*K + D + K],
+ * per segment and batch row (end_state [D][K], decay_d [D], decay_k [K]) as t2fw_lfw_segment_summary
+ * returns them (end_state converted to fp32); start, at_segment, total: fp32 [B][D][K].
+ *   backward = 0: start = the state before step 0; at_segment = the state that enters `segment`
+ *                 (segments 0 .. segment-1 applied in order); total (may be null) = the state after
+ *                 the last segment
+ *   backward = 1: start = the gradient of the final state; at_segment = the state gradient at the END
+ *                 of `segment` (segments n_segments-1 .. segment+1 applied, last one first); total unused
+ * No counterpart in the reference (no multi-device code); the recurrence is t2fw/torch.py:21-28. */
+int t2fw_lfw_fold_summaries(int backward, const float *gathered, const float *start, float *at_segment,
+                            float *total, int n_segments, int segment, int64_t B, int64_t D, int64_t K,
+                            void *stream);
+
 /*
  * Delta rule forward:  o_t = S_{t-1} q_t ,  delta_t = v_t - S_{t-1} k_t ,
  *                      S_t = S_{t-1} + delta_t k_t^T.

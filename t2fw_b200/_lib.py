@@ -23,7 +23,7 @@ EXPORTS = (
     "t2fw_dfw_forward_ws", "t2fw_dfw_forward_scratch_bytes",
     "t2fw_dfw_backward_noalloc_max_elems", "t2fw_dfw_backward_noalloc",
     "t2fw_lfw_fused_scratch_bytes", "t2fw_lfw_fused_forward", "t2fw_lfw_fused_backward",
-    "t2fw_lfw_segment_summary_scratch_bytes", "t2fw_lfw_segment_summary",
+    "t2fw_lfw_segment_summary_scratch_bytes", "t2fw_lfw_segment_summary", "t2fw_lfw_fold_summaries",
 )
 
 _core = None

@@ -252,6 +252,18 @@ int t2fw_lfw_segment_summary(int backward, const void *val_d, const void *gate_d
                              scratch, static_cast<cudaStream_t>(stream));
 }
 
+int t2fw_lfw_fold_summaries(int backward, const float *gathered, const float *start, float *at_segment,
+                            float *total, int n_segments, int segment, int64_t B, int64_t D, int64_t K,
+                            void *stream) {
+  T2FW_CHECK_ARG(B > 0 && D > 0 && K > 0, "sizes must be positive (B=%lld D=%lld K=%lld)", (long long)B, (long long)D,
+                 (long long)K);
+  T2FW_CHECK_ARG(n_segments > 0 && segment >= 0 && segment < n_segments, "segment %d of %d", segment, n_segments);
+  T2FW_CHECK_ARG(gathered && start && at_segment, "null pointer argument");
+  T2FW_CHECK_ARG(B <= (int64_t)1 << 40 && D <= 4096 && K <= 4096, "sizes out of range");
+  return lfw_fold_summaries(backward != 0, gathered, start, at_segment, total, n_segments, segment, B, D, K,
+                            static_cast<cudaStream_t>(stream));
+}
+
 // ---- fused decay-rule layer (heads read in place from the projection output) -------------------
 static int check_fused(int64_t B, int64_t T, int64_t H, int dtype) {
   T2FW_CHECK_ARG(B > 0 && T > 0 && H > 0, "sizes must be positive (B=%lld T=%lld H=%lld)", (long long)B,

@@ -165,6 +165,9 @@ size_t lfw_segment_summary_scratch_bytes(int64_t B, int64_t T);
 int lfw_segment_summary(bool backward, const void *val_d, const void *gate_d, const void *val_k, const void *gate_k,
                         void *end_state, float *A_out, float *G_out, int64_t B, int64_t T, int dtype, void *scratch,
                         cudaStream_t st);
+// fold of gathered segment summaries into the state / state gradient that enters segment r (lfw_fold.cu)
+int lfw_fold_summaries(bool backward, const float *gathered, const float *start, float *at_rank, float *total,
+                       int n, int r, int64_t B, int64_t D, int64_t K, cudaStream_t st);
 // fused layer form of the chunked path: qkvg [B][T][4*H*64] read in place (lfw_c64_host.cu)
 size_t lfw_fused_scratch_bytes(int64_t B, int64_t T, int H);
 int lfw_fused_forward(const void *qkvg, const void *state, void *out, void *ckpt, int64_t B, int64_t T, int H,

@@ -343,6 +343,31 @@ std::vector<at::Tensor> lfw_segment_summary(at::Tensor val_d, at::Tensor gate_d,
   return {end_state, decay_d, decay_k};
 }
 
+// Fold of gathered segment summaries [n][B][D*K+D+K] (fp32) over `start` [B,D,K] (fp32):
+// {state entering segment `segment`, state after the last segment} (backward = false) or
+// {state gradient at the end of `segment`} (backward = true).  See t2fw_lfw_fold_summaries.
+std::vector<at::Tensor> lfw_fold_summaries(at::Tensor gathered, at::Tensor start, int64_t segment, bool backward) {
+  T2FW_CHECK_INPUT(gathered);
+  T2FW_CHECK_INPUT(start);
+  TORCH_CHECK(gathered.scalar_type() == at::kFloat && start.scalar_type() == at::kFloat,
+              "fold_summaries: fp32 tensors expected");
+  TORCH_CHECK(gathered.dim() == 3 && start.dim() == 3, "fold_summaries: expected [n,B,D*K+D+K] and [B,D,K]");
+  const int64_t n = gathered.size(0), B = start.size(0), D = start.size(1), K = start.size(2);
+  TORCH_CHECK(gathered.size(1) == B && gathered.size(2) == D * K + D + K && gathered.device() == start.device(),
+              "fold_summaries: tensor shapes or devices do not agree");
+  TORCH_CHECK(n > 0 && n < (1 << 20) && segment >= 0 && segment < n, "fold_summaries: segment out of range");
+  const c10::cuda::CUDAGuard guard(start.device());
+  at::Tensor at_seg = at::empty_like(start);
+  at::Tensor total = backward ? at::Tensor() : at::empty_like(start);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check_status(t2fw_lfw_fold_summaries(backward ? 1 : 0, gathered.data_ptr<float>(), start.data_ptr<float>(),
+                                       at_seg.data_ptr<float>(), backward ? nullptr : total.data_ptr<float>(), (int)n,
+                                       (int)segment, B, D, K, stream.stream()),
+               "lfw.fold_summaries");
+  if (backward) return {at_seg};
+  return {at_seg, total};
+}
+
 }  // namespace
 
 TORCH_LIBRARY(lfw, m) {
@@ -352,6 +377,7 @@ TORCH_LIBRARY(lfw, m) {
   m.def("fused_forward", lfw_fused_forward);
   m.def("fused_backward", lfw_fused_backward);
   m.def("segment_summary", lfw_segment_summary);
+  m.def("fold_summaries", lfw_fold_summaries);
 }
 
 TORCH_LIBRARY(dfw, m) {

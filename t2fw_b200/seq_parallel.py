@@ -12,7 +12,8 @@ and the state gradient runs backwards through the same map.  One call therefore 
 
     forward:   summary of the own segment (two cheap kernels)  ->  ONE all-gather of the summaries
                ([B,64,64] + 2 x [B,64] floats per rank, received into local memory)  ->  fold of
-               the ranks before this one into the incoming state  ->  the ordinary forward kernels
+               the ranks before this one into the incoming state (one kernel: torch.ops.lfw.fold_summaries;
+               the CPU ranks of the tests fold with tensor operations)  ->  the ordinary forward kernels
     backward:  the same with the summaries of the output gradients, folded from the last rank down.
 
 No kernel reads another device's memory; the only collectives are the two all-gathers (and one
@@ -34,6 +35,11 @@ class CudaSegmentOps:
 
     def summary(self, val_d, gate_d, val_k, gate_k, backward):
         return torch.ops.lfw.segment_summary(val_d, gate_d, val_k, gate_k, backward)
+
+    def fold(self, gathered, start32, segment, backward):
+        """gathered [world, B, D*K+D+K] fp32 -> [state entering `segment`, state after the last segment]
+        (backward: [state gradient at the end of `segment`]), one launch."""
+        return torch.ops.lfw.fold_summaries(gathered, start32, segment, backward)
 
     def forward(self, x, f, q, k, fk, state):
         return torch.ops.lfw.forward(x, f, q, k, fk, state)
@@ -78,9 +84,10 @@ def fold_backward(grad_final, summaries, after, D, K):
 
 
 def all_gather_summaries(buf, group):
+    """[world, B, N]: every rank's packed summary, received into one local tensor."""
     world = dist.get_world_size(group)
-    out = [torch.empty_like(buf) for _ in range(world)]
-    dist.all_gather(out, buf, group=group)
+    out = torch.empty((world,) + tuple(buf.shape), dtype=buf.dtype, device=buf.device)
+    dist.all_gather(list(out.unbind(0)), buf, group=group)
     return out
 
 
@@ -102,18 +109,22 @@ class LFWSeqParallelFunction(torch.autograd.Function):
         x, f, q, k, fk = (t.contiguous() for t in (value, forget, query, key, f_key))
         L, A, G = ops.summary(x, f, k, fk, False)
         summaries = all_gather_summaries(pack_summary(L, A, G), group)
-        s_in32 = fold_forward(state, summaries, rank, D, K)
+        if hasattr(ops, "fold"):
+            s_in32, final32 = ops.fold(summaries, state.to(_acc(state.dtype)).contiguous(), rank, False)
+        else:
+            s_in32 = fold_forward(state, summaries, rank, D, K)
+            # the state after the whole sequence: carry on from this rank's incoming state
+            final32 = fold_forward(s_in32, summaries[rank:], world - rank, D, K)
         s_in = s_in32.to(state.dtype).contiguous()
         outputs, ckpt = ops.forward(x, f, q, k, fk, s_in)
-        # the state after the whole sequence: carry on from this rank's incoming state
-        final = fold_forward(s_in32, summaries[rank:], world - rank, D, K).to(state.dtype)
-        ctx.save_for_backward(x, f, q, k, fk, outputs, s_in, ckpt, *summaries)
+        final = final32.to(state.dtype)
+        ctx.save_for_backward(x, f, q, k, fk, outputs, s_in, ckpt, summaries[rank])
         ctx.group, ctx.ops, ctx.dims = group, ops, (D, K)
         return outputs, final
 
     @staticmethod
     def backward(ctx, grad_output, grad_final):
-        x, f, q, k, fk, outputs, s_in, ckpt, *fwd_summaries = ctx.saved_tensors
+        x, f, q, k, fk, outputs, s_in, ckpt, own_summary = ctx.saved_tensors
         group, ops, (D, K) = ctx.group, ctx.ops, ctx.dims
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         go = grad_output.contiguous()
@@ -121,9 +132,13 @@ class LFWSeqParallelFunction(torch.autograd.Function):
         dist.all_reduce(g_final, group=group)      # every rank may have used final_state
         Gb, _, _ = ops.summary(go, f, q, fk, True)
         # the decays of a segment are the same in both directions: take them from the forward exchange
-        _, A, G = unpack_summary(fwd_summaries[rank], D, K)
+        _, A, G = unpack_summary(own_summary, D, K)
         summaries = all_gather_summaries(pack_summary(Gb, A, G), group)
-        r_end = fold_backward(g_final, summaries, rank, D, K).to(s_in.dtype).contiguous()
+        if hasattr(ops, "fold"):
+            r_end32 = ops.fold(summaries, g_final, rank, True)[0]
+        else:
+            r_end32 = fold_backward(g_final, summaries, rank, D, K)
+        r_end = r_end32.to(s_in.dtype).contiguous()
         d_x, d_f, d_q, d_k, d_fk, d_s = ops.backward(go, r_end, x, f, q, k, fk, outputs, s_in, ckpt)
         if rank != 0:
             d_s = torch.zeros_like(d_s)

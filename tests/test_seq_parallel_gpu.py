@@ -71,13 +71,22 @@ def test_split_pipeline_with_emulated_ranks(cuda, cuts):
         o, c = ops.forward(xs, fs, qs, ks, fks, s_in)
         outs.append(o); ckpts.append(c); s_ins.append(s_in)
     final = fold_forward(s, summ, len(seg), 64, 64).to(dt)
+    # the one-launch fold of the product path against the tensor-operation fold, every rank
+    gathered = torch.stack(summ)
+    for r in range(len(seg)):
+        at_r, total = ops.fold(gathered, s.float().contiguous(), r, False)
+        assert max_rel_err(at_r, fold_forward(s, summ, r, 64, 64)) <= 1e-6
+        assert max_rel_err(total, fold_forward(s, summ, len(seg), 64, 64)) <= 1e-6
     bsum = []
     for r, (xs, fs, qs, ks, fks, gos) in enumerate(seg):
         Gb, _, _ = ops.summary(gos, fs, qs, fks, True)
         _, A, G = unpack_summary(summ[r], 64, 64)
         bsum.append(pack_summary(Gb, A, G))
     grads = []
+    bgathered = torch.stack(bsum)
     for r, (xs, fs, qs, ks, fks, gos) in enumerate(seg):
+        (r_end_k,) = ops.fold(bgathered, gs.float().contiguous(), r, True)
+        assert max_rel_err(r_end_k, fold_backward(gs, bsum, r, 64, 64)) <= 1e-6
         r_end = fold_backward(gs, bsum, r, 64, 64).to(dt).contiguous()
         grads.append(ops.backward(gos, r_end, xs, fs, qs, ks, fks, outs[r], s_ins[r], ckpts[r]))
     torch.cuda.synchronize()
