@@ -107,6 +107,12 @@ class LFWSeqParallelFunction(torch.autograd.Function):
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         D, K = value.shape[2], key.shape[2]
         x, f, q, k, fk = (t.contiguous() for t in (value, forget, query, key, f_key))
+        if world == 1:      # nothing to exchange: the ordinary call, its last checkpoint is the final state
+            s_in = state.contiguous()
+            outputs, ckpt = ops.forward(x, f, q, k, fk, s_in)
+            ctx.save_for_backward(x, f, q, k, fk, outputs, s_in, ckpt)
+            ctx.group, ctx.ops, ctx.dims = group, ops, (D, K)
+            return outputs, ckpt[:, -1].clone()
         L, A, G = ops.summary(x, f, k, fk, False)
         summaries = all_gather_summaries(pack_summary(L, A, G), group)
         if hasattr(ops, "fold"):
@@ -124,10 +130,14 @@ class LFWSeqParallelFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output, grad_final):
-        x, f, q, k, fk, outputs, s_in, ckpt, own_summary = ctx.saved_tensors
         group, ops, (D, K) = ctx.group, ctx.ops, ctx.dims
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         go = grad_output.contiguous()
+        if world == 1:
+            x, f, q, k, fk, outputs, s_in, ckpt = ctx.saved_tensors
+            grads = ops.backward(go, grad_final.to(s_in.dtype).contiguous(), x, f, q, k, fk, outputs, s_in, ckpt)
+            return (*grads, None, None)
+        x, f, q, k, fk, outputs, s_in, ckpt, own_summary = ctx.saved_tensors
         g_final = grad_final.to(_acc(grad_final.dtype)).contiguous()
         dist.all_reduce(g_final, group=group)      # every rank may have used final_state
         Gb, _, _ = ops.summary(go, f, q, fk, True)

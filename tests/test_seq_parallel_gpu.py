@@ -99,6 +99,31 @@ def test_split_pipeline_with_emulated_ranks(cuda, cuts):
     assert max_rel_err(grads[0][5], r_grads[5]) <= GRAD_TOL[dt]
 
 
+@pytest.mark.gpu
+def test_single_rank_group_is_the_ordinary_call(cuda, tmp_path):
+    """A group of one rank exchanges nothing: same results as LFWFunction, bit for bit."""
+    import torch.distributed as dist
+
+    from t2fw_b200.functional_lfw import LFWFunction
+    from t2fw_b200.seq_parallel import LFWSeqParallelFunction
+
+    dt = torch.float16
+    x, f, q, k, fk, s, go, gs = to_dev(lfw_inputs(3, 200, 64, 64, "sigmoid", 0.5, 77), dt, cuda)
+    dist.init_process_group("gloo", init_method="file://" + str(tmp_path / "store"), rank=0, world_size=1)
+    try:
+        la = [t.clone().requires_grad_(True) for t in (x, f, q, k, fk, s)]
+        out_a, fin_a = LFWSeqParallelFunction.apply(*la)
+        ga = torch.autograd.grad([out_a, fin_a], la, [go, gs])
+    finally:
+        dist.destroy_process_group()
+    lb = [t.clone().requires_grad_(True) for t in (x, f, q, k, fk, s)]
+    out_b, fin_b = LFWFunction.apply(*lb)
+    gb = torch.autograd.grad([out_b, fin_b], lb, [go, gs])
+    assert torch.equal(out_a, out_b) and torch.equal(fin_a, fin_b)
+    for a, b in zip(ga, gb):
+        assert torch.equal(a, b)
+
+
 CHILD = r"""
 import os, sys, numpy as np, torch, torch.distributed as dist
 sys.path.insert(0, {tests!r}); sys.path.insert(0, {root!r})
