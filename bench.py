@@ -963,7 +963,9 @@ def run_ours(args):
                       "three streams with %d steps in flight (a step's D2H overlaps the next steps' H2D and compute)"
                       % ("one copy per tensor" if args.e2e_separate_inputs else "one copy of the arena that holds them", n_slots),
                "wall_ms_per_step": wall * 1e3 / e2e_steps,
-               "blocks_ms_per_step": [b[0] / e2e_steps for b in blocks], "reported_block": "median"}
+               "blocks_ms_per_step": [b[0] / e2e_steps for b in blocks], "reported_block": "median",
+               # the least disturbed block, for information: what the loop does when the host is quiet
+               "fastest_block_value": rows_all * T * e2e_steps / (min(b[0] for b in blocks) * 1e-3)}
 
     if rank != 0:
         if world > 1:
